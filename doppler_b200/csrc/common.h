@@ -1,0 +1,170 @@
+// Internal definitions shared by the translation units of libdoppler_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/doppler_b200.h"
+
+struct dp_buf_s {
+  void *dptr = nullptr;
+  size_t bytes = 0;     // requested
+  size_t capacity = 0;  // bucket
+  dp_ctx *ctx = nullptr;
+  bool active = false;
+  std::string label;
+};
+
+struct dp_tp_state;  // tp.cu
+
+struct dp_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  size_t smem_optin = 0;
+  std::string err;
+  uint64_t launches = 0;
+  // buffer pool: bucket size -> idle allocations
+  std::multimap<size_t, dp_buf_s *> idle;
+  std::vector<dp_buf_s *> all;
+  dp_pool_stats stats{};
+  // lazily grown scratch for split-K attention partials (stream ordered)
+  dp_buf attn_scratch = nullptr;
+  dp_buf argmax_scratch = nullptr;
+  dp_recorder *active_recorder = nullptr;
+  dp_tp_state *tp = nullptr;
+};
+
+struct dp_recorder {
+  dp_ctx *ctx = nullptr;
+  std::string label;
+  bool capture = false;
+  bool open = false;
+  std::vector<dp_buf> temporaries;
+  uint32_t ops = 0;
+  uint64_t launches_at_begin = 0;
+};
+
+struct dp_graph {
+  dp_ctx *ctx = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernels = 0;
+};
+
+dp_status dp_fail(dp_ctx *ctx, dp_status st, const char *fmt, ...);
+
+#define DP_CUDA(ctx, expr)                                                                  \
+  do {                                                                                      \
+    cudaError_t _e = (expr);                                                                \
+    if (_e != cudaSuccess)                                                                  \
+      return dp_fail((ctx), _e == cudaErrorMemoryAllocation ? DP_ERR_OOM : DP_ERR_CUDA,     \
+                     "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+  } while (0)
+
+#define DP_CHECK(ctx, cond, ...)                                   \
+  do {                                                             \
+    if (!(cond)) return dp_fail((ctx), DP_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define DP_TRY(expr)                 \
+  do {                               \
+    dp_status _s = (expr);           \
+    if (_s != DP_OK) return _s;      \
+  } while (0)
+
+// Every kernel launch of this library goes through here so launches are counted
+// and launch errors surface as a status.
+#define DP_LAUNCH(ctx, kernel, grid, block, smem, ...)                                   \
+  do {                                                                                   \
+    kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);                     \
+    (ctx)->launches++;                                                                   \
+    cudaError_t _e = cudaGetLastError();                                                 \
+    if (_e != cudaSuccess)                                                               \
+      return dp_fail((ctx), DP_ERR_CUDA, "launch of %s failed: %s", #kernel,             \
+                     cudaGetErrorString(_e));                                            \
+  } while (0)
+
+static inline size_t dp_dtype_size(dp_dtype t) {
+  switch (t) {
+    case DP_F32: return 4;
+    case DP_F16: return 2;
+    case DP_I32: return 4;
+    default: return 0;
+  }
+}
+
+static inline const char *dp_dtype_name(dp_dtype t) {
+  switch (t) {
+    case DP_F32: return "f32";
+    case DP_F16: return "f16";
+    case DP_Q4K: return "q4k";
+    case DP_I32: return "i32";
+  }
+  return "?";
+}
+
+static inline size_t dp_cdiv(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Pointer of a tensor/weight (buffer base + offset), or nullptr
+static inline char *dp_tptr(const dp_tensor *t) {
+  return (t && t->buf) ? (char *)t->buf->dptr + t->offset : nullptr;
+}
+static inline size_t dp_tavail(const dp_tensor *t) {
+  return (t && t->buf && t->offset <= t->buf->capacity) ? t->buf->capacity - t->offset : 0;
+}
+
+// output helper: use out_buf when given (checked for size), else acquire from the pool
+dp_status dp_out_buffer(dp_ctx *ctx, dp_buf out_buf, size_t offset, size_t bytes, const char *label,
+                        dp_buf *result);
+void dp_note_op(dp_ctx *ctx, dp_recorder *rec);
+dp_status dp_check_rec(dp_ctx *ctx, dp_recorder *rec);
+dp_status dp_scratch(dp_ctx *ctx, dp_buf *slot, size_t bytes, const char *label);
+
+// ---- kernel launchers (one per .cu) --------------------------------------
+dp_status dpk_dequant_q4k(dp_ctx *ctx, const uint8_t *packed, size_t rows, size_t bpr, size_t K,
+                          void *out, dp_dtype out_dtype);
+dp_status dpk_gemv_q4k(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype,
+                       int N, int K, float alpha, const float *residual);
+dp_status dpk_gemm_q4k_simt(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C,
+                            dp_dtype c_dtype, int M, int N, int K, float alpha);
+dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_dtype, void *C,
+                        dp_dtype c_dtype, int M, int N, int K, float alpha);
+dp_status dpk_gemv_f32w(dp_ctx *ctx, const float *W, const float *A, float *C, int M, int N, int K,
+                        float alpha);
+struct dpk_attn_params {
+  const float *q;
+  const __half *k, *v;
+  float *out;
+  int batch, seq_len, kv_len, num_heads, num_kv_heads, head_dim;
+  float scale, softcap;
+  int causal, start_pos, sliding_window, kv_start;
+  size_t kv_batch_stride;
+  const int *kv_lens;
+};
+dp_status dpk_attention(dp_ctx *ctx, const dpk_attn_params &p);
+// variant with caller-provided scratch (no allocation); scratch_bytes must cover dpk_attention_scratch_bytes
+size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *splits_out);
+dp_status dpk_attention_with_scratch(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);
+
+dp_status dpk_rmsnorm(dp_ctx *ctx, const float *x, const void *w, bool w_f16, const float *residual,
+                      bool pre_residual, float *residual_sum_out, float *y, int rows, int size,
+                      float eps, bool weight_offset, float output_scale);
+dp_status dpk_rmsnorm_qk(dp_ctx *ctx, float *q, const float *qw, float *k, const float *kw, int q_rows,
+                         int k_rows, int head_dim, float eps, bool weight_offset);
+dp_status dpk_rope(dp_ctx *ctx, float *x, const float *cos_t, const float *sin_t, int seq_len,
+                   int num_heads, int head_dim, int rotary_dim, int pair_span, bool interleaved,
+                   int start_pos);
+dp_status dpk_silu_mul(dp_ctx *ctx, const float *up, const float *gate, float *out, size_t n, float clamp_max);
+dp_status dpk_residual_add(dp_ctx *ctx, const float *a, const float *b, float *out, size_t n, float scale);
+dp_status dpk_gather_f16(dp_ctx *ctx, const int *ids, const __half *table, float *out, int n_ids, int hidden);
+dp_status dpk_kv_write(dp_ctx *ctx, const float *src, __half *dst, size_t n);
+dp_status dpk_argmax(dp_ctx *ctx, const float *logits, int n, int pad_id, int *out, int out_index,
+                     float *scratch_vals, int *scratch_idx, int index_base, float *best_val_out);

@@ -1,0 +1,593 @@
+// Decoder runner: packed-Q4_K weight upload, f16 KV allocation and the
+// decode / prefill schedule for a dense Qwen3-shaped model.
+//
+// Replaces the slices of the reference that feed the kernels:
+//   - src/loader/tensors/tensor-loader.js:540-558 (loadQ4KFused: 144-byte blocks stay packed),
+//   - src/inference/kv-cache/base.js:99-153 (contiguous f16 cache),
+//   - src/inference/pipelines/text/generator-steps.js:588 (decodeStep) and layer.js:682
+//     (processLayerGPU): one recorded command buffer per token there, one CUDA
+//     graph per decode step here; the sampled token and the position stay on the
+//     device so consecutive steps need no host round trip.
+// Op order and rounding points follow the reference pipeline: rmsnorm -> q/k/v ->
+// per-head QK RMSNorm -> rotate-half RoPE -> K,V rounded to f16 into the cache ->
+// attention over the cache (including the new token) -> o_proj + residual ->
+// rmsnorm -> gate/up -> silu(gate)*up -> down + residual; final rmsnorm -> f16 LM
+// head -> greedy argmax (lower index wins ties).
+#include "common.h"
+#include "q4k.cuh"
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
+                          int M, int N, int K, float alpha, bool *handled);
+dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
+                            float alpha, const float *residual, bool *handled);
+dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
+dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
+bool dp_tp_ready(dp_ctx *ctx);
+
+struct LayerW {
+  dp_buf qkv = nullptr, o = nullptr, gateup = nullptr, down = nullptr;
+  float *in_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+};
+
+struct dp_model {
+  dp_ctx *ctx;
+  dp_model_cfg cfg;
+  int nh, nkv, qdim, kvdim, inter, vocab_l, vocab0;  // this rank's share
+  int T;                                              // rows of the activation buffers
+  std::vector<LayerW> layers;
+  dp_buf norms = nullptr, embed = nullptr, lm_head = nullptr;
+  float *final_norm = nullptr;
+  std::vector<dp_buf> kc, vc;
+  dp_buf rope = nullptr;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  dp_buf act = nullptr;  // one slab for all activations
+  float *h, *n, *qkv, *q, *att, *gu, *actv, *partial, *logits;
+  dp_buf state = nullptr;  // device ints: pos[B], kvlen[B], tok[B], step, then argmax scratch
+  int *d_pos, *d_kvlen, *d_tok, *d_step;
+  float *am_vals; int *am_idx; float *am_best; int *am_pair_i; float *am_gather;
+  dp_buf out_tokens = nullptr;
+  int out_tokens_cap = 0;
+  dp_buf attn_scratch = nullptr;
+  int attn_splits_decode = 1;
+  std::vector<int> seq_len;
+  dp_graph *graph[2] = {nullptr, nullptr};
+  int graph_batch[2] = {0, 0};
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  double last_ms = 0;
+  size_t weight_bytes = 0;
+  int allreduce_mode = 0;
+};
+
+// ---- model-specific kernels ---------------------------------------------------
+
+// Per-head QK RMSNorm + rotate-half RoPE + KV append, one warp per (token, head).
+// Reference ops fused here: rmsnorm_qk.wgsl:75-118, rope.wgsl:62-106,
+// kv_cache_write_f32_to_f16.wgsl:19 (the reference ships the same fusion as
+// split_qkv_rmsnorm_rope_qk_f16kv_cache.wgsl).  head_dim must be a multiple of 64.
+__global__ void __launch_bounds__(256) qk_norm_rope_kv_kernel(
+    const float *__restrict__ qkv, float *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc,
+    const float *__restrict__ q_norm, const float *__restrict__ k_norm, const float *__restrict__ cos_t,
+    const float *__restrict__ sin_t, const int *__restrict__ pos_arr, int start_pos, int seq, int tokens, int nh,
+    int nkv, int D, float eps, size_t kv_seq_stride) {
+  const int heads = nh + 2 * nkv;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (gw >= tokens * heads) return;
+  const int t = gw / heads, hd = gw % heads;
+  const int pos = pos_arr ? pos_arr[t] : start_pos + t;
+  const int sq = pos_arr ? t : seq;
+  const float *src = qkv + (size_t)t * heads * D + (size_t)hd * D;
+  const int half = D / 2, per = half / 32;  // pairs per lane
+  float x0[4], x1[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) if (i < per) { x0[i] = src[lane + 32 * i]; x1[i] = src[lane + 32 * i + half]; }
+  if (hd < nh + nkv) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (i < per) ss = fmaf(x0[i], x0[i], fmaf(x1[i], x1[i], ss));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    const float *w = hd < nh ? q_norm : k_norm;
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (i < per) {
+      const int d = lane + 32 * i;
+      const float a = x0[i] * inv * w[d], b = x1[i] * inv * w[d + half];
+      const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
+      x0[i] = a * c - b * s;
+      x1[i] = a * s + b * c;
+    }
+  }
+  if (hd < nh) {
+    float *dst = q_out + ((size_t)t * nh + hd) * D;
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (i < per) { dst[lane + 32 * i] = x0[i]; dst[lane + 32 * i + half] = x1[i]; }
+  } else {
+    const int kh = hd < nh + nkv ? hd - nh : hd - nh - nkv;
+    __half *dst = (hd < nh + nkv ? kc : vc) + (size_t)sq * kv_seq_stride + ((size_t)pos * nkv + kh) * D;
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (i < per) {
+      dst[lane + 32 * i] = __float2half_rn(x0[i]);
+      dst[lane + 32 * i + half] = __float2half_rn(x1[i]);
+    }
+  }
+}
+
+// out[t, :] = silu(gu[t, 0:I]) * gu[t, I:2I]   (silu.wgsl:30-37,98-104, sigmoid argument clamped to +-15)
+__global__ void silu_gateup_kernel(const float *__restrict__ gu, float *__restrict__ out, int tokens, int inter) {
+  const size_t total = (size_t)tokens * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter, c = i % inter;
+    const float g = gu[t * 2 * inter + c], u = gu[t * 2 * inter + inter + c];
+    const float cl = fminf(fmaxf(g, -15.0f), 15.0f);
+    out[i] = (g * (1.0f / (1.0f + expf(-cl)))) * u;
+  }
+}
+
+// after a decode step: record the sampled tokens and move every sequence on by one
+__global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, int *out_tokens, int batch) {
+  const int b = threadIdx.x;
+  const int s = *step;
+  if (b < batch) { out_tokens[s * batch + b] = tok[b]; pos[b] += 1; kvlen[b] += 1; }
+  __syncthreads();
+  if (b == 0) *step = s + 1;
+}
+
+// combine the per-rank (best value, index) pairs of a vocabulary-sharded argmax;
+// ties go to the lower global index (sample.wgsl:45-53)
+__global__ void argmax_merge_kernel(const float *pairs, int ranks, int batch, int *tok) {
+  const int b = threadIdx.x;
+  if (b >= batch) return;
+  float bv = -3.402823e+38f;
+  int bi = 0x7fffffff;
+  for (int r = 0; r < ranks; r++) {
+    const float v = pairs[(r * batch + b) * 2];
+    const int i = __float_as_int(pairs[(r * batch + b) * 2 + 1]);
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  tok[b] = bi;
+}
+
+__global__ void pack_pair_kernel(const float *best, const int *tok, float *pairs, int batch) {
+  const int b = threadIdx.x;
+  if (b < batch) { pairs[2 * b] = best[b]; pairs[2 * b + 1] = __int_as_float(tok[b]); }
+}
+
+// ---- create / destroy -----------------------------------------------------------
+static size_t q4k_bytes(size_t n, size_t k) { return n * dp_cdiv(k, DP_QK_K) * DP_Q4K_BLOCK_BYTES; }
+static size_t align_up(size_t v, size_t a) { return dp_cdiv(v, a) * a; }
+
+extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_model **out) {
+  if (!ctx || !cfg || !out) return DP_ERR_INVALID;
+  const dp_model_cfg &c = *cfg;
+  const int p = c.tp_size > 0 ? c.tp_size : 1;
+  DP_CHECK(ctx, c.n_layers > 0 && c.hidden > 0 && c.n_heads > 0 && c.n_kv_heads > 0 && c.head_dim > 0 && c.inter > 0 &&
+                    c.vocab > 0 && c.max_seq > 0, "model: invalid configuration");
+  DP_CHECK(ctx, c.head_dim % 64 == 0 && c.head_dim <= 256, "model: head_dim %d must be 64, 128, 192 or 256", c.head_dim);
+  DP_CHECK(ctx, c.n_heads % c.n_kv_heads == 0, "model: n_heads %d not a multiple of n_kv_heads %d", c.n_heads, c.n_kv_heads);
+  DP_CHECK(ctx, c.tp_rank >= 0 && c.tp_rank < p, "model: tp_rank %d outside [0,%d)", c.tp_rank, p);
+  DP_CHECK(ctx, c.n_kv_heads % p == 0 && c.n_heads % p == 0, "model: heads (%d/%d) do not divide over %d ranks", c.n_heads, c.n_kv_heads, p);
+  DP_CHECK(ctx, c.inter % (p * DP_QK_K) == 0 && (c.n_heads * c.head_dim) % (p * DP_QK_K) == 0,
+           "model: row-parallel matrices must split on 256-element super-blocks over %d ranks", p);
+  DP_CHECK(ctx, c.hidden % DP_QK_K == 0, "model: hidden %d must be a multiple of 256", c.hidden);
+  DP_CHECK(ctx, c.vocab % p == 0, "model: vocab %d does not divide over %d ranks", c.vocab, p);
+  DP_CHECK(ctx, p == 1 || dp_tp_ready(ctx), "model: tp_size %d needs dp_tp_init on this context first", p);
+  dp_model *m = new dp_model();
+  m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
+  if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
+  DP_CHECK(ctx, m->cfg.max_batch <= 256, "model: max_batch %d > 256", m->cfg.max_batch);
+  m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
+  m->qdim = m->nh * c.head_dim; m->kvdim = m->nkv * c.head_dim;
+  m->inter = c.inter / p; m->vocab_l = c.vocab / p; m->vocab0 = m->vocab_l * c.tp_rank;
+  const int B = m->cfg.max_batch;
+  m->T = B > 512 ? B : 512;  // prefill chunk
+  m->layers.resize(c.n_layers);
+  m->seq_len.assign(B, 0);
+  dp_status st = DP_OK;
+  auto acquire = [&](size_t bytes, const char *label, dp_buf *b) { if (st == DP_OK) st = dp_buf_acquire(ctx, bytes, label, b); };
+  const int H = c.hidden, D = c.head_dim;
+  for (int l = 0; l < c.n_layers; l++) {
+    LayerW &L = m->layers[l];
+    acquire(q4k_bytes(m->qdim + 2 * m->kvdim, H), "w_qkv_q4k", &L.qkv);
+    acquire(q4k_bytes(H, m->qdim), "w_o_q4k", &L.o);
+    acquire(q4k_bytes(2 * m->inter, H), "w_gateup_q4k", &L.gateup);
+    acquire(q4k_bytes(H, m->inter), "w_down_q4k", &L.down);
+    if (st == DP_OK) m->weight_bytes += L.qkv->bytes + L.o->bytes + L.gateup->bytes + L.down->bytes;
+  }
+  const size_t per_layer_norm = (size_t)2 * H + 2 * D;
+  acquire(((size_t)c.n_layers * per_layer_norm + H) * 4, "norm_weights", &m->norms);
+  acquire((size_t)c.vocab * H * 2, "embedding_f16", &m->embed);
+  acquire((size_t)m->vocab_l * H * 2, "lm_head_f16", &m->lm_head);
+  const size_t kv_bytes = (size_t)B * c.max_seq * m->kvdim * 2;
+  m->kc.assign(c.n_layers, nullptr); m->vc.assign(c.n_layers, nullptr);
+  for (int l = 0; l < c.n_layers; l++) { acquire(kv_bytes, "kv_cache_keys", &m->kc[l]); acquire(kv_bytes, "kv_cache_values", &m->vc[l]); }
+  acquire((size_t)c.max_seq * D * 4, "rope_tables", &m->rope);
+  const size_t T = m->T;
+  const size_t n_h = align_up(T * H, 64), n_qkv = align_up(T * (m->qdim + 2 * m->kvdim), 64), n_q = align_up(T * m->qdim, 64);
+  const size_t n_gu = align_up(T * 2 * m->inter, 64), n_act = align_up(T * m->inter, 64), n_log = align_up((size_t)B * m->vocab_l, 64);
+  acquire((3 * n_h + n_qkv + 2 * n_q + n_gu + n_act + n_log) * 4, "activations", &m->act);
+  acquire(4096 + 1024 + 2048 + 16384 + (size_t)B * 256 * 8, "decode_state", &m->state);
+  // split-K scratch sized for the longest context
+  dpk_attn_params ap{};
+  ap.batch = B; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
+  size_t sbytes = dpk_attention_scratch_bytes(ctx, ap, &m->attn_splits_decode);
+  acquire(sbytes ? sbytes : 256, "attention_split_partials", &m->attn_scratch);
+  if (st != DP_OK) { dp_model_destroy(m); return st; }
+  m->weight_bytes += m->lm_head->bytes;
+
+  float *nb = (float *)m->norms->dptr;
+  for (int l = 0; l < c.n_layers; l++) {
+    LayerW &L = m->layers[l];
+    L.in_norm = nb; nb += H; L.post_norm = nb; nb += H; L.q_norm = nb; nb += D; L.k_norm = nb; nb += D;
+  }
+  m->final_norm = nb;
+  float *a = (float *)m->act->dptr;
+  m->h = a; a += n_h; m->n = a; a += n_h; m->partial = a; a += n_h; m->qkv = a; a += n_qkv; m->q = a; a += n_q;
+  m->att = a; a += n_q; m->gu = a; a += n_gu; m->actv = a; a += n_act; m->logits = a;
+  int *si = (int *)m->state->dptr;
+  m->d_pos = si; m->d_kvlen = si + 256; m->d_tok = si + 512; m->d_step = si + 768;
+  char *sp = (char *)m->state->dptr + 4096;
+  m->am_best = (float *)sp; sp += 1024;             // best logit per sequence
+  m->am_pair_i = (int *)sp; sp += 2048;             // (value, index) per sequence, this rank
+  m->am_gather = (float *)sp; sp += 16384;          // the pairs of up to 8 ranks
+  m->am_vals = (float *)sp; m->am_idx = (int *)(m->am_vals + (size_t)B * 256);
+  // rope tables (host build, init-rope.js semantics)
+  {
+    std::vector<float> cs((size_t)c.max_seq * D / 2), sn((size_t)c.max_seq * D / 2);
+    dp_rope_tables((double)c.rope_theta, D, c.max_seq, cs.data(), sn.data());
+    m->rope_cos = (float *)m->rope->dptr; m->rope_sin = m->rope_cos + (size_t)c.max_seq * D / 2;
+    st = dp_buf_upload(ctx, m->rope, cs.data(), 0, cs.size() * 4);
+    if (st == DP_OK) st = dp_buf_upload(ctx, m->rope, sn.data(), cs.size() * 4, sn.size() * 4);
+  }
+  if (st == DP_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
+    st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaEventCreate failed");
+  if (st == DP_OK) st = dp_buf_fill(ctx, m->state, 0, 0, m->state->capacity);
+  if (st != DP_OK) { dp_model_destroy(m); return st; }
+  *out = m;
+  return DP_OK;
+}
+
+extern "C" void dp_model_destroy(dp_model *m) {
+  if (!m) return;
+  dp_ctx *ctx = m->ctx;
+  cudaStreamSynchronize(ctx->stream);
+  for (int i = 0; i < 2; i++) if (m->graph[i]) dp_graph_destroy(m->graph[i]);
+  auto rel = [&](dp_buf b) { if (b) dp_buf_release(ctx, b); };
+  for (LayerW &L : m->layers) { rel(L.qkv); rel(L.o); rel(L.gateup); rel(L.down); }
+  rel(m->norms); rel(m->embed); rel(m->lm_head); rel(m->rope); rel(m->act); rel(m->state); rel(m->out_tokens); rel(m->attn_scratch);
+  for (dp_buf b : m->kc) rel(b);
+  for (dp_buf b : m->vc) rel(b);
+  if (m->ev0) cudaEventDestroy(m->ev0);
+  if (m->ev1) cudaEventDestroy(m->ev1);
+  delete m;
+}
+
+// ---- weight upload ------------------------------------------------------------------
+extern "C" dp_status dp_model_load_q4k(dp_model *m, int layer, dp_weight_id which, const void *host, int N, int K) {
+  if (!m) return DP_ERR_INVALID;
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  DP_CHECK(ctx, layer >= 0 && layer < c.n_layers, "loadQ4K: layer %d out of range", layer);
+  DP_CHECK(ctx, host != nullptr, "loadQ4K: null host pointer");
+  const int p = c.tp_size, r = c.tp_rank, H = c.hidden;
+  LayerW &L = m->layers[layer];
+  const size_t bpr = dp_cdiv((size_t)K, DP_QK_K), row_bytes = bpr * DP_Q4K_BLOCK_BYTES;
+  auto expect = [&](int n, int k, const char *name) -> dp_status {
+    if (N != n || K != k) return dp_fail(ctx, DP_ERR_INVALID, "loadQ4K: %s expects shape [%d,%d], got [%d,%d]", name, n, k, N, K);
+    return DP_OK;
+  };
+  const uint8_t *src = (const uint8_t *)host;
+  switch (which) {
+    case DP_W_Q: case DP_W_K: case DP_W_V: {  // column parallel: contiguous rows of this rank
+      const int full = which == DP_W_Q ? c.n_heads * c.head_dim : c.n_kv_heads * c.head_dim;
+      DP_TRY(expect(full, H, which == DP_W_Q ? "q_proj" : which == DP_W_K ? "k_proj" : "v_proj"));
+      const int rows = full / p;
+      const size_t dst_row = which == DP_W_Q ? 0 : which == DP_W_K ? (size_t)m->qdim : (size_t)m->qdim + m->kvdim;
+      return dp_buf_upload(ctx, L.qkv, src + (size_t)r * rows * row_bytes, dst_row * row_bytes, (size_t)rows * row_bytes);
+    }
+    case DP_W_GATE: case DP_W_UP: {
+      DP_TRY(expect(c.inter, H, which == DP_W_GATE ? "gate_proj" : "up_proj"));
+      const int rows = c.inter / p;
+      const size_t dst_row = which == DP_W_GATE ? 0 : (size_t)m->inter;
+      return dp_buf_upload(ctx, L.gateup, src + (size_t)r * rows * row_bytes, dst_row * row_bytes, (size_t)rows * row_bytes);
+    }
+    case DP_W_O: case DP_W_DOWN: {  // row parallel: this rank's super-block columns of every row
+      const int kfull = which == DP_W_O ? c.n_heads * c.head_dim : c.inter;
+      DP_TRY(expect(H, kfull, which == DP_W_O ? "o_proj" : "down_proj"));
+      dp_buf dst = which == DP_W_O ? L.o : L.down;
+      if (p == 1) return dp_buf_upload(ctx, dst, src, 0, (size_t)N * row_bytes);
+      const size_t bl = bpr / p, seg = bl * DP_Q4K_BLOCK_BYTES;
+      std::vector<uint8_t> stage((size_t)N * seg);
+      for (int n = 0; n < N; n++) memcpy(stage.data() + (size_t)n * seg, src + (size_t)n * row_bytes + (size_t)r * seg, seg);
+      return dp_buf_upload(ctx, dst, stage.data(), 0, stage.size());
+    }
+    default:
+      return dp_fail(ctx, DP_ERR_INVALID, "loadQ4K: weight id %d is not a Q4_K matrix", (int)which);
+  }
+}
+
+extern "C" dp_status dp_model_load_norm(dp_model *m, int layer, dp_weight_id which, const float *host, int n) {
+  if (!m) return DP_ERR_INVALID;
+  dp_ctx *ctx = m->ctx;
+  DP_CHECK(ctx, layer >= 0 && layer < m->cfg.n_layers && host, "loadNorm: bad layer or null pointer");
+  LayerW &L = m->layers[layer];
+  float *dst; int want;
+  switch (which) {
+    case DP_W_IN_NORM: dst = L.in_norm; want = m->cfg.hidden; break;
+    case DP_W_POST_NORM: dst = L.post_norm; want = m->cfg.hidden; break;
+    case DP_W_Q_NORM: dst = L.q_norm; want = m->cfg.head_dim; break;
+    case DP_W_K_NORM: dst = L.k_norm; want = m->cfg.head_dim; break;
+    default: return dp_fail(ctx, DP_ERR_INVALID, "loadNorm: weight id %d is not a norm", (int)which);
+  }
+  DP_CHECK(ctx, n == want, "loadNorm: expected %d values, got %d", want, n);
+  return dp_buf_upload(ctx, m->norms, host, (size_t)((char *)dst - (char *)m->norms->dptr), (size_t)n * 4);
+}
+
+extern "C" dp_status dp_model_load_final_norm(dp_model *m, const float *host, int n) {
+  if (!m || !host) return DP_ERR_INVALID;
+  DP_CHECK(m->ctx, n == m->cfg.hidden, "loadFinalNorm: expected %d values, got %d", m->cfg.hidden, n);
+  return dp_buf_upload(m->ctx, m->norms, host, (size_t)((char *)m->final_norm - (char *)m->norms->dptr), (size_t)n * 4);
+}
+
+extern "C" dp_status dp_model_load_embed(dp_model *m, const void *host, int row0, int rows) {
+  if (!m || !host) return DP_ERR_INVALID;
+  DP_CHECK(m->ctx, row0 >= 0 && rows >= 0 && row0 + rows <= m->cfg.vocab, "loadEmbed: rows [%d,%d) outside the vocabulary", row0, row0 + rows);
+  return dp_buf_upload(m->ctx, m->embed, host, (size_t)row0 * m->cfg.hidden * 2, (size_t)rows * m->cfg.hidden * 2);
+}
+
+// rows are GLOBAL vocabulary rows; only the part that falls in this rank's shard is kept
+extern "C" dp_status dp_model_load_lm_head(dp_model *m, const void *host, int row0, int rows) {
+  if (!m || !host) return DP_ERR_INVALID;
+  DP_CHECK(m->ctx, row0 >= 0 && rows >= 0 && row0 + rows <= m->cfg.vocab, "loadLmHead: rows [%d,%d) outside the vocabulary", row0, row0 + rows);
+  int lo = row0 > m->vocab0 ? row0 : m->vocab0;
+  int hi = row0 + rows < m->vocab0 + m->vocab_l ? row0 + rows : m->vocab0 + m->vocab_l;
+  if (hi <= lo) return DP_OK;
+  const size_t rb = (size_t)m->cfg.hidden * 2;
+  return dp_buf_upload(m->ctx, m->lm_head, (const char *)host + (size_t)(lo - row0) * rb, (size_t)(lo - m->vocab0) * rb, (size_t)(hi - lo) * rb);
+}
+
+extern "C" dp_status dp_model_reset(dp_model *m) {
+  if (!m) return DP_ERR_INVALID;
+  for (int &s : m->seq_len) s = 0;
+  return DP_OK;
+}
+
+extern "C" size_t dp_model_weight_bytes(dp_model *m) { return m ? m->weight_bytes : 0; }
+extern "C" int dp_model_seq_len(dp_model *m, int seq) { return (m && seq >= 0 && seq < (int)m->seq_len.size()) ? m->seq_len[seq] : -1; }
+extern "C" double dp_model_last_decode_ms(dp_model *m) { return m ? m->last_ms : 0.0; }
+
+extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
+  if (!m) return DP_ERR_INVALID;
+  if (mode != 0) return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode %d is not available", mode);
+  m->allreduce_mode = mode;
+  return DP_OK;
+}
+
+// ---- the schedule ---------------------------------------------------------------------
+static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float *y, int M, int N, int K,
+                            const float *residual) {
+  dp_ctx *ctx = m->ctx;
+  if (M == 1) {
+    bool handled = false;
+    DP_TRY(dpk_gemv_q4k_fast(ctx, W, x, y, DP_F32, N, K, 1.0f, residual, &handled));
+    if (!handled) DP_TRY(dpk_gemv_q4k(ctx, W, x, y, DP_F32, N, K, 1.0f, residual));
+    return DP_OK;
+  }
+  bool handled = false;
+  DP_TRY(dpk_gemm_q4k_tc(ctx, W, x, DP_F32, y, DP_F32, M, N, K, 1.0f, &handled));
+  if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, y, DP_F32, M, N, K, 1.0f));
+  if (residual) DP_TRY(dpk_residual_add(ctx, y, residual, y, (size_t)M * N, 1.0f));
+  return DP_OK;
+}
+
+// One pass over `tokens` rows already gathered in m->h.  decode: rows are
+// sequences (positions from the device arrays); prefill: rows are consecutive
+// positions of sequence `seq` starting at start_pos.
+static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  const int H = c.hidden, D = c.head_dim, p = c.tp_size;
+  const size_t kv_seq_stride = (size_t)c.max_seq * m->kvdim;
+  const int heads = m->nh + 2 * m->nkv;
+  for (int l = 0; l < c.n_layers; l++) {
+    LayerW &L = m->layers[l];
+    DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr));
+    {
+      const int warps = tokens * heads;
+      DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
+                (__half *)m->vc[l]->dptr, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin, decode ? m->d_pos : nullptr,
+                start_pos, seq, tokens, m->nh, m->nkv, D, c.eps, kv_seq_stride);
+    }
+    dpk_attn_params ap{};
+    ap.q = m->q; ap.out = m->att;
+    ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
+    ap.scale = 1.0f / sqrtf((float)D); ap.softcap = 0.0f; ap.sliding_window = 0; ap.kv_start = 0;
+    int splits;
+    if (decode) {
+      ap.k = (const __half *)m->kc[l]->dptr; ap.v = (const __half *)m->vc[l]->dptr;
+      ap.batch = tokens; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.causal = 0; ap.start_pos = 0;
+      ap.kv_batch_stride = kv_seq_stride; ap.kv_lens = m->d_kvlen;
+      splits = m->attn_splits_decode;
+    } else {
+      ap.k = (const __half *)m->kc[l]->dptr + (size_t)seq * kv_seq_stride;
+      ap.v = (const __half *)m->vc[l]->dptr + (size_t)seq * kv_seq_stride;
+      ap.batch = 1; ap.seq_len = tokens; ap.kv_len = start_pos + tokens; ap.causal = 1; ap.start_pos = start_pos;
+      ap.kv_batch_stride = 0; ap.kv_lens = nullptr;
+      splits = 1;
+    }
+    DP_TRY(dpk_attention_with_scratch(ctx, ap, (float *)m->attn_scratch->dptr, splits));
+    if (p == 1) {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->h, tokens, H, m->qdim, m->h));
+    } else {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, tokens, H, m->qdim, nullptr));
+      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+    }
+    DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr));
+    {
+      const size_t total = (size_t)tokens * m->inter;
+      size_t grid = (total + 255) / 256;
+      if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
+      DP_LAUNCH(ctx, silu_gateup_kernel, (unsigned)grid, 256, 0, m->gu, m->actv, tokens, m->inter);
+    }
+    if (p == 1) {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->h, tokens, H, m->inter, m->h));
+    } else {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, tokens, H, m->inter, nullptr));
+      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+    }
+  }
+  return DP_OK;
+}
+
+// final norm + LM head + greedy argmax for `rows` rows of hidden state starting at hrow
+static dp_status run_head(dp_model *m, const float *hrow, int rows) {
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  DP_TRY(dpk_rmsnorm(ctx, hrow, m->final_norm, false, nullptr, false, nullptr, m->n, rows, c.hidden, c.eps, false, 1.0f));
+  DP_TRY(dpk_gemv_f16w(ctx, (const __half *)m->lm_head->dptr, m->n, DP_F32, m->logits, DP_F32, rows, m->vocab_l, c.hidden, 1.0f));
+  for (int b = 0; b < rows; b++)
+    DP_TRY(dpk_argmax(ctx, m->logits + (size_t)b * m->vocab_l, m->vocab_l, -1, m->d_tok, b, m->am_vals + (size_t)b * 256,
+                      m->am_idx + (size_t)b * 256, m->vocab0, m->am_best + b));
+  if (c.tp_size > 1) {
+    float *pairs = (float *)m->am_pair_i;
+    DP_LAUNCH(ctx, pack_pair_kernel, 1, 256, 0, m->am_best, m->d_tok, pairs, rows);
+    DP_TRY(dp_tp_allgather_ptr(ctx, pairs, m->am_gather, (size_t)rows * 8));
+    DP_LAUNCH(ctx, argmax_merge_kernel, 1, 256, 0, m->am_gather, c.tp_size, rows, m->d_tok);
+  }
+  return DP_OK;
+}
+
+extern "C" dp_status dp_model_prefill(dp_model *m, int seq, const int32_t *tokens, int n, int32_t *next_token) {
+  if (!m) return DP_ERR_INVALID;
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  DP_CHECK(ctx, seq >= 0 && seq < c.max_batch, "prefill: sequence %d outside [0,%d)", seq, c.max_batch);
+  DP_CHECK(ctx, tokens && n > 0, "prefill: empty prompt");
+  DP_CHECK(ctx, m->seq_len[seq] + n <= c.max_seq, "prefill: %d + %d tokens exceed max_seq %d", m->seq_len[seq], n, c.max_seq);
+  for (int i = 0; i < n; i++) DP_CHECK(ctx, tokens[i] >= 0 && tokens[i] < c.vocab, "prefill: token id %d outside the vocabulary", tokens[i]);
+  dp_buf ids = nullptr;
+  DP_TRY(dp_buf_acquire(ctx, (size_t)m->T * 4, "prefill_token_ids", &ids));
+  dp_status st = DP_OK;
+  for (int off = 0; off < n && st == DP_OK; off += m->T) {
+    const int cnt = n - off < m->T ? n - off : m->T;
+    st = dp_buf_upload(ctx, ids, tokens + off, 0, (size_t)cnt * 4);
+    if (st == DP_OK) st = dpk_gather_f16(ctx, (const int *)ids->dptr, (const __half *)m->embed->dptr, m->h, cnt, c.hidden);
+    if (st == DP_OK) st = run_layers(m, cnt, false, seq, m->seq_len[seq]);
+    if (st == DP_OK) {
+      m->seq_len[seq] += cnt;
+      if (off + cnt >= n) st = run_head(m, m->h + (size_t)(cnt - 1) * c.hidden, 1);
+    }
+  }
+  dp_buf_release(ctx, ids);
+  DP_TRY(st);
+  int tok = 0;
+  DP_CUDA(ctx, cudaMemcpyAsync(&tok, m->d_tok, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (next_token) *next_token = tok;
+  return DP_OK;
+}
+
+static dp_status record_decode_step(dp_model *m, int batch) {
+  dp_ctx *ctx = m->ctx;
+  DP_TRY(dpk_gather_f16(ctx, m->d_tok, (const __half *)m->embed->dptr, m->h, batch, m->cfg.hidden));
+  DP_TRY(run_layers(m, batch, true, 0, 0));
+  DP_TRY(run_head(m, m->h, batch));
+  DP_LAUNCH(ctx, advance_kernel, 1, 256, 0, m->d_pos, m->d_kvlen, m->d_tok, m->d_step, (int *)m->out_tokens->dptr, batch);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *first_tokens, int steps, int32_t *out_tokens) {
+  if (!m) return DP_ERR_INVALID;
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  DP_CHECK(ctx, batch > 0 && batch <= c.max_batch, "decode: batch %d outside [1,%d]", batch, c.max_batch);
+  DP_CHECK(ctx, first_tokens && out_tokens && steps > 0, "decode: null tokens or no steps");
+  for (int b = 0; b < batch; b++) {
+    DP_CHECK(ctx, first_tokens[b] >= 0 && first_tokens[b] < c.vocab, "decode: token id %d outside the vocabulary", first_tokens[b]);
+    DP_CHECK(ctx, m->seq_len[b] + steps <= c.max_seq, "decode: sequence %d would exceed max_seq %d", b, c.max_seq);
+  }
+  if (m->out_tokens_cap < steps * batch) {
+    if (m->out_tokens) { dp_buf_release(ctx, m->out_tokens); m->out_tokens = nullptr; }
+    for (int i = 0; i < 2; i++) if (m->graph[i]) { dp_graph_destroy(m->graph[i]); m->graph[i] = nullptr; }
+    DP_TRY(dp_buf_acquire(ctx, (size_t)steps * batch * 4, "decode_out_tokens", &m->out_tokens));
+    m->out_tokens_cap = steps * batch;
+  }
+  std::vector<int> st(1024, 0);
+  for (int b = 0; b < batch; b++) { st[b] = m->seq_len[b]; st[256 + b] = m->seq_len[b] + 1; st[512 + b] = first_tokens[b]; }
+  DP_TRY(dp_buf_upload(ctx, m->state, st.data(), 0, 4096));
+  const int slot = 0;
+  if (!m->graph[slot] || m->graph_batch[slot] != batch) {
+    if (m->graph[slot]) { dp_graph_destroy(m->graph[slot]); m->graph[slot] = nullptr; }
+    dp_recorder *rec = nullptr;
+    DP_TRY(dp_recorder_begin(ctx, "decode_step", 1, &rec));
+    dp_status s = record_decode_step(m, batch);
+    if (s != DP_OK) { std::string keep = ctx->err; dp_recorder_abort(rec); ctx->err = keep; return s; }
+    DP_TRY(dp_recorder_finish_graph(rec, &m->graph[slot]));
+    m->graph_batch[slot] = batch;
+  }
+  DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
+  for (int s = 0; s < steps; s++) DP_TRY(dp_graph_launch(m->graph[slot]));
+  DP_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+  DP_CUDA(ctx, cudaMemcpyAsync(out_tokens, m->out_tokens->dptr, (size_t)steps * batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  float ms = 0;
+  DP_CUDA(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+  m->last_ms = ms;
+  for (int b = 0; b < batch; b++) m->seq_len[b] += steps;
+  return DP_OK;
+}
+
+extern "C" dp_status dp_model_read_logits(dp_model *m, float *host, int n) {
+  if (!m || !host) return DP_ERR_INVALID;
+  DP_CHECK(m->ctx, n > 0 && n <= m->cfg.max_batch * m->vocab_l, "readLogits: %d values requested, %d available", n, m->cfg.max_batch * m->vocab_l);
+  DP_CUDA(m->ctx, cudaMemcpyAsync(host, m->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+  DP_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  return DP_OK;
+}
+
+extern "C" dp_status dp_model_read_hidden(dp_model *m, float *host, int n) {
+  if (!m || !host) return DP_ERR_INVALID;
+  DP_CHECK(m->ctx, n > 0 && (size_t)n <= (size_t)m->T * m->cfg.hidden, "readHidden: %d values requested", n);
+  DP_CUDA(m->ctx, cudaMemcpyAsync(host, m->h, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+  DP_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  return DP_OK;
+}
+
+extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total, uint64_t *launches, uint64_t *bytes) {
+  if (!m || !ms_total || !launches || !bytes) return DP_ERR_INVALID;
+  dp_ctx *ctx = m->ctx;
+  const dp_model_cfg &c = m->cfg;
+  DP_CHECK(ctx, reps > 0, "bench_gemv: reps must be positive");
+  const int H = c.hidden;
+  struct Shape { int N, K; };
+  const Shape sh[4] = {{m->qdim + 2 * m->kvdim, H}, {H, m->qdim}, {2 * m->inter, H}, {H, m->inter}};
+  uint64_t n_launch = 0, n_bytes = 0;
+  const uint64_t l0 = ctx->launches;
+  DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
+  for (int r = 0; r < reps; r++)
+    for (int l = 0; l < c.n_layers; l++) {
+      LayerW &L = m->layers[l];
+      const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,
+                             (const uint8_t *)L.down->dptr};
+      const float *X[4] = {m->n, m->att, m->n, m->actv};
+      float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
+      for (int i = 0; i < 4; i++) {
+        DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr));
+        n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
+      }
+    }
+  DP_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+  DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  float ms = 0;
+  DP_CUDA(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+  n_launch = ctx->launches - l0;
+  *ms_total = ms; *launches = n_launch; *bytes = n_bytes;
+  return DP_OK;
+}

@@ -1,0 +1,132 @@
+// Tensor-parallel group: NCCL (loaded at run time) for allreduce / allgather on
+// the context's stream.  One process per GPU; the 128-byte NCCL unique id is
+// created on rank 0 and handed to every rank by the host program.
+//
+// The reference has no collective backend (src/config/schema/emulation.schema.js
+// :108-143 only names TP degrees for an external simulator); this is the
+// data-path exchange of the column/row-parallel split: one sum over ranks after
+// o_proj and one after down_proj.
+#include "common.h"
+
+#include <dlfcn.h>
+
+#include <cstring>
+
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0 };
+enum { ncclInt8 = 0, ncclChar = 0, ncclFloat32 = 7 };
+enum { ncclSum = 0 };
+
+struct NcclApi {
+  void *handle = nullptr;
+  int (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*CommAbort)(ncclComm_t) = nullptr;
+  int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  const char *(*GetErrorString)(int) = nullptr;
+};
+
+static NcclApi g_nccl;
+
+static bool load_nccl(std::string *why) {
+  if (g_nccl.handle) return true;
+  const char *names[] = {"libnccl.so.2", "libnccl.so"};
+  void *h = nullptr;
+  for (const char *n : names) {
+    h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (h) break;
+  }
+  if (!h) { *why = std::string("cannot load libnccl: ") + dlerror(); return false; }
+  NcclApi a;
+  a.handle = h;
+#define SYM(field, name) *(void **)(&a.field) = dlsym(h, name); if (!a.field) { *why = std::string("libnccl lacks ") + name; return false; }
+  SYM(GetUniqueId, "ncclGetUniqueId");
+  SYM(CommInitRank, "ncclCommInitRank");
+  SYM(CommDestroy, "ncclCommDestroy");
+  SYM(CommAbort, "ncclCommAbort");
+  SYM(AllReduce, "ncclAllReduce");
+  SYM(AllGather, "ncclAllGather");
+  SYM(GetErrorString, "ncclGetErrorString");
+#undef SYM
+  g_nccl = a;
+  return true;
+}
+
+struct dp_tp_state {
+  int rank = 0, size = 1;
+  ncclComm_t comm = nullptr;
+};
+
+bool dp_tp_ready(dp_ctx *ctx) { return ctx && ctx->tp && ctx->tp->comm; }
+
+extern "C" dp_status dp_tp_unique_id(void *out128) {
+  if (!out128) return DP_ERR_INVALID;
+  std::string why;
+  if (!load_nccl(&why)) return DP_ERR_COMM;
+  ncclUniqueId id;
+  if (g_nccl.GetUniqueId(&id) != ncclSuccess) return DP_ERR_COMM;
+  memcpy(out128, &id, 128);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_tp_init(dp_ctx *ctx, int rank, int size, const void *id128) {
+  if (!ctx || !id128) return DP_ERR_INVALID;
+  DP_CHECK(ctx, size >= 1 && rank >= 0 && rank < size, "tp_init: rank %d outside [0,%d)", rank, size);
+  if (ctx->tp) return dp_fail(ctx, DP_ERR_STATE, "tp_init: the context already has a group");
+  std::string why;
+  if (!load_nccl(&why)) return dp_fail(ctx, DP_ERR_COMM, "tp_init: %s", why.c_str());
+  ncclUniqueId id;
+  memcpy(&id, id128, 128);
+  DP_CUDA(ctx, cudaSetDevice(ctx->device));
+  dp_tp_state *tp = new dp_tp_state();
+  tp->rank = rank; tp->size = size;
+  int rc = g_nccl.CommInitRank(&tp->comm, size, id, rank);
+  if (rc != ncclSuccess) {
+    delete tp;
+    return dp_fail(ctx, DP_ERR_COMM, "tp_init: ncclCommInitRank failed: %s", g_nccl.GetErrorString(rc));
+  }
+  ctx->tp = tp;
+  return DP_OK;
+}
+
+extern "C" dp_status dp_tp_destroy(dp_ctx *ctx) {
+  if (!ctx || !ctx->tp) return DP_OK;
+  if (ctx->tp->comm) g_nccl.CommDestroy(ctx->tp->comm);
+  delete ctx->tp;
+  ctx->tp = nullptr;
+  return DP_OK;
+}
+
+dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count) {
+  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "allreduce: no tensor-parallel group on this context");
+  int rc = g_nccl.AllReduce(ptr, ptr, count, ncclFloat32, ncclSum, ctx->tp->comm, ctx->stream);
+  if (rc != ncclSuccess) return dp_fail(ctx, DP_ERR_COMM, "ncclAllReduce failed: %s", g_nccl.GetErrorString(rc));
+  return DP_OK;
+}
+
+dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank) {
+  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "allgather: no tensor-parallel group on this context");
+  int rc = g_nccl.AllGather(send, recv, bytes_per_rank, ncclChar, ctx->tp->comm, ctx->stream);
+  if (rc != ncclSuccess) return dp_fail(ctx, DP_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+  return DP_OK;
+}
+
+extern "C" dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf buf, size_t offset, size_t count) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  DP_CHECK(ctx, buf && buf->active, "allreduce: null or released buffer");
+  DP_CHECK(ctx, offset % 4 == 0 && offset + count * 4 <= buf->capacity, "allreduce: range exceeds the buffer");
+  DP_TRY(dp_tp_allreduce_ptr(ctx, (float *)((char *)buf->dptr + offset), count));
+  dp_note_op(ctx, rec);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *) {
+  return dp_fail(ctx, DP_ERR_UNSUPPORTED, "peer-memory exchange area is not built into this library yet");
+}
+
+extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *) {
+  return dp_fail(ctx, DP_ERR_UNSUPPORTED, "peer-memory exchange area is not built into this library yet");
+}

@@ -1,0 +1,112 @@
+"""Decode / prefill attention over the f16 KV cache, through the C ABI, against attentionRef."""
+import numpy as np
+import pytest
+
+from doppler_b200 import ops, synthetic
+from oracle import oracle as O
+from parity import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _attn(dev, q, k16, v16, H, D, **opt):
+    qt, kt, vt = dev.tensor_from(q.astype(np.float32)), dev.tensor_from(k16), dev.tensor_from(v16)
+    out = ops.run_attention(qt, kt, vt, None, H, D, **opt)
+    res = dev.read_tensor(out)
+    for t in (out, qt, kt, vt):
+        dev.release_buffer(t.buffer)
+    return res
+
+
+def test_reference_suite_case(dev):  # tests/kernels/browser/kernel-suite.js:717-733
+    Q, K, V = O.lcg_test_data(32, 901), O.lcg_test_data(32, 902), O.lcg_test_data(32, 903)
+    k16, v16 = K.astype(np.float16), V.astype(np.float16)
+    got = _attn(dev, Q, k16, v16, 2, 8, seq_len=2, kv_len=4, num_kv_heads=1, causal=False)
+    exp = O.attention(Q, k16.astype(np.float32), v16.astype(np.float32), 2, 4, 2, 1, 8)
+    assert got.shape == (2, 2, 8)
+    assert np.all(np.abs(got.ravel() - exp) <= 1e-5 + 1e-4 * np.abs(exp))  # KERNEL_TOLERANCES.attention
+    # causal with startPos=2: first query sees keys 0..2, second 0..3
+    got = _attn(dev, Q, k16, v16, 2, 8, seq_len=2, kv_len=4, num_kv_heads=1, causal=True, start_pos=2)
+    exp = O.attention_f16kv(Q, k16, v16, 2, 4, 2, 1, 8, causal=True, start_pos=2)
+    assert np.all(np.abs(got.ravel() - exp) <= 1e-5 + 1e-4 * np.abs(exp))
+
+
+@pytest.mark.parametrize("H,Hkv,D,kv", [(32, 8, 128, 8192), (16, 8, 128, 700), (32, 8, 128, 1), (8, 8, 128, 257),
+                                        (16, 2, 128, 4096), (8, 2, 64, 1000), (6, 3, 32, 333), (4, 4, 256, 129)])
+def test_decode_shapes(dev, H, Hkv, D, kv):
+    s = synthetic.key(51, H * 1000 + kv)
+    q = synthetic.normal_f32(s, H * D)
+    k16 = synthetic.normal_f16(s + 1, kv * Hkv * D)
+    v16 = synthetic.normal_f16(s + 2, kv * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, start_pos=kv - 1)
+    exp = O.attention_f16kv(q, k16, v16, 1, kv, H, Hkv, D, causal=True, start_pos=kv - 1)
+    assert_close(got, exp, f"decode attention H{H}/Hkv{Hkv}/D{D}/kv{kv}")
+
+
+def test_config2_batch(dev):
+    """BASELINE config 2: batch 32, 32 heads, 8 KV heads, D 128, context 8192 (extension: batch dim)."""
+    B, H, Hkv, D, kv = 32, 32, 8, 128, 8192
+    s = synthetic.key(synthetic.DEFAULT_SEED, 20)
+    q = synthetic.normal_f16(s, B * H * D).astype(np.float32)
+    k16 = synthetic.normal_f16(s + 1, B * kv * Hkv * D)
+    v16 = synthetic.normal_f16(s + 2, B * kv * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False, batch=B,
+                kv_batch_stride=kv * Hkv * D)
+    assert got.shape == (B, 1, H, D)
+    got = got.reshape(B, H * D)
+    n = kv * Hkv * D
+    for b in (0, 13, 31):
+        exp = O.attention_f16kv(q[b * H * D:(b + 1) * H * D], k16[b * n:(b + 1) * n], v16[b * n:(b + 1) * n], 1, kv, H, Hkv, D,
+                                causal=False)
+        assert_close(got[b], exp, f"config2 sequence {b}")
+    # size-independent property: attention output is a convex combination of V rows
+    vmax = np.abs(v16.astype(np.float32)).max()
+    assert np.abs(got).max() <= vmax
+
+
+def test_kv_len_zero_and_kv_len_buffer(dev):
+    H, Hkv, D, kv = 8, 2, 128, 512
+    s = synthetic.key(52, 0)
+    q, k16, v16 = synthetic.normal_f32(s, H * D), synthetic.normal_f16(s + 1, kv * Hkv * D), synthetic.normal_f16(s + 2, kv * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=0, num_kv_heads=Hkv, causal=False)
+    assert np.all(got == 0)  # attention_decode_online_f16kv.wgsl:107-115
+    lens = dev.tensor_from(np.array([300], np.int32))
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False, kv_len_buffer=lens.buffer)
+    exp = O.attention_f16kv(q, k16, v16, 1, 300, H, Hkv, D, causal=False)
+    assert_close(got, exp, "kvLenBuffer overrides kvLen")
+    dev.release_buffer(lens.buffer)
+
+
+def test_sliding_window_and_kv_start(dev):
+    H, Hkv, D, kv, win = 8, 4, 128, 600, 128
+    s = synthetic.key(53, 0)
+    q, k16, v16 = synthetic.normal_f32(s, H * D), synthetic.normal_f16(s + 1, kv * Hkv * D), synthetic.normal_f16(s + 2, kv * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, start_pos=kv - 1, sliding_window=win)
+    n = Hkv * D
+    exp = O.attention_f16kv(q, k16[(kv - win) * n:], v16[(kv - win) * n:], 1, win, H, Hkv, D, causal=False)
+    assert_close(got, exp, "sliding window keeps the last `win` keys")
+
+
+def test_prefill_causal(dev):
+    H, Hkv, D, T = 16, 8, 128, 96
+    s = synthetic.key(54, 0)
+    q = synthetic.normal_f32(s, T * H * D)
+    k16, v16 = synthetic.normal_f16(s + 1, (T + 32) * Hkv * D), synthetic.normal_f16(s + 2, (T + 32) * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=T, kv_len=T + 32, num_kv_heads=Hkv, causal=True, start_pos=32)
+    exp = O.attention_f16kv(q, k16, v16, T, T + 32, H, Hkv, D, causal=True, start_pos=32)
+    assert_close(got, exp, "prefill attention, causal with startPos")
+
+
+def test_attention_argument_errors(dev):
+    q = dev.tensor_from(np.zeros(8 * 128, np.float32))
+    kv = dev.tensor_from(np.zeros(16 * 2 * 128, np.float16))
+    with pytest.raises(ops.DopplerError):
+        ops.run_attention(q, kv, kv, None, 8, 128, kv_len=17, num_kv_heads=2)  # cache too small
+    with pytest.raises(ops.DopplerError):
+        ops.run_attention(q, kv, kv, None, 8, 128, kv_len=16, num_kv_heads=3)  # heads not divisible
+    with pytest.raises(ops.DopplerError):
+        ops.run_attention(q, kv, kv, None, 8, 128, kv_len=16, num_kv_heads=2, kv_layout="paged")
+    with pytest.raises(ops.DopplerError):
+        ops.run_attention(kv, kv, kv, None, 8, 128, kv_len=16, num_kv_heads=2)  # Q must be f32
+    dev.release_buffer(q.buffer)
+    dev.release_buffer(kv.buffer)

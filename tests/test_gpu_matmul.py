@@ -1,0 +1,160 @@
+"""Q4_K fused dequant+matmul (decode GEMV, prefill GEMM) and the f16-weight GEMV, through
+the C ABI, against the double-accumulate oracle."""
+import numpy as np
+import pytest
+
+from doppler_b200 import ops, synthetic
+from oracle import oracle as O
+from parity import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f32", wdtype="q4k", **opt):
+    wb = dev.weight_from(W, wdtype, [N, K])
+    a = np.ascontiguousarray(A, np.float32 if a_dtype == "f32" else np.float16).reshape(M, K)
+    at = dev.tensor_from(a)
+    ct = ops.run_matmul(at, wb, M, N, K, output_dtype=out_dtype, **opt)
+    assert ct.shape == [M, N] and ct.dtype == out_dtype
+    out = dev.read_tensor(ct)
+    for b in (ct.buffer, at.buffer, wb.buffer):
+        dev.release_buffer(b)
+    return out
+
+
+def test_config0_gemv(dev):
+    """BASELINE config 0: x f32[1,1024] ~N(0,1), W [3072,1024] synthetic blocks."""
+    N, K = 3072, 1024
+    W = synthetic.q4k_matrix(synthetic.key(synthetic.DEFAULT_SEED, 1), N, K)
+    x = synthetic.normal_f32(synthetic.key(synthetic.DEFAULT_SEED, 2), K)
+    got = _matmul(dev, W, N, K, x, 1)
+    assert_close(got, O.q4k_gemv(W, N, K, x), "config0 gemv [1,1024]x[3072,1024]")
+    again = _matmul(dev, W, N, K, x, 1)
+    assert np.array_equal(got.view(np.uint32), again.view(np.uint32)), "GEMV is not run-to-run deterministic"
+
+
+@pytest.mark.parametrize("N,K", [(12288, 4096), (4096, 12288), (6144, 4096), (4096, 4096)])
+def test_9b_shape_gemv(dev, N, K):
+    W = synthetic.q4k_matrix(synthetic.key(21, N * 7 + K), N, K)
+    x = synthetic.normal_f32(synthetic.key(22, K), K)
+    got = _matmul(dev, W, N, K, x, 1)
+    assert_close(got, O.q4k_gemv(W, N, K, x), f"gemv [{N},{K}]")
+
+
+def test_gemv_linearity_and_alpha(dev):
+    N, K = 12288, 4096
+    W = synthetic.q4k_matrix(synthetic.key(23, 0), N, K)
+    x1, x2 = synthetic.normal_f32(synthetic.key(23, 1), K), synthetic.normal_f32(synthetic.key(23, 2), K)
+    y1, y2, y12 = _matmul(dev, W, N, K, x1, 1), _matmul(dev, W, N, K, x2, 1), _matmul(dev, W, N, K, x1 + x2, 1)
+    assert_close(y12, y1.astype(np.float64) + y2, "gemv linearity")
+    ya = _matmul(dev, W, N, K, x1, 1, alpha=0.25)
+    assert_close(ya, 0.25 * y1.astype(np.float64), "gemv alpha")
+
+
+@pytest.mark.parametrize("N,K", [(5, 300), (3, 192), (33, 384), (1, 256), (257, 512), (100, 2560)])
+def test_gemv_ragged_shapes(dev, N, K):  # K tails padded inside the last block of each row
+    w = O.lcg_test_data(N * K, 77 + N, -0.5, 0.5)
+    W = O.q4k_quantize_rowwise(w, N, K)
+    x = O.lcg_test_data(K, 78)
+    assert_close(_matmul(dev, W, N, K, x, 1), O.q4k_gemv(W, N, K, x), f"gemv ragged [{N},{K}]")
+
+
+def test_gemv_f16_output_and_f16_activation(dev):
+    N, K = 512, 1024
+    w = O.lcg_test_data(N * K, 5, -0.05, 0.05)
+    W = O.q4k_quantize_rowwise(w, N, K)
+    x = O.lcg_test_data(K, 6)
+    exp = O.q4k_gemv(W, N, K, x)
+    got16 = _matmul(dev, W, N, K, x, 1, out_dtype="f16")
+    assert np.abs(got16.astype(np.float64) - exp).max() <= np.abs(exp).max() * 2**-10
+    x16 = x.astype(np.float16)
+    got = _matmul(dev, W, N, K, x16, 1, a_dtype="f16")
+    assert_close(got, O.q4k_gemv(W, N, K, x16.astype(np.float32)), "gemv f16 activations")
+
+
+def test_reference_suite_matmul_q4k(dev):  # tests/kernels/browser/kernel-suite.js:218-232
+    M, N, K = 2, 4, 256
+    A = O.lcg_test_data(M * K, 2101, -0.5, 0.5)
+    B = O.lcg_test_data(N * K, 2102, -0.5, 0.5)
+    W = O.q4k_quantize_flat(B)
+    got = _matmul(dev, W, N, K, A, M, exact_weights=True)
+    exp = O.q4k_gemm(W, N, K, A, M)
+    assert np.all(np.abs(got - exp) <= 1e-2 + 1e-2 * np.abs(exp))  # the reference's own tolerance
+    assert_close(got, exp, "kernel-suite matmul_q4k")
+
+
+def test_reference_widetile_parity_case(dev):
+    """tests/kernels/fused-matmul-q4-widetile-f16a-parity.test.js: M=4,K=1536,N=6144, LCG seed 7,
+    f16 activations, f16 output, max_abs_diff < 1.0 and no NaN/Inf."""
+    M, K, N = 4, 1536, 6144
+    r = O.prng1664525(M * K + N * K, 7)
+    a32 = ((r[:M * K] - 0.5) * 1.0).astype(np.float32)
+    w32 = ((r[M * K:] - 0.5) * 0.1).astype(np.float32)
+    a16 = np.array([O.f32_to_f16_kvhost(float(v)) for v in a32], np.uint16).view(np.float16)
+    W = O.q4k_quantize_rowwise(w32, N, K)
+    exp = O.q4k_gemm(W, N, K, a16.astype(np.float32), M)
+    got = _matmul(dev, W, N, K, a16, M, out_dtype="f16", a_dtype="f16")
+    assert np.all(np.isfinite(got)) and np.abs(got.astype(np.float64) - exp).max() < 1.0
+    got32 = _matmul(dev, W, N, K, a16, M, out_dtype="f32", a_dtype="f16", exact_weights=True)
+    assert_close(got32, exp, "widetile parity case, f32 out")
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 64, 256), (7, 130, 300), (64, 256, 1024), (65, 96, 512)])
+def test_gemm_exact_weight_path(dev, M, N, K):
+    w = O.lcg_test_data(N * K, 11 + M, -0.5, 0.5)
+    W = O.q4k_quantize_rowwise(w, N, K)
+    A = O.lcg_test_data(M * K, 12 + M)
+    got = _matmul(dev, W, N, K, A, M, exact_weights=True)
+    assert_close(got, O.q4k_gemm(W, N, K, A, M), f"gemm exact [{M},{K}]x[{N},{K}]")
+
+
+def test_config1_gemm(dev):
+    """BASELINE config 1: A f16[512,4096] ~N(0,1), W [12288,4096], f32 accumulate, f16 out.
+    Gate: f16 output within one f16 ulp of the oracle's rounding plus the f32 gate."""
+    M, N, K = 512, 12288, 4096
+    W = synthetic.q4k_matrix(synthetic.key(synthetic.DEFAULT_SEED, 10), N, K)
+    A = synthetic.normal_f16(synthetic.key(synthetic.DEFAULT_SEED, 11), M * K)
+    exp = O.q4k_gemm(W, N, K, A.astype(np.float32), M)
+    got32 = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
+    assert_close(got32, exp, "config1 gemm f32 out", rtol=2e-3)
+    got16 = _matmul(dev, W, N, K, A, M, out_dtype="f16", a_dtype="f16")
+    assert np.all(np.isfinite(got16.astype(np.float32)))
+    assert_close(got16.astype(np.float32), exp, "config1 gemm f16 out", rtol=2e-3)
+
+
+def test_f16_weight_gemv_lm_head_shape(dev):
+    N, K = 8192, 1024
+    W = synthetic.normal_f16(synthetic.key(31, 0), N * K, 0.02)
+    x = synthetic.normal_f32(synthetic.key(31, 1), K)
+    got = _matmul(dev, W, N, K, x, 1, wdtype="f16")
+    assert_close(got, O.f16_gemv(W, N, K, x), "f16-weight gemv")
+    A = synthetic.normal_f32(synthetic.key(31, 2), 5 * K).reshape(5, K)
+    gotm = _matmul(dev, W, N, K, A, 5, wdtype="f16")
+    for m in range(5):
+        assert_close(gotm[m], O.f16_gemv(W, N, K, A[m]), f"f16-weight gemv row {m}")
+
+
+def test_matmul_argument_errors(dev):
+    N, K = 8, 256
+    W = synthetic.q4k_matrix(synthetic.key(41, 0), N, K)
+    wb = dev.weight_from(W, "q4k", [N, K])
+    at = dev.tensor_from(np.zeros((1, K), np.float32))
+    with pytest.raises(ops.DopplerError, match="outputDtype"):
+        ops.run_matmul(at, wb, 1, N, K)
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 1, N + 1, K, output_dtype="f32")  # weight shape mismatch
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 1, N, K, output_dtype="f32", a_offset=128)  # misaligned offset
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 2, N, K, output_dtype="f32")  # A too small for M=2
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 1, N, K, output_dtype="f32", transpose_b=False)
+    small = dev.acquire_buffer(16, "small")
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 1, N, K, output_dtype="f32", output_buffer=small)
+    stats0 = dev.pool_stats()
+    with pytest.raises(ops.DopplerError):
+        ops.run_matmul(at, wb, 0, N, K, output_dtype="f32")
+    assert dev.pool_stats()["bytes_in_use"] == stats0["bytes_in_use"]  # nothing leaked on the error path
+    for b in (small, at.buffer, wb.buffer):
+        dev.release_buffer(b)
