@@ -137,9 +137,9 @@ extern "C" dp_status dp_buf_release(dp_ctx *ctx, dp_buf buf) {
 static dp_status check_range(dp_ctx *ctx, dp_buf buf, size_t offset, size_t bytes, const char *what) {
   if (!ctx || !buf) return DP_ERR_INVALID;
   if (!buf->active) return dp_fail(ctx, DP_ERR_STATE, "%s: buffer '%s' was released", what, buf->label.c_str());
-  if (offset > buf->capacity || bytes > buf->capacity - offset)
+  if (offset > buf->bytes || bytes > buf->bytes - offset)
     return dp_fail(ctx, DP_ERR_INVALID, "%s: range [%zu, %zu) exceeds buffer '%s' of %zu bytes", what, offset,
-                   offset + bytes, buf->label.c_str(), buf->capacity);
+                   offset + bytes, buf->label.c_str(), buf->bytes);
   return DP_OK;
 }
 
@@ -198,9 +198,9 @@ dp_status dp_out_buffer(dp_ctx *ctx, dp_buf out_buf, size_t offset, size_t bytes
   if (out_buf) {
     if (!out_buf->active) return dp_fail(ctx, DP_ERR_STATE, "%s: outputBuffer was released", label);
     if (offset % DP_BUFFER_ALIGN) return dp_fail(ctx, DP_ERR_INVALID, "%s: output offset %zu is not 256-byte aligned", label, offset);
-    if (offset > out_buf->capacity || bytes > out_buf->capacity - offset)
+    if (offset > out_buf->bytes || bytes > out_buf->bytes - offset)
       return dp_fail(ctx, DP_ERR_INVALID, "%s: outputBuffer too small: need %zu bytes at offset %zu, have %zu", label,
-                     bytes, offset, out_buf->capacity);
+                     bytes, offset, out_buf->bytes);
     *result = out_buf;
     return DP_OK;
   }

@@ -85,6 +85,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
   const __half *kbase = p.k + (size_t)b * p.kv_batch_stride + (size_t)kvh * D + sub * DPL;
   const __half *vbase = p.v + (size_t)b * p.kv_batch_stride + (size_t)kvh * D + sub * DPL;
 
+  // The four 8-lane groups of a warp may run different trip counts, so the shuffles inside
+  // the loop name only the lanes of their own group.
+  const unsigned gmask = 0xFFu << (lane & 24);
 #pragma unroll 2
   for (int key = k_begin + grp; key < k_end; key += ATT_GROUPS) {
     uint4 kraw[DPL / 8], vraw[DPL / 8];
@@ -106,9 +109,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
       float a = 0.0f;
 #pragma unroll
       for (int i = 0; i < DPL; i++) a = fmaf(q[g][i], kf[i], a);
-      a += __shfl_xor_sync(0xffffffffu, a, 1);
-      a += __shfl_xor_sync(0xffffffffu, a, 2);
-      a += __shfl_xor_sync(0xffffffffu, a, 4);
+      a += __shfl_xor_sync(gmask, a, 1);
+      a += __shfl_xor_sync(gmask, a, 2);
+      a += __shfl_xor_sync(gmask, a, 4);
       if (p.softcap > 0.0f) a = tanhf(a / p.softcap) * p.softcap;
       s[g] = a * LOG2E;
     }

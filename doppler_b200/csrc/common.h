@@ -38,6 +38,7 @@ struct dp_ctx {
   // lazily grown scratch for split-K attention partials (stream ordered)
   dp_buf attn_scratch = nullptr;
   dp_buf argmax_scratch = nullptr;
+  dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
   dp_recorder *active_recorder = nullptr;
   dp_tp_state *tp = nullptr;
 };
@@ -118,7 +119,7 @@ static inline char *dp_tptr(const dp_tensor *t) {
   return (t && t->buf) ? (char *)t->buf->dptr + t->offset : nullptr;
 }
 static inline size_t dp_tavail(const dp_tensor *t) {
-  return (t && t->buf && t->offset <= t->buf->capacity) ? t->buf->capacity - t->offset : 0;
+  return (t && t->buf && t->offset <= t->buf->bytes) ? t->buf->bytes - t->offset : 0;
 }
 
 // output helper: use out_buf when given (checked for size), else acquire from the pool

@@ -24,6 +24,11 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
                           int M, int N, int K, float alpha, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
                             float alpha, const float *residual, bool *handled);
+dp_status dpk_q4k_prep_act(dp_ctx *ctx, const float *x, void *actq, int K);
+dp_status dpk_gemv_q4k_actq(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
+                            float alpha, const float *residual);
+size_t dpk_q4k_actq_bytes(int K);
+bool dpk_gemv_q4k_fast_ok(int N, int K);
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
 dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 bool dp_tp_ready(dp_ctx *ctx);
@@ -52,6 +57,7 @@ struct dp_model {
   dp_buf out_tokens = nullptr;
   int out_tokens_cap = 0;
   dp_buf attn_scratch = nullptr;
+  dp_buf actq = nullptr;  // fixed-point activation digits of the decode GEMV (sized for the largest K)
   int attn_splits_decode = 1;
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
@@ -215,6 +221,11 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   ap.batch = B; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
   size_t sbytes = dpk_attention_scratch_bytes(ctx, ap, &m->attn_splits_decode);
   acquire(sbytes ? sbytes : 256, "attention_split_partials", &m->attn_scratch);
+  {
+    int kmax = H > m->qdim ? H : m->qdim;
+    if (m->inter > kmax) kmax = m->inter;
+    acquire(dpk_q4k_actq_bytes(kmax), "gemv_activation_digits", &m->actq);
+  }
   if (st != DP_OK) { dp_model_destroy(m); return st; }
   m->weight_bytes += m->lm_head->bytes;
 
@@ -244,7 +255,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   }
   if (st == DP_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
     st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaEventCreate failed");
-  if (st == DP_OK) st = dp_buf_fill(ctx, m->state, 0, 0, m->state->capacity);
+  if (st == DP_OK) st = dp_buf_fill(ctx, m->state, 0, 0, m->state->bytes);
   if (st != DP_OK) { dp_model_destroy(m); return st; }
   *out = m;
   return DP_OK;
@@ -257,7 +268,7 @@ extern "C" void dp_model_destroy(dp_model *m) {
   for (int i = 0; i < 2; i++) if (m->graph[i]) dp_graph_destroy(m->graph[i]);
   auto rel = [&](dp_buf b) { if (b) dp_buf_release(ctx, b); };
   for (LayerW &L : m->layers) { rel(L.qkv); rel(L.o); rel(L.gateup); rel(L.down); }
-  rel(m->norms); rel(m->embed); rel(m->lm_head); rel(m->rope); rel(m->act); rel(m->state); rel(m->out_tokens); rel(m->attn_scratch);
+  rel(m->norms); rel(m->embed); rel(m->lm_head); rel(m->rope); rel(m->act); rel(m->state); rel(m->out_tokens); rel(m->attn_scratch); rel(m->actq);
   for (dp_buf b : m->kc) rel(b);
   for (dp_buf b : m->vc) rel(b);
   if (m->ev0) cudaEventDestroy(m->ev0);
@@ -371,15 +382,20 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
                             const float *residual) {
   dp_ctx *ctx = m->ctx;
   if (M == 1) {
-    bool handled = false;
-    DP_TRY(dpk_gemv_q4k_fast(ctx, W, x, y, DP_F32, N, K, 1.0f, residual, &handled));
-    if (!handled) DP_TRY(dpk_gemv_q4k(ctx, W, x, y, DP_F32, N, K, 1.0f, residual));
+    if (dpk_gemv_q4k_fast_ok(N, K)) {
+      DP_TRY(dpk_q4k_prep_act(ctx, x, m->actq->dptr, K));
+      DP_TRY(dpk_gemv_q4k_actq(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual));
+    } else {
+      DP_TRY(dpk_gemv_q4k(ctx, W, x, y, DP_F32, N, K, 1.0f, residual));
+    }
     return DP_OK;
   }
+  // the GEMM may not alias its output with the residual: go through the partial buffer
+  float *dst = (residual && residual == y) ? m->partial : y;
   bool handled = false;
-  DP_TRY(dpk_gemm_q4k_tc(ctx, W, x, DP_F32, y, DP_F32, M, N, K, 1.0f, &handled));
-  if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, y, DP_F32, M, N, K, 1.0f));
-  if (residual) DP_TRY(dpk_residual_add(ctx, y, residual, y, (size_t)M * N, 1.0f));
+  DP_TRY(dpk_gemm_q4k_tc(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f, &handled));
+  if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
+  if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
 }
 

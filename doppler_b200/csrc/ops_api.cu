@@ -42,7 +42,7 @@ static dp_status check_tensor(dp_ctx *ctx, const dp_tensor *t, const char *op, c
   if (t->offset % DP_BUFFER_ALIGN) return dp_fail(ctx, DP_ERR_INVALID, "%s: %s offset %zu is not 256-byte aligned", op, name, t->offset);
   if (dp_tavail(t) < need_bytes)
     return dp_fail(ctx, DP_ERR_INVALID, "%s: %s too small: need %zu bytes at offset %zu, buffer has %zu", op, name,
-                   need_bytes, t->offset, t->buf->capacity);
+                   need_bytes, t->offset, t->buf->bytes);
   return DP_OK;
 }
 
@@ -192,7 +192,7 @@ extern "C" dp_status dp_attention(dp_ctx *ctx, dp_recorder *rec, const dp_tensor
   const size_t kv_need = ((size_t)(o.batch - 1) * o.kv_batch_stride + (size_t)o.kv_len * kv_row) * 2;
   DP_TRY(check_tensor(ctx, K, "attention", "K", kv_need));
   DP_TRY(check_tensor(ctx, V, "attention", "V", kv_need));
-  if (o.kv_lens) DP_CHECK(ctx, o.kv_lens->active && o.kv_lens->capacity >= (size_t)o.batch * 4, "attention: kvLenBuffer too small");
+  if (o.kv_lens) DP_CHECK(ctx, o.kv_lens->active && o.kv_lens->bytes >= (size_t)o.batch * 4, "attention: kvLenBuffer too small");
   dp_buf obuf = nullptr;
   DP_TRY(dp_out_buffer(ctx, o.out_buf, 0, q_elems * 4, "attention_output", &obuf));
   dpk_attn_params p;
@@ -237,7 +237,7 @@ extern "C" dp_status dp_rmsnorm(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *
   DP_TRY(check_tensor(ctx, weight, "rmsnorm", "weight", (size_t)o.hidden_size * dp_dtype_size(weight->dtype)));
   if (o.residual) DP_TRY(check_tensor(ctx, o.residual, "rmsnorm", "residual", n * 4));
   DP_CHECK(ctx, !o.pre_residual || o.residual, "rmsnorm: preResidual needs a residual tensor");
-  if (o.residual_sum_output) DP_CHECK(ctx, o.residual_sum_output->active && o.residual_sum_output->capacity >= n * 4,
+  if (o.residual_sum_output) DP_CHECK(ctx, o.residual_sum_output->active && o.residual_sum_output->bytes >= n * 4,
                                        "rmsnorm: residualSumOutput too small");
   dp_buf obuf = nullptr;
   DP_TRY(dp_out_buffer(ctx, o.out_buf, 0, n * 4, "rmsnorm_output", &obuf));
@@ -367,8 +367,8 @@ extern "C" dp_status dp_kv_write_f32_to_f16(dp_ctx *ctx, dp_recorder *rec, const
   DP_CHECK(ctx, src && src->dtype == DP_F32, "kv_cache_write: source must be f32");
   DP_CHECK(ctx, dst && dst->active, "kv_cache_write: destination buffer is null or released");
   DP_TRY(check_tensor(ctx, src, "kv_cache_write", "source", n * 4));
-  DP_CHECK(ctx, (dst_offset_elems + n) * 2 <= dst->capacity, "kv_cache_write: %zu elements at offset %zu exceed the cache buffer (%zu bytes)",
-           n, dst_offset_elems, dst->capacity);
+  DP_CHECK(ctx, (dst_offset_elems + n) * 2 <= dst->bytes, "kv_cache_write: %zu elements at offset %zu exceed the cache buffer (%zu bytes)",
+           n, dst_offset_elems, dst->bytes);
   DP_TRY(dpk_kv_write(ctx, (const float *)dp_tptr(src), (__half *)dst->dptr + dst_offset_elems, n));
   dp_note_op(ctx, rec);
   return DP_OK;
@@ -380,7 +380,7 @@ extern "C" dp_status dp_argmax(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *l
   DP_CHECK(ctx, n > 0, "argmax: invalid vocab size %d", n);
   DP_CHECK(ctx, logits && logits->dtype == DP_F32, "argmax: logits must be f32");
   DP_TRY(check_tensor(ctx, logits, "argmax", "logits", (size_t)n * 4));
-  DP_CHECK(ctx, out_tokens && out_tokens->active && output_index >= 0 && (size_t)(output_index + 1) * 4 <= out_tokens->capacity,
+  DP_CHECK(ctx, out_tokens && out_tokens->active && output_index >= 0 && (size_t)(output_index + 1) * 4 <= out_tokens->bytes,
            "argmax: output token buffer too small for index %d", output_index);
   DP_TRY(dp_scratch(ctx, &ctx->argmax_scratch, 256 * 8, "argmax_partials"));
   float *vals = (float *)ctx->argmax_scratch->dptr;

@@ -117,7 +117,7 @@ dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t 
 extern "C" dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf buf, size_t offset, size_t count) {
   DP_TRY(dp_check_rec(ctx, rec));
   DP_CHECK(ctx, buf && buf->active, "allreduce: null or released buffer");
-  DP_CHECK(ctx, offset % 4 == 0 && offset + count * 4 <= buf->capacity, "allreduce: range exceeds the buffer");
+  DP_CHECK(ctx, offset % 4 == 0 && offset + count * 4 <= buf->bytes, "allreduce: range exceeds the buffer");
   DP_TRY(dp_tp_allreduce_ptr(ctx, (float *)((char *)buf->dptr + offset), count));
   dp_note_op(ctx, rec);
   return DP_OK;
