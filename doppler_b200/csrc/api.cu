@@ -38,6 +38,11 @@ extern "C" dp_status dp_ctx_create(int device, dp_ctx **out) {
     delete ctx;
     return DP_ERR_CUDA;
   }
+  if (cudaMalloc(&ctx->dev_status, 256) != cudaSuccess || cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) {
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return DP_ERR_CUDA;
+  }
   *out = ctx;
   return DP_OK;
 }
@@ -53,6 +58,7 @@ extern "C" void dp_ctx_destroy(dp_ctx *ctx) {
     if (b->dptr) cudaFree(b->dptr);
     delete b;
   }
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
 }
@@ -65,6 +71,12 @@ extern "C" uint64_t dp_ctx_launch_count(dp_ctx *ctx) { return ctx ? ctx->launche
 extern "C" dp_status dp_ctx_sync(dp_ctx *ctx) {
   if (!ctx) return DP_ERR_INVALID;
   DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int flag = 0;
+  DP_CUDA(ctx, cudaMemcpy(&flag, ctx->dev_status, 4, cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset(ctx->dev_status, 0, 4);
+    return dp_fail(ctx, DP_ERR_TIMEOUT, "a kernel gave up on a bounded device-side wait (status %d); its output is invalid", flag);
+  }
   return DP_OK;
 }
 

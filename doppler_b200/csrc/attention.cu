@@ -13,6 +13,7 @@
 // groups are merged at the end (warp shuffles, then shared memory).  Split
 // partials (m, l, o) go to a scratch buffer and a second kernel merges them.
 #include "common.h"
+#include "pdl.cuh"
 
 #include <cfloat>
 
@@ -43,6 +44,8 @@ __device__ __forceinline__ AttnRange attn_range(int kv_len, int causal, int star
 template <int DPL, int GT>
 __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params p, float *__restrict__ part, int splits,
                                                                   int head_tiles) {
+  pdl_launch();
+  pdl_wait();
   constexpr int D = DPL * 8;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane & 7;          // which D/8 slice of the key this lane owns
@@ -196,6 +199,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
 // Any head_dim <= 512 and any GQA ratio: one CTA per (split, query head, row),
 // lanes over dims.  Used for shapes outside the fast kernel.
 __global__ void __launch_bounds__(128) attn_split_generic_kernel(dpk_attn_params p, float *__restrict__ part, int splits) {
+  pdl_launch();
+  pdl_wait();
   const int D = p.head_dim;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int split = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
@@ -265,12 +270,15 @@ __global__ void __launch_bounds__(128) attn_split_generic_kernel(dpk_attn_params
 
 // merge the split partials of one (row, head)
 __global__ void attn_combine_kernel(const float *__restrict__ part, float *__restrict__ out, int D, int splits) {
+  pdl_launch();
+  pdl_wait();
   const size_t rh = blockIdx.x;
   const float *pp = part + rh * splits * (D + 2);
   float mm = -FLT_MAX;
   for (int s = 0; s < splits; s++) mm = fmaxf(mm, pp[s * (D + 2) + D]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float ll = 0.0f, acc = 0.0f;
+#pragma unroll 4
     for (int s = 0; s < splits; s++) {
       const float ms = pp[s * (D + 2) + D];
       const float c = (ms == -FLT_MAX) ? 0.0f : exp2f(ms - mm);
@@ -297,12 +305,12 @@ size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *s
   const long base_ctas = fast ? rows * p.num_kv_heads * (G / gt) : rows * p.num_heads;
   const long target = (long)ctx->sm_count * 4;
   long splits = (target + base_ctas - 1) / base_ctas;
-  const int keys_per_cta_min = fast ? 64 : 32;
+  const int keys_per_cta_min = fast ? 128 : 32;
   long max_splits = (p.kv_len + keys_per_cta_min - 1) / keys_per_cta_min;
   if (max_splits < 1) max_splits = 1;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
-  if (splits > 256) splits = 256;
+  if (splits > 32) splits = 32;
   *splits_out = (int)splits;
   if (splits == 1) return 0;
   return (size_t)rows * p.num_heads * splits * (p.head_dim + 2) * sizeof(float);

@@ -39,6 +39,8 @@ struct dp_ctx {
   dp_buf attn_scratch = nullptr;
   dp_buf argmax_scratch = nullptr;
   dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
+  bool pdl = false;  // launch with programmatic dependent launch (set while the decode step is recorded)
+  int *dev_status = nullptr;  // device word raised by a kernel whose bounded wait gave up
   dp_recorder *active_recorder = nullptr;
   dp_tp_state *tp = nullptr;
 };
@@ -82,12 +84,31 @@ dp_status dp_fail(dp_ctx *ctx, dp_status st, const char *fmt, ...);
   } while (0)
 
 // Every kernel launch of this library goes through here so launches are counted
-// and launch errors surface as a status.
+// and launch errors surface as a status.  With ctx->pdl the launch carries the
+// programmatic-stream-serialization attribute: the kernel may start while its
+// predecessor drains, and must execute pdl_wait() before it touches anything the
+// predecessor wrote (every kernel on the decode path does, see pdl.cuh).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dp_launch_impl(dp_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define DP_LAUNCH(ctx, kernel, grid, block, smem, ...)                                   \
   do {                                                                                   \
-    kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);                     \
+    cudaError_t _e = dp_launch_impl((ctx), kernel, dim3(grid), dim3(block), (smem), __VA_ARGS__); \
     (ctx)->launches++;                                                                   \
-    cudaError_t _e = cudaGetLastError();                                                 \
+    if (_e == cudaSuccess) _e = cudaGetLastError();                                      \
     if (_e != cudaSuccess)                                                               \
       return dp_fail((ctx), DP_ERR_CUDA, "launch of %s failed: %s", #kernel,             \
                      cudaGetErrorString(_e));                                            \

@@ -10,6 +10,7 @@
 // f32 as the reference CPU dequantizer produces (d*sc and dmin*m are exact in
 // f32, and so is (d*sc)*q).
 #include "common.h"
+#include "pdl.cuh"
 #include "q4k.cuh"
 
 template <typename OutT>
@@ -36,6 +37,8 @@ __device__ __forceinline__ void store4<__half>(__half *p, float a, float b, floa
 template <typename OutT>
 __global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint32_t *__restrict__ packed, OutT *__restrict__ out,
                                                           size_t total_blocks, uint32_t bpr, uint32_t K) {
+  pdl_launch();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const size_t warp0 = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const size_t nwarps = (size_t)gridDim.x * (blockDim.x >> 5);

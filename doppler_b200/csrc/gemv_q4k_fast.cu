@@ -25,6 +25,7 @@
 // it reads 8 bytes of each 32-byte quant chunk, so four threads cover a chunk and a
 // warp-wide load touches whole 32-byte sectors.
 #include "common.h"
+#include "pdl.cuh"
 #include "q4k.cuh"
 
 // ---- activation pre-pass -------------------------------------------------------
@@ -34,6 +35,8 @@
 //   ssum   f32  [K/32]          sum of the fixed-point integers of each sub-block
 __global__ void __launch_bounds__(256) q4k_prep_act_kernel(const float *__restrict__ x, int8_t *__restrict__ limbs,
                                                            float *__restrict__ xscale, float *__restrict__ ssum, int bpr) {
+  pdl_launch();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * (blockDim.x >> 5);
   for (int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < bpr; b += warps_total) {
@@ -94,6 +97,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_q4k_mma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int bpr, float alpha,
     const float *__restrict__ residual) {
+  pdl_launch();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
@@ -171,6 +176,9 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_q4k_mma_kernel(
   }
 }
 
+dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
+                                float alpha, const float *residual, bool *handled);
+
 static size_t actq_bytes(int K) { return (size_t)K * 4 + (size_t)(K / 256) * 4 + (size_t)(K / 32) * 4; }
 
 // quantise x (f32[K]) into `actq` (actq_bytes(K)); exposed to the runner so producers can be fused later
@@ -208,7 +216,291 @@ dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void 
   if (!dpk_gemv_q4k_fast_ok(N, K) || (y_dtype != DP_F32 && y_dtype != DP_F16)) return DP_OK;
   DP_TRY(dp_scratch(ctx, &ctx->gemv_scratch, actq_bytes(K), "gemv_activation_digits"));
   DP_TRY(dpk_q4k_prep_act(ctx, x, ctx->gemv_scratch->dptr, K));
-  DP_TRY(dpk_gemv_q4k_actq(ctx, W, ctx->gemv_scratch->dptr, y, y_dtype, N, K, alpha, residual));
+  bool tma = false;
+  DP_TRY(dpk_gemv_q4k_actq_tma(ctx, W, ctx->gemv_scratch->dptr, y, y_dtype, N, K, alpha, residual, &tma));
+  if (!tma) DP_TRY(dpk_gemv_q4k_actq(ctx, W, ctx->gemv_scratch->dptr, y, y_dtype, N, K, alpha, residual));
+  *handled = true;
+  return DP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Persistent, TMA-fed variant (needs ceil(K/256) to be a multiple of the chunk size).
+//
+// One CTA per SM loops over 16-row tiles.  A producer warp streams the packed weight
+// rows into a ring of shared-memory stages with untiled bulk copies (one contiguous
+// copy per row and chunk of up to eight super-blocks, completion counted on an
+// mbarrier), so many tens of KB per SM are in flight regardless of what the consumer
+// warps are doing.  The eight consumer warps each take one super-block column of the
+// chunk out of shared memory (rows are padded by 32 bytes so that the 8-byte reads of a
+// half-warp fall in distinct banks), run the integer MMAs as above and hand the stage
+// back through an "empty" mbarrier.  The activation digits live in shared memory for
+// the whole kernel.  Every wait is bounded: on give-up the CTA raises an abort flag, all
+// its threads leave their loops, and a status word tells the host (DP_ERR_TIMEOUT).
+// ---------------------------------------------------------------------------
+#include "mbar.cuh"
+
+#include <cstdlib>
+
+#define TG_CONSUMERS 8  // warps per consumer group (one per super-block column of a chunk)
+#define TG_ROW_PAD 32
+#define TG_RED_SLOTS 16
+
+struct TgLayout {
+  uint32_t digits, ssum, xscale, stages, bars, red, abort_flag, total;
+  uint32_t row_stride, stage_bytes;
+};
+
+__host__ __device__ inline TgLayout tg_layout(int K, int cb, int stages) {
+  TgLayout l;
+  const uint32_t bpr = (uint32_t)K / QK_K;
+  l.digits = 0;
+  l.xscale = (uint32_t)K * 4;  // same order as the global buffer: digits, block scales, sub-block sums
+  l.ssum = l.xscale + bpr * 4;
+  uint32_t off = l.ssum + (uint32_t)(K / 32) * 4;
+  off = (off + 127u) & ~127u;
+  l.row_stride = (uint32_t)cb * Q4K_BLOCK_BYTES + TG_ROW_PAD;
+  l.stage_bytes = 16u * l.row_stride;
+  l.stages = off;
+  off += (uint32_t)stages * l.stage_bytes;
+  l.bars = off;  // full[stages], empty[stages], red[TG_RED_SLOTS]
+  off += (2u * (uint32_t)stages + TG_RED_SLOTS) * 8u;
+  l.red = off;
+  off += TG_RED_SLOTS * TG_CONSUMERS * 16u * 4u;
+  l.abort_flag = off;
+  l.total = off + 16u;
+  return l;
+}
+
+// GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
+// while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
+template <typename OutT, int GROUPS>
+__global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
+    const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
+    const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
+    const float *__restrict__ residual, int *__restrict__ err) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const TgLayout L = tg_layout(K, cb, stages);
+  const int tid = threadIdx.x, lane = tid & 31, warp_all = tid >> 5;
+  const int group = warp_all / TG_CONSUMERS, warp = warp_all % TG_CONSUMERS;  // producer: group == GROUPS
+  const int bpr = K / QK_K, chunks = bpr / cb, tiles = N / 16;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
+  const uint32_t bars = smem_u32(smem + L.bars);
+  auto full_bar = [&](int s) { return bars + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (uint32_t)(stages + s); };
+  auto red_bar = [&](int s) { return bars + 8u * (uint32_t)(2 * stages + s); };
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), TG_CONSUMERS); }
+    for (int s = 0; s < TG_RED_SLOTS; s++) mbar_init(red_bar(s), TG_CONSUMERS);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  pdl_launch();
+  __syncthreads();
+  (void)xscale; (void)ssum;
+  const float *sm_ssum = reinterpret_cast<const float *>(smem + L.ssum);
+  const float *sm_xscale = reinterpret_cast<const float *>(smem + L.xscale);
+  // The producer starts streaming weights at once: they are written by no kernel of the step,
+  // so under programmatic dependent launch the ring fills while the previous kernel drains.
+  // The consumers first wait for the previous kernel (which produced the activation digits).
+  if (group < GROUPS) {
+    pdl_wait();
+    constexpr int CT = GROUPS * TG_CONSUMERS * 32;  // consumer threads
+    const uint4 *src = reinterpret_cast<const uint4 *>(limbs);
+    uint4 *dst = reinterpret_cast<uint4 *>(smem);
+    const int total = K * 4 + (K / 32) * 4 + bpr * 4;
+    const int n16 = total / 16;
+    for (int i = tid; i < n16; i += CT) dst[i] = __ldg(src + i);
+    const int rem_words = (total - n16 * 16) / 4;
+    if (tid < rem_words) reinterpret_cast<uint32_t *>(smem)[n16 * 4 + tid] = __ldg(reinterpret_cast<const uint32_t *>(limbs) + n16 * 4 + tid);
+    asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+  }
+
+  if (group == GROUPS) {
+    // ---------------- producer ----------------
+    uint32_t u = 0;
+    bool ok = true;
+    for (int rt = blockIdx.x; rt < tiles && ok; rt += gridDim.x) {
+      for (int ch = 0; ch < chunks && ok; ch++, u++) {
+        const int s = (int)(u % (uint32_t)stages);
+        const uint32_t n = u / (uint32_t)stages;
+        int good = 1;
+        if (lane == 0) {
+          if (n > 0) good = mbar_wait_bounded(empty_bar(s), (n - 1) & 1u, abort_flag) ? 1 : 0;
+          if (good) mbar_expect_tx(full_bar(s), 16u * (uint32_t)cb * Q4K_BLOCK_BYTES);
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { ok = false; break; }
+        if (lane < 16) {
+          const uint8_t *src = W + ((size_t)(rt * 16 + lane) * bpr + (size_t)ch * cb) * Q4K_BLOCK_BYTES;
+          bulk_g2s(smem_u32(smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)lane * L.row_stride), src,
+                   (uint32_t)cb * Q4K_BLOCK_BYTES, full_bar(s));
+        }
+      }
+    }
+    if (!ok && lane == 0) {  // gave up: let the copies already issued land before the CTA exits
+      const uint32_t first = u > (uint32_t)stages ? u - (uint32_t)stages : 0u;
+      for (uint32_t v = first; v < u; v++) {
+        const uint32_t bar = full_bar((int)(v % (uint32_t)stages)), par = (v / (uint32_t)stages) & 1u;
+        for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(bar, par); i++) {}
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, t = lane & 3;
+    const float w0 = t == 0 ? 1.0f : (t == 1 ? 65536.0f : 0.0f);
+    const float w1 = t == 0 ? 256.0f : 0.0f;
+    const uint32_t M4 = 0x0f0f0f0fu;
+    uint32_t tile_no = (uint32_t)group;
+    bool ok = true;
+    float *red = reinterpret_cast<float *>(smem + L.red);
+    for (int rt = blockIdx.x + group * gridDim.x; rt < tiles && ok; rt += GROUPS * gridDim.x, tile_no += GROUPS) {
+      float resA = 0.0f, resB = 0.0f;
+      uint32_t u = tile_no * (uint32_t)chunks;
+      for (int ch = 0; ch < chunks; ch++, u++) {
+        const int s = (int)(u % (uint32_t)stages);
+        const uint32_t n = u / (uint32_t)stages;
+        if (!mbar_wait_bounded(full_bar(s), n & 1u, abort_flag)) { ok = false; break; }
+        for (int bw = warp; bw < cb; bw += TG_CONSUMERS) {
+          const int b = ch * cb + bw;
+          const uint8_t *pa = smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)g * L.row_stride + (uint32_t)bw * Q4K_BLOCK_BYTES;
+          const uint8_t *pb = pa + 8u * L.row_stride;
+          const uint4 ha = *reinterpret_cast<const uint4 *>(pa);
+          const uint4 hb = *reinterpret_cast<const uint4 *>(pb);
+          uint2 qa[4], qb[4];
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            qa[c] = *reinterpret_cast<const uint2 *>(pa + 16 + 32 * c + 8 * t);
+            qb[c] = *reinterpret_cast<const uint2 *>(pb + 16 + 32 * c + 8 * t);
+          }
+          const Q4KScales sa = q4k_unpack_scales(ha.y, ha.z, ha.w);
+          const Q4KScales sb_ = q4k_unpack_scales(hb.y, hb.z, hb.w);
+          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 8 * 128) + g * 4 + t;
+          int accA0 = 0, accA1 = 0, accB0 = 0, accB1 = 0;
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+              const int sb = 2 * c + hi;
+              uint2 bf = make_uint2(0u, 0u);
+              if (g < 3) bf = lb[sb * 16];
+              const uint32_t a0 = hi ? (qa[c].x >> 4) & M4 : qa[c].x & M4;
+              const uint32_t a1 = hi ? (qb[c].x >> 4) & M4 : qb[c].x & M4;
+              const uint32_t a2 = hi ? (qa[c].y >> 4) & M4 : qa[c].y & M4;
+              const uint32_t a3 = hi ? (qb[c].y >> 4) & M4 : qb[c].y & M4;
+              int c0, c1, c2, c3;
+              mma_u8s8(c0, c1, c2, c3, a0, a1, a2, a3, bf.x, bf.y);
+              const int scA = (int)q4k_byte(sb < 4 ? sa.sc03 : sa.sc47, sb & 3);
+              const int scB = (int)q4k_byte(sb < 4 ? sb_.sc03 : sb_.sc47, sb & 3);
+              accA0 += scA * c0; accA1 += scA * c1;
+              accB0 += scB * c2; accB1 += scB * c3;
+            }
+          }
+          const float xs = sm_xscale[b];
+          const float2 dA = q4k_d_dmin(ha.x), dB = q4k_d_dmin(hb.x);
+          const float fa = fmaf((float)accA1, w1, (float)accA0 * w0);
+          const float fb = fmaf((float)accB1, w1, (float)accB0 * w0);
+          const float s0 = sm_ssum[b * 8 + 2 * t], s1 = sm_ssum[b * 8 + 2 * t + 1];
+          const uint32_t mwA = t < 2 ? sa.mn03 : sa.mn47, mwB = t < 2 ? sb_.mn03 : sb_.mn47;
+          const int sh = (t & 1) * 16;
+          const float mA = fmaf((float)((mwA >> (sh + 8)) & 0xffu), s1, (float)((mwA >> sh) & 0xffu) * s0);
+          const float mB = fmaf((float)((mwB >> (sh + 8)) & 0xffu), s1, (float)((mwB >> sh) & 0xffu) * s0);
+          resA = fmaf(xs, fmaf(dA.x, fa, -dA.y * mA), resA);
+          resB = fmaf(xs, fmaf(dB.x, fb, -dB.y * mB), resB);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+      }
+      if (!ok) break;
+      // sum the eight warps' partial rows through a ring of reduction slots
+      resA += __shfl_xor_sync(0xffffffffu, resA, 1);
+      resA += __shfl_xor_sync(0xffffffffu, resA, 2);
+      resB += __shfl_xor_sync(0xffffffffu, resB, 1);
+      resB += __shfl_xor_sync(0xffffffffu, resB, 2);
+      const int slot = (int)(tile_no % TG_RED_SLOTS);
+      float *rs = red + slot * TG_CONSUMERS * 16;
+      if (t == 0) { rs[warp * 16 + g] = resA; rs[warp * 16 + g + 8] = resB; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_bar(slot));
+      if (warp == 0) {
+        if (!mbar_wait_bounded(red_bar(slot), (tile_no / TG_RED_SLOTS) & 1u, abort_flag)) { ok = false; break; }
+        if (lane < 16) {
+          float v = 0.0f;
+#pragma unroll
+          for (int w = 0; w < TG_CONSUMERS; w++) v += rs[w * 16 + lane];
+          const int row = rt * 16 + lane;
+          v *= alpha;
+          if (residual) v += residual[row];
+          if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
+        }
+      }
+    }
+  }
+  if (*abort_flag && lane == 0) atomicExch(err, 1);
+}
+
+static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, uint32_t *smem_out) {
+  if (!dpk_gemv_q4k_fast_ok(N, K)) return false;
+  const int bpr = K / QK_K;
+  // chunk = the largest divisor of the row's block count whose stage (16 padded row pieces) stays
+  // under the limit: long per-row copies keep the number of bulk-copy requests per byte low
+  static int limit = -1;
+  if (limit < 0) { const char *e = getenv("DP_GEMV_STAGE_KB"); limit = (e ? atoi(e) : 56) * 1024; }
+  int cb = 0;
+  for (int c = bpr; c >= 1; c--)
+    if (bpr % c == 0 && 16 * (c * Q4K_BLOCK_BYTES + TG_ROW_PAD) <= limit) { cb = c; break; }
+  if (cb == 0) return false;
+  const size_t budget = ctx->smem_optin < 227 * 1024 ? ctx->smem_optin : 227 * 1024;
+  int stages = 8;
+  while (stages >= 2 && tg_layout(K, cb, stages).total > budget) stages--;
+  if (stages < 2) return false;
+  *cb_out = cb; *stages_out = stages; *smem_out = tg_layout(K, cb, stages).total;
+  return true;
+}
+
+template <typename OutT, int GROUPS>
+static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
+                            uint32_t smem, float alpha, const float *residual) {
+  const float *xscale = (const float *)(limbs + (size_t)K * 4);
+  const float *ssum = xscale + K / QK_K;
+  const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set = true;
+  }
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+            N, K, cb, stages, alpha, residual, ctx->dev_status);
+  return DP_OK;
+}
+
+// 0 = plain MMA kernel, 1 / 2 = TMA kernel with one / two consumer groups
+static int gemv_variant() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("DP_GEMV_VARIANT");
+    v = e ? atoi(e) : 2;
+    if (v < 0 || v > 3) v = 2;
+  }
+  return v;
+}
+
+dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
+                                float alpha, const float *residual, bool *handled) {
+  *handled = false;
+  int cb, stages;
+  uint32_t smem;
+  const int variant = gemv_variant();
+  if (variant == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
+  const int8_t *limbs = (const int8_t *)actq;
+  if (y_dtype == DP_F32) {
+    if (variant == 1) DP_TRY((launch_tma<float, 1>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
+    else if (variant == 3) DP_TRY((launch_tma<float, 3>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
+    else DP_TRY((launch_tma<float, 2>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
+  } else {
+    if (variant == 1) DP_TRY((launch_tma<__half, 1>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual)));
+    else DP_TRY((launch_tma<__half, 2>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual)));
+  }
   *handled = true;
   return DP_OK;
 }

@@ -4,6 +4,7 @@
 // Replaces src/gpu/kernels/fused_matmul_q4.wgsl (main_gemv :279, main_multicol
 // :122), fused_matmul_q4_batched*.wgsl (:122) and matmul_gemv_subgroup.wgsl.
 #include "common.h"
+#include "pdl.cuh"
 #include "q4k.cuh"
 
 // ---------------------------------------------------------------------------
@@ -36,6 +37,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(256) gemv_q4k_kernel(const uint8_t *__restrict__ W, const float *__restrict__ x,
                                                        OutT *__restrict__ y, int N, int K, int bpr, float alpha,
                                                        const float *__restrict__ residual) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ float smem[];
   float *xs = smem;                  // [bpr*256], zero beyond K
   float *xsum = smem + bpr * QK_K;   // [bpr*8] sum of x over each 32-element sub-block
@@ -122,6 +125,8 @@ template <typename AT, typename OutT>
 __global__ void __launch_bounds__(256) gemm_q4k_simt_kernel(const uint8_t *__restrict__ W, const AT *__restrict__ A,
                                                             OutT *__restrict__ C, int M, int N, int K, int bpr,
                                                             float alpha) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float As[32][64 + 4];  // [k][m]
   __shared__ float Ws[32][64 + 4];  // [k][n]
   const int tid = threadIdx.x;
@@ -228,6 +233,8 @@ dp_status dpk_gemm_q4k_simt(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dty
 template <typename AT, typename OutT, int MT>
 __global__ void __launch_bounds__(256) gemv_f16w_kernel(const __half *__restrict__ W, const AT *__restrict__ A,
                                                         OutT *__restrict__ C, int M, int m_base, int N, int K, float alpha) {
+  pdl_launch();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const bool vec_ok = (K % 8) == 0;
   for (int row = blockIdx.x * warps + (threadIdx.x >> 5); row < N; row += gridDim.x * warps) {
@@ -274,6 +281,40 @@ __global__ void __launch_bounds__(256) gemv_f16w_kernel(const __half *__restrict
   }
 }
 
+// M == 1, f32 activations: x is staged once per CTA in shared memory and the weight row is
+// streamed with four 16-byte loads in flight per lane.
+template <typename OutT>
+__global__ void __launch_bounds__(256) gemv_f16w_m1_kernel(const __half *__restrict__ W, const float *__restrict__ x,
+                                                           OutT *__restrict__ y, int N, int K, float alpha) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float xs[];
+  for (int i = threadIdx.x; i < K / 4; i += blockDim.x)
+    reinterpret_cast<float4 *>(xs)[i] = __ldg(reinterpret_cast<const float4 *>(x) + i);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int row = blockIdx.x * warps + (threadIdx.x >> 5); row < N; row += gridDim.x * warps) {
+    const uint4 *wr = reinterpret_cast<const uint4 *>(W + (size_t)row * K);
+    float acc = 0.0f;
+    const int n16 = K / 8;
+#pragma unroll 4
+    for (int c = lane; c < n16; c += 32) {
+      const uint4 wv = __ldg(wr + c);
+      const __half2 *h = reinterpret_cast<const __half2 *>(&wv);
+      const float4 x0 = *reinterpret_cast<const float4 *>(xs + 8 * c), x1 = *reinterpret_cast<const float4 *>(xs + 8 * c + 4);
+      const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+      acc = fmaf(f0.x, x0.x, acc); acc = fmaf(f0.y, x0.y, acc); acc = fmaf(f1.x, x0.z, acc); acc = fmaf(f1.y, x0.w, acc);
+      acc = fmaf(f2.x, x1.x, acc); acc = fmaf(f2.y, x1.y, acc); acc = fmaf(f3.x, x1.z, acc); acc = fmaf(f3.y, x1.w, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const float v = acc * alpha;
+      if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
+    }
+  }
+}
+
 template <typename AT, typename OutT>
 static dp_status launch_f16w(dp_ctx *ctx, const __half *W, const AT *A, OutT *C, int M, int N, int K, float alpha) {
   const int threads = 256, warps = 8;
@@ -292,6 +333,16 @@ static dp_status launch_f16w(dp_ctx *ctx, const __half *W, const AT *A, OutT *C,
 
 dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
                         int N, int K, float alpha) {
+  if (M == 1 && a_dtype == DP_F32 && K % 8 == 0 && (size_t)K * 4 <= 48 * 1024) {
+    int grid = (N + 7) / 8;
+    if (grid > ctx->sm_count * 8) grid = ctx->sm_count * 8;
+    if (c_dtype == DP_F32) {
+      DP_LAUNCH(ctx, gemv_f16w_m1_kernel<float>, grid, 256, (size_t)K * 4, W, (const float *)A, (float *)C, N, K, alpha);
+    } else {
+      DP_LAUNCH(ctx, gemv_f16w_m1_kernel<__half>, grid, 256, (size_t)K * 4, W, (const float *)A, (__half *)C, N, K, alpha);
+    }
+    return DP_OK;
+  }
   if (a_dtype == DP_F32 && c_dtype == DP_F32) return launch_f16w<float, float>(ctx, W, (const float *)A, (float *)C, M, N, K, alpha);
   if (a_dtype == DP_F32 && c_dtype == DP_F16) return launch_f16w<float, __half>(ctx, W, (const float *)A, (__half *)C, M, N, K, alpha);
   if (a_dtype == DP_F16 && c_dtype == DP_F32) return launch_f16w<__half, float>(ctx, W, (const __half *)A, (float *)C, M, N, K, alpha);
@@ -302,6 +353,8 @@ dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_
 // f32 weights: plain warp-per-row kernel (kept for API completeness)
 __global__ void __launch_bounds__(256) gemv_f32w_kernel(const float *__restrict__ W, const float *__restrict__ A,
                                                         float *__restrict__ C, int M, int N, int K, float alpha) {
+  pdl_launch();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const long total = (long)M * N;
   for (long o = (long)blockIdx.x * warps + (threadIdx.x >> 5); o < total; o += (long)gridDim.x * warps) {

@@ -14,6 +14,7 @@
 // rmsnorm -> gate/up -> silu(gate)*up -> down + residual; final rmsnorm -> f16 LM
 // head -> greedy argmax (lower index wins ties).
 #include "common.h"
+#include "pdl.cuh"
 #include "q4k.cuh"
 
 #include <cmath>
@@ -27,6 +28,8 @@ dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void 
 dp_status dpk_q4k_prep_act(dp_ctx *ctx, const float *x, void *actq, int K);
 dp_status dpk_gemv_q4k_actq(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
                             float alpha, const float *residual);
+dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
+                                float alpha, const float *residual, bool *handled);
 size_t dpk_q4k_actq_bytes(int K);
 bool dpk_gemv_q4k_fast_ok(int N, int K);
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
@@ -79,6 +82,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_kernel(
     const float *__restrict__ q_norm, const float *__restrict__ k_norm, const float *__restrict__ cos_t,
     const float *__restrict__ sin_t, const int *__restrict__ pos_arr, int start_pos, int seq, int tokens, int nh,
     int nkv, int D, float eps, size_t kv_seq_stride) {
+  pdl_launch();
+  pdl_wait();
   const int heads = nh + 2 * nkv;
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (gw >= tokens * heads) return;
@@ -124,6 +129,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_kernel(
 
 // out[t, :] = silu(gu[t, 0:I]) * gu[t, I:2I]   (silu.wgsl:30-37,98-104, sigmoid argument clamped to +-15)
 __global__ void silu_gateup_kernel(const float *__restrict__ gu, float *__restrict__ out, int tokens, int inter) {
+  pdl_launch();
+  pdl_wait();
   const size_t total = (size_t)tokens * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / inter, c = i % inter;
@@ -135,6 +142,8 @@ __global__ void silu_gateup_kernel(const float *__restrict__ gu, float *__restri
 
 // after a decode step: record the sampled tokens and move every sequence on by one
 __global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, int *out_tokens, int batch) {
+  pdl_launch();
+  pdl_wait();
   const int b = threadIdx.x;
   const int s = *step;
   if (b < batch) { out_tokens[s * batch + b] = tok[b]; pos[b] += 1; kvlen[b] += 1; }
@@ -145,6 +154,8 @@ __global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, 
 // combine the per-rank (best value, index) pairs of a vocabulary-sharded argmax;
 // ties go to the lower global index (sample.wgsl:45-53)
 __global__ void argmax_merge_kernel(const float *pairs, int ranks, int batch, int *tok) {
+  pdl_launch();
+  pdl_wait();
   const int b = threadIdx.x;
   if (b >= batch) return;
   float bv = -3.402823e+38f;
@@ -158,6 +169,8 @@ __global__ void argmax_merge_kernel(const float *pairs, int ranks, int batch, in
 }
 
 __global__ void pack_pair_kernel(const float *best, const int *tok, float *pairs, int batch) {
+  pdl_launch();
+  pdl_wait();
   const int b = threadIdx.x;
   if (b < batch) { pairs[2 * b] = best[b]; pairs[2 * b + 1] = __int_as_float(tok[b]); }
 }
@@ -384,7 +397,9 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   if (M == 1) {
     if (dpk_gemv_q4k_fast_ok(N, K)) {
       DP_TRY(dpk_q4k_prep_act(ctx, x, m->actq->dptr, K));
-      DP_TRY(dpk_gemv_q4k_actq(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual));
+      bool tma = false;
+      DP_TRY(dpk_gemv_q4k_actq_tma(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual, &tma));
+      if (!tma) DP_TRY(dpk_gemv_q4k_actq(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual));
     } else {
       DP_TRY(dpk_gemv_q4k(ctx, W, x, y, DP_F32, N, K, 1.0f, residual));
     }
@@ -543,7 +558,9 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
     if (m->graph[slot]) { dp_graph_destroy(m->graph[slot]); m->graph[slot] = nullptr; }
     dp_recorder *rec = nullptr;
     DP_TRY(dp_recorder_begin(ctx, "decode_step", 1, &rec));
+    ctx->pdl = true;  // kernels of the step overlap their launch with the predecessor's tail
     dp_status s = record_decode_step(m, batch);
+    ctx->pdl = false;
     if (s != DP_OK) { std::string keep = ctx->err; dp_recorder_abort(rec); ctx->err = keep; return s; }
     DP_TRY(dp_recorder_finish_graph(rec, &m->graph[slot]));
     m->graph_batch[slot] = batch;

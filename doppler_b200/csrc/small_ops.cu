@@ -1,6 +1,7 @@
 // The small memory-bound ops on the decode path.  Each kernel cites the WGSL it
 // replaces; arithmetic is f32 like the reference's.
 #include "common.h"
+#include "pdl.cuh"
 
 #include <cfloat>
 
@@ -23,6 +24,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
                                                       const float *__restrict__ residual, int pre_residual,
                                                       float *__restrict__ residual_sum_out, float *__restrict__ y,
                                                       int size, float eps, int weight_offset, float output_scale) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float sh[32];
   const size_t base = (size_t)blockIdx.x * size;
   float ss = 0.0f;
@@ -45,10 +48,72 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
   }
 }
 
+// Same op for rows of up to 4096 values (size % 4 == 0): the row is read once with 16-byte
+// loads, kept in registers across the reduction, and written with 16-byte stores.
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float *__restrict__ x, const void *__restrict__ w, int w_f16,
+                                                          const float *__restrict__ residual, int pre_residual,
+                                                          float *__restrict__ residual_sum_out, float *__restrict__ y,
+                                                          int size, float eps, int weight_offset, float output_scale) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sh[32];
+  const size_t base = (size_t)blockIdx.x * size;
+  const int n4 = size >> 2;
+  float4 v[4], r[4];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int idx = threadIdx.x + i * 256;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    r[i] = v[i];
+    if (idx < n4) {
+      v[i] = *reinterpret_cast<const float4 *>(x + base + 4 * idx);
+      if (residual) r[i] = *reinterpret_cast<const float4 *>(residual + base + 4 * idx);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    if (pre_residual) { v[i].x += r[i].x; v[i].y += r[i].y; v[i].z += r[i].z; v[i].w += r[i].w; }
+    ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+  }
+  const float total = block_sum(ss, sh);
+  const float inv_rms = 1.0f / sqrtf(total / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx >= n4) continue;
+    float wv[4];
+    if (w_f16) {
+      const __half2 *wp = reinterpret_cast<const __half2 *>((const __half *)w + 4 * idx);
+      const float2 a = __half22float2(wp[0]), b = __half22float2(wp[1]);
+      wv[0] = a.x; wv[1] = a.y; wv[2] = b.x; wv[3] = b.y;
+    } else {
+      const float4 t = *reinterpret_cast<const float4 *>((const float *)w + 4 * idx);
+      wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+    }
+    const float xv[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, rv[4] = {r[i].x, r[i].y, r[i].z, r[i].w};
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float ww = weight_offset ? 1.0f + wv[j] : wv[j];
+      float t = xv[j] * inv_rms * ww;
+      if (residual && !pre_residual) t += rv[j];
+      o[j] = t * output_scale;
+    }
+    if (pre_residual && residual_sum_out) *reinterpret_cast<float4 *>(residual_sum_out + base + 4 * idx) = v[i];
+    *reinterpret_cast<float4 *>(y + base + 4 * idx) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 dp_status dpk_rmsnorm(dp_ctx *ctx, const float *x, const void *w, bool w_f16, const float *residual, bool pre_residual,
                       float *residual_sum_out, float *y, int rows, int size, float eps, bool weight_offset,
                       float output_scale) {
   if (rows <= 0) return DP_OK;
+  if (size % 4 == 0 && size >= 1024 && size <= 4096) {
+    DP_LAUNCH(ctx, rmsnorm_vec_kernel, rows, 256, 0, x, w, w_f16 ? 1 : 0, residual, pre_residual ? 1 : 0, residual_sum_out,
+              y, size, eps, weight_offset ? 1 : 0, output_scale);
+    return DP_OK;
+  }
   int threads = size >= 1024 ? 256 : (size >= 256 ? 128 : 32);
   DP_LAUNCH(ctx, rmsnorm_kernel, rows, threads, 0, x, w, w_f16 ? 1 : 0, residual, pre_residual ? 1 : 0, residual_sum_out,
             y, size, eps, weight_offset ? 1 : 0, output_scale);
@@ -60,6 +125,8 @@ dp_status dpk_rmsnorm(dp_ctx *ctx, const float *x, const void *w, bool w_f16, co
 __global__ void __launch_bounds__(256) rmsnorm_qk_kernel(float *__restrict__ q, const float *__restrict__ qw,
                                                          float *__restrict__ k, const float *__restrict__ kw, int q_rows,
                                                          int k_rows, int head_dim, float eps, int weight_offset) {
+  pdl_launch();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= q_rows + k_rows) return;
   float *p = row < q_rows ? q + (size_t)row * head_dim : k + (size_t)(row - q_rows) * head_dim;
@@ -90,6 +157,8 @@ dp_status dpk_rmsnorm_qk(dp_ctx *ctx, float *q, const float *qw, float *k, const
 __global__ void rope_kernel(float *__restrict__ x, const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                             int seq_len, int num_heads, int head_dim, int rotary_dim, int pair_span, int interleaved,
                             int start_pos) {
+  pdl_launch();
+  pdl_wait();
   const int half = rotary_dim / 2;
   const long total = (long)seq_len * num_heads * half;
   for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
@@ -122,6 +191,8 @@ dp_status dpk_rope(dp_ctx *ctx, float *x, const float *cos_t, const float *sin_t
 // optional SwiGLU clamp.
 __global__ void silu_mul_kernel(const float *__restrict__ up, const float *__restrict__ gate, float *__restrict__ out,
                                 size_t n, float clamp_max) {
+  pdl_launch();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float g = gate[i];
     const float cl = fminf(fmaxf(g, -15.0f), 15.0f);
@@ -143,6 +214,8 @@ dp_status dpk_silu_mul(dp_ctx *ctx, const float *up, const float *gate, float *o
 // src/gpu/kernels/residual.wgsl:25-32
 __global__ void residual_add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
                                     size_t n, float scale) {
+  pdl_launch();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float s = a[i] + b[i];
     out[i] = scale == 1.0f ? s : s * scale;
@@ -160,6 +233,8 @@ dp_status dpk_residual_add(dp_ctx *ctx, const float *a, const float *b, float *o
 // src/gpu/kernels/gather_f16.wgsl:35-66: embedding rows f16 -> f32
 __global__ void gather_f16_kernel(const int *__restrict__ ids, const __half *__restrict__ table, float *__restrict__ out,
                                   int hidden) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const __half *row = table + (size_t)ids[t] * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = __half2float(row[i]);
@@ -173,6 +248,8 @@ dp_status dpk_gather_f16(dp_ctx *ctx, const int *ids, const __half *table, float
 
 // src/gpu/kernels/kv_cache_write_f32_to_f16.wgsl:19 (round to nearest even, like WGSL f16())
 __global__ void kv_write_kernel(const float *__restrict__ src, __half *__restrict__ dst, size_t n) {
+  pdl_launch();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     dst[i] = __float2half_rn(src[i]);
 }
@@ -195,6 +272,8 @@ __device__ __forceinline__ bool beats(float cv, int ci, float bv, int bi) {
 
 __global__ void __launch_bounds__(256) argmax_phase1(const float *__restrict__ logits, int n, int pad_id,
                                                      float *__restrict__ vals, int *__restrict__ idxs) {
+  pdl_launch();
+  pdl_wait();
   float best = -3.402823e+38f;
   int bi = 0;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -218,6 +297,8 @@ __global__ void __launch_bounds__(256) argmax_phase1(const float *__restrict__ l
 __global__ void __launch_bounds__(256) argmax_phase2(const float *__restrict__ vals, const int *__restrict__ idxs,
                                                      int groups, int *__restrict__ out, int out_index, int index_base,
                                                      float *__restrict__ best_val_out) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float sv[256];
   __shared__ int si[256];
   const int t = threadIdx.x;
