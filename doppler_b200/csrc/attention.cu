@@ -325,7 +325,18 @@ static dp_status launch_fast(dp_ctx *ctx, const dpk_attn_params &p, float *scrat
   return DP_OK;
 }
 
+static dp_status attention_impl(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits, bool combine);
+
 dp_status dpk_attention_with_scratch(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits) {
+  return attention_impl(ctx, p, scratch, splits, true);
+}
+
+// the split kernel alone (splits > 1): the caller merges the partials itself
+dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits) {
+  return attention_impl(ctx, p, scratch, splits, false);
+}
+
+static dp_status attention_impl(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits, bool combine) {
   int gt = 1;
   if (fast_shape(p, &gt)) {
     if (p.head_dim == 128) {
@@ -341,7 +352,7 @@ dp_status dpk_attention_with_scratch(dp_ctx *ctx, const dpk_attn_params &p, floa
     dim3 grid(splits, p.num_heads, p.batch * p.seq_len);
     DP_LAUNCH(ctx, attn_split_generic_kernel, grid, 128, 0, p, scratch, splits);
   }
-  if (splits > 1) {
+  if (splits > 1 && combine) {
     const unsigned rows = (unsigned)((long)p.batch * p.seq_len * p.num_heads);
     int threads = p.head_dim < 128 ? ((p.head_dim + 31) / 32) * 32 : 128;
     DP_LAUNCH(ctx, attn_combine_kernel, rows, threads, 0, scratch, p.out, p.head_dim, splits);

@@ -27,14 +27,14 @@
 #include "common.h"
 #include "pdl.cuh"
 #include "q4k.cuh"
+#include "actq.cuh"
 
 // ---- activation pre-pass -------------------------------------------------------
 // layout of the quantised activation buffer for K = 256*bpr:
 //   limbs  int8 [K/32][4][32]   column c = digit c (c = 3 is zero), bytes in element order
 //   xscale f32  [bpr]           2^(e_b - 22)
 //   ssum   f32  [K/32]          sum of the fixed-point integers of each sub-block
-__global__ void __launch_bounds__(256) q4k_prep_act_kernel(const float *__restrict__ x, int8_t *__restrict__ limbs,
-                                                           float *__restrict__ xscale, float *__restrict__ ssum, int bpr) {
+__global__ void __launch_bounds__(256) q4k_prep_act_kernel(const float *__restrict__ x, void *__restrict__ actq, int bpr) {
   pdl_launch();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -43,42 +43,7 @@ __global__ void __launch_bounds__(256) q4k_prep_act_kernel(const float *__restri
     const float4 v0 = *reinterpret_cast<const float4 *>(x + b * QK_K + lane * 8);
     const float4 v1 = *reinterpret_cast<const float4 *>(x + b * QK_K + lane * 8 + 4);
     const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    int e = 0;
-    if (amax > 0.0f) frexpf(amax, &e);  // amax < 2^e
-    if (e < -100) e = -100;
-    const float up = ldexpf(1.0f, 22 - e);
-    int q[8], s = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) { q[i] = __float2int_rn(v[i] * up); s += q[i]; }
-    uint32_t d[3][2] = {{0, 0}, {0, 0}, {0, 0}};
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      int r = q[i];
-      const int l0 = ((r + 128) & 255) - 128;
-      r = (r - l0) >> 8;
-      const int l1 = ((r + 128) & 255) - 128;
-      const int l2 = (r - l1) >> 8;
-      d[0][i >> 2] |= (uint32_t)(l0 & 255) << (8 * (i & 3));
-      d[1][i >> 2] |= (uint32_t)(l1 & 255) << (8 * (i & 3));
-      d[2][i >> 2] |= (uint32_t)(l2 & 255) << (8 * (i & 3));
-    }
-    const int sb = b * 8 + (lane >> 2);
-    uint2 *dst = reinterpret_cast<uint2 *>(limbs + (size_t)sb * 128) + (lane & 3);
-    dst[0] = make_uint2(d[0][0], d[0][1]);
-    dst[4] = make_uint2(d[1][0], d[1][1]);
-    dst[8] = make_uint2(d[2][0], d[2][1]);
-    dst[12] = make_uint2(0u, 0u);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    if ((lane & 3) == 0) ssum[sb] = (float)s;
-    float sc = ldexpf(1.0f, e - 22);
-    if (!(amax <= 3.0e38f)) sc = __int_as_float(0x7fc00000);  // inf / nan activations poison the block
-    if (lane == 0) xscale[b] = sc;
+    actq_emit_block(v, lane, b, bpr, actq);
   }
 }
 
@@ -184,11 +149,8 @@ static size_t actq_bytes(int K) { return (size_t)K * 4 + (size_t)(K / 256) * 4 +
 // quantise x (f32[K]) into `actq` (actq_bytes(K)); exposed to the runner so producers can be fused later
 dp_status dpk_q4k_prep_act(dp_ctx *ctx, const float *x, void *actq, int K) {
   const int bpr = K / QK_K;
-  int8_t *limbs = (int8_t *)actq;
-  float *xscale = (float *)(limbs + (size_t)K * 4);
-  float *ssum = xscale + bpr;
   const int grid = (bpr + 7) / 8;
-  DP_LAUNCH(ctx, q4k_prep_act_kernel, grid, 256, 0, x, limbs, xscale, ssum, bpr);
+  DP_LAUNCH(ctx, q4k_prep_act_kernel, grid, 256, 0, x, actq, bpr);
   return DP_OK;
 }
 

@@ -16,7 +16,9 @@
 #include "common.h"
 #include "pdl.cuh"
 #include "q4k.cuh"
+#include "actq.cuh"
 
+#include <cfloat>
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -32,6 +34,7 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
                                 float alpha, const float *residual, bool *handled);
 size_t dpk_q4k_actq_bytes(int K);
 bool dpk_gemv_q4k_fast_ok(int N, int K);
+dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
 dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 bool dp_tp_ready(dp_ctx *ctx);
@@ -173,6 +176,112 @@ __global__ void pack_pair_kernel(const float *best, const int *tok, float *pairs
   pdl_wait();
   const int b = threadIdx.x;
   if (b < batch) { pairs[2 * b] = best[b]; pairs[2 * b + 1] = __int_as_float(tok[b]); }
+}
+
+
+// ---- single-token producers that also emit the GEMV's fixed-point activation digits ----
+// (reference ops: rmsnorm.wgsl:119-187, silu.wgsl:98-104, and the split-K merge of the decode
+// attention; the digits feed gemv_q4k_fast.cu, so no separate quantisation launch is needed)
+
+// RMSNorm of one row of `size` values (size % 256 == 0, size <= 8192); warp w owns blocks w, w+8, ...
+__global__ void __launch_bounds__(256) rmsnorm_actq_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                           float *__restrict__ y, void *__restrict__ actq, int size, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sh[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, bpr = size / QK_K;
+  float v[4][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const float4 a = *reinterpret_cast<const float4 *>(x + b * QK_K + lane * 8);
+      const float4 c = *reinterpret_cast<const float4 *>(x + b * QK_K + lane * 8 + 4);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+#pragma unroll
+      for (int j = 0; j < 8; j++) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) sh[warp] = ss;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) total += sh[i];
+  const float inv_rms = 1.0f / sqrtf(total / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const float4 wa = *reinterpret_cast<const float4 *>(w + b * QK_K + lane * 8);
+      const float4 wc = *reinterpret_cast<const float4 *>(w + b * QK_K + lane * 8 + 4);
+      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) o[j] = v[i][j] * inv_rms * wv[j];
+      *reinterpret_cast<float4 *>(y + b * QK_K + lane * 8) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4 *>(y + b * QK_K + lane * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+      actq_emit_block(o, lane, b, bpr, actq);
+    }
+  }
+}
+
+// act = silu(gate) * up for one token, inter % 256 == 0; one warp per block
+__global__ void __launch_bounds__(256) silu_actq_kernel(const float *__restrict__ gu, float *__restrict__ out,
+                                                        void *__restrict__ actq, int inter) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, bpr = inter / QK_K;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= bpr) return;
+  const float *gp = gu + b * QK_K + lane * 8, *up = gu + inter + b * QK_K + lane * 8;
+  const float4 g0 = *reinterpret_cast<const float4 *>(gp), g1 = *reinterpret_cast<const float4 *>(gp + 4);
+  const float4 u0 = *reinterpret_cast<const float4 *>(up), u1 = *reinterpret_cast<const float4 *>(up + 4);
+  const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float cl = fminf(fmaxf(g[j], -15.0f), 15.0f);
+    o[j] = (g[j] * (1.0f / (1.0f + expf(-cl)))) * u[j];
+  }
+  *reinterpret_cast<float4 *>(out + b * QK_K + lane * 8) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4 *>(out + b * QK_K + lane * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  actq_emit_block(o, lane, b, bpr, actq);
+}
+
+// merge of the split-K attention partials of one token (layout of attention.cu: per (head, split)
+// D values, then running max and sum); (H*D) % 256 == 0 and D % 8 == 0; one warp per 256 outputs
+__global__ void __launch_bounds__(256) attn_combine_actq_kernel(const float *__restrict__ part, float *__restrict__ out,
+                                                                void *__restrict__ actq, int H, int D, int splits) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, bpr = H * D / QK_K;
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b >= bpr) return;
+  const int e0 = b * QK_K + lane * 8, h = e0 / D, d0 = e0 % D;
+  const float *pp = part + (size_t)h * splits * (D + 2);
+  float mm = -FLT_MAX;
+  for (int s = 0; s < splits; s++) mm = fmaxf(mm, pp[s * (D + 2) + D]);
+  float ll = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 2
+  for (int s = 0; s < splits; s++) {
+    const float *ps = pp + s * (D + 2);
+    const float ms = ps[D];
+    const float c = (ms == -FLT_MAX) ? 0.0f : exp2f(ms - mm);
+    ll = fmaf(ps[D + 1], c, ll);
+    const float2 a0 = *reinterpret_cast<const float2 *>(ps + d0), a1 = *reinterpret_cast<const float2 *>(ps + d0 + 2);
+    const float2 a2 = *reinterpret_cast<const float2 *>(ps + d0 + 4), a3 = *reinterpret_cast<const float2 *>(ps + d0 + 6);
+    acc[0] = fmaf(a0.x, c, acc[0]); acc[1] = fmaf(a0.y, c, acc[1]); acc[2] = fmaf(a1.x, c, acc[2]); acc[3] = fmaf(a1.y, c, acc[3]);
+    acc[4] = fmaf(a2.x, c, acc[4]); acc[5] = fmaf(a2.y, c, acc[5]); acc[6] = fmaf(a3.x, c, acc[6]); acc[7] = fmaf(a3.y, c, acc[7]);
+  }
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) o[j] = ll > 0.0f ? acc[j] / ll : 0.0f;
+  *reinterpret_cast<float4 *>(out + e0) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4 *>(out + e0 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  actq_emit_block(o, lane, b, bpr, actq);
 }
 
 // ---- create / destroy -----------------------------------------------------------
@@ -392,11 +501,11 @@ extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
 
 // ---- the schedule ---------------------------------------------------------------------
 static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float *y, int M, int N, int K,
-                            const float *residual) {
+                            const float *residual, bool digits_ready = false) {
   dp_ctx *ctx = m->ctx;
   if (M == 1) {
     if (dpk_gemv_q4k_fast_ok(N, K)) {
-      DP_TRY(dpk_q4k_prep_act(ctx, x, m->actq->dptr, K));
+      if (!digits_ready) DP_TRY(dpk_q4k_prep_act(ctx, x, m->actq->dptr, K));
       bool tma = false;
       DP_TRY(dpk_gemv_q4k_actq_tma(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual, &tma));
       if (!tma) DP_TRY(dpk_gemv_q4k_actq(ctx, W, m->actq->dptr, y, DP_F32, N, K, 1.0f, residual));
@@ -425,8 +534,18 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
   const int heads = m->nh + 2 * m->nkv;
   for (int l = 0; l < c.n_layers; l++) {
     LayerW &L = m->layers[l];
-    DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr));
+    // single-token decode: the producers of a GEMV's input also emit its fixed-point digits
+    const bool fuse = decode && tokens == 1 && H % QK_K == 0 && H <= 8192;
+    const bool fuse_qkv = fuse && dpk_gemv_q4k_fast_ok(m->qdim + 2 * m->kvdim, H);
+    const bool fuse_gu = fuse && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
+    const bool fuse_o = fuse && dpk_gemv_q4k_fast_ok(H, m->qdim) && m->attn_splits_decode > 1 && D % 8 == 0;
+    const bool fuse_down = fuse && dpk_gemv_q4k_fast_ok(H, m->inter);
+    if (fuse_qkv) {
+      DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.in_norm, m->n, m->actq->dptr, H, c.eps);
+    } else {
+      DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+    }
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr, fuse_qkv));
     {
       const int warps = tokens * heads;
       DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
@@ -450,26 +569,40 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       ap.kv_batch_stride = 0; ap.kv_lens = nullptr;
       splits = 1;
     }
-    DP_TRY(dpk_attention_with_scratch(ctx, ap, (float *)m->attn_scratch->dptr, splits));
-    if (p == 1) {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->h, tokens, H, m->qdim, m->h));
+    if (fuse_o) {
+      DP_TRY(dpk_attention_split_only(ctx, ap, (float *)m->attn_scratch->dptr, splits));
+      const int blocks = m->qdim / QK_K;
+      DP_LAUNCH(ctx, attn_combine_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->attn_scratch->dptr, m->att,
+                m->actq->dptr, m->nh, D, splits);
     } else {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, tokens, H, m->qdim, nullptr));
+      DP_TRY(dpk_attention_with_scratch(ctx, ap, (float *)m->attn_scratch->dptr, splits));
+    }
+    if (p == 1) {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->h, tokens, H, m->qdim, m->h, fuse_o));
+    } else {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, tokens, H, m->qdim, nullptr, fuse_o));
       DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
       DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
     }
-    DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr));
-    {
+    if (fuse_gu) {
+      DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps);
+    } else {
+      DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+    }
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, fuse_gu));
+    if (fuse_down) {
+      const int blocks = m->inter / QK_K;
+      DP_LAUNCH(ctx, silu_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->gu, m->actv, m->actq->dptr, m->inter);
+    } else {
       const size_t total = (size_t)tokens * m->inter;
       size_t grid = (total + 255) / 256;
       if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
       DP_LAUNCH(ctx, silu_gateup_kernel, (unsigned)grid, 256, 0, m->gu, m->actv, tokens, m->inter);
     }
     if (p == 1) {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->h, tokens, H, m->inter, m->h));
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->h, tokens, H, m->inter, m->h, fuse_down));
     } else {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, tokens, H, m->inter, nullptr));
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, tokens, H, m->inter, nullptr, fuse_down));
       DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
       DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
     }
@@ -602,7 +735,10 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
   struct Shape { int N, K; };
   const Shape sh[4] = {{m->qdim + 2 * m->kvdim, H}, {H, m->qdim}, {2 * m->inter, H}, {H, m->inter}};
   uint64_t n_launch = 0, n_bytes = 0;
+  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
+  DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
   const uint64_t l0 = ctx->launches;
+  ctx->pdl = true;
   DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
   for (int r = 0; r < reps; r++)
     for (int l = 0; l < c.n_layers; l++) {
@@ -612,10 +748,12 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
       const float *X[4] = {m->n, m->att, m->n, m->actv};
       float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
       for (int i = 0; i < 4; i++) {
-        DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr));
+        // digits_ready: in the decode step the producer kernel has already written them
+        DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K)));
         n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
       }
     }
+  ctx->pdl = false;
   DP_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
   DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   float ms = 0;

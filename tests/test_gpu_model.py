@@ -58,6 +58,12 @@ def test_small_model_tokens_identical(dev):
     _run_pair(dev, "small", prompt_len=40, steps=64, max_seq=128, kind="gaussian")
 
 
+def test_small_model_long_context_split_attention(dev):
+    """max_seq 1024 makes the decode attention split the KV range, which takes the fused
+    split-merge + activation-digit kernel on the way to o_proj."""
+    _run_pair(dev, "small", prompt_len=300, steps=64, max_seq=1024, kind="gaussian")
+
+
 def test_small_model_benchmark_blocks(dev):
     _run_pair(dev, "small", prompt_len=40, steps=64, max_seq=128, kind="blocks")
 
