@@ -1,3 +1,341 @@
-// placeholder, replaced below
+// Q4_K prefill GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// Replaces src/gpu/kernels/fused_matmul_q4_batched*.wgsl (:122, one workgroup per 4 rows x 1
+// column, every workgroup re-dequantises its weight row) and follows the numerics of the
+// reference's tiled prefill kernel fused_matmul_q4_prefill_tiled_f16.wgsl (:118-201): the
+// dequantised weight is rounded to f16 in shared memory, the contraction accumulates in f32.
+//
+//   C[M,N] = alpha * A[M,K] . W[N,K]^T,  A f16 (f32 inputs are cast first), W packed Q4_K.
+//
+// One CTA owns a 256 (M) x BN (N) output tile, two 128 x BN f32 accumulators in tensor memory.
+// Per 64-wide K step and pipeline stage:
+//   - warp 0 (one lane) brings the two 128 x 64 f16 activation tiles in with TMA tensor copies
+//     (128-byte swizzle, zero fill beyond M);
+//   - warps 2..9 read the packed Q4_K bytes of the BN weight rows (32 quant bytes + the block
+//     header per row and step), dequantise in registers, w = fma(d*sc, q, -dmin*m) rounded to
+//     f16, and store the BN x 64 tile into shared memory in the same 128-byte-swizzled K-major
+//     layout the tensor core expects (each weight is dequantised once per CTA);
+//   - warp 1 (one lane) issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) for both accumulators
+//     and commits to an mbarrier that frees the stage.
+// After the last step warps 2..9 read the accumulators back with tcgen05.ld (each warp its own
+// 32-lane quarter of tensor memory) and write C as f32 or f16.
+// Every mbarrier wait is bounded; on give-up the CTA raises a status word and still frees its
+// tensor memory.
 #include "common.h"
-dp_status dpk_gemm_q4k_tc(dp_ctx *, const uint8_t *, const void *, dp_dtype, void *, dp_dtype, int, int, int, float, bool *handled) { *handled = false; return DP_OK; }
+#include "mbar.cuh"
+#include "pdl.cuh"
+#include "q4k.cuh"
+
+#include <cuda.h>
+
+#include <cstdlib>
+#include <map>
+
+namespace {
+
+constexpr int BM = 256, BK = 64, TC_STAGES = 3;
+constexpr int TC_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 dequant + epilogue
+constexpr int DQ_WARPS = 8;
+
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  // K-major operand, 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO); LBO unused
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // start address
+  d |= (uint64_t)0 << 16;                             // leading byte offset
+  d |= (uint64_t)(1024u >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)1 << 46;                             // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                             // layout: SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N) {
+  // D = f32, A = B = f16, both K-major
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+struct TcSmem {
+  uint32_t a, b, bars, tmem_slot, abort_flag, total;
+  uint32_t stage_a, stage_b;
+};
+__host__ __device__ inline TcSmem tc_layout(int BN) {
+  TcSmem l;
+  l.stage_a = 2u * 128u * 128u;      // two 128-row tiles of 64 f16
+  l.stage_b = (uint32_t)BN * 128u;
+  l.a = 0;
+  l.b = TC_STAGES * l.stage_a;
+  l.bars = l.b + TC_STAGES * l.stage_b;  // full_a[S], full_b[S], empty[S], accum
+  l.tmem_slot = l.bars + (3 * TC_STAGES + 1) * 8;
+  l.abort_flag = l.tmem_slot + 8;
+  l.total = l.abort_flag + 8;
+  return l;
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                    const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
+                                                                    int N, int K, float alpha, int *__restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const TcSmem L = tc_layout(BN);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int bpr = K / QK_K, num_k = K / BK;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
+  const uint32_t bars = smem_u32(smem + L.bars);
+  auto full_a = [&](int s) { return bars + 8u * (uint32_t)s; };
+  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(TC_STAGES + s); };
+  auto empty = [&](int s) { return bars + 8u * (uint32_t)(2 * TC_STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (uint32_t)(3 * TC_STAGES);
+  constexpr uint32_t TMEM_COLS = 512;  // two accumulators of BN columns, rounded up to a power of two
+
+  pdl_launch();
+  pdl_wait();
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_a(s), 1); mbar_init(full_b(s), DQ_WARPS); mbar_init(empty(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {  // tensor-memory allocation is a warp-wide operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem + L.tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- activation tiles: TMA ----------------
+    if (lane == 0) {
+      for (int kt = 0; kt < num_k; kt++) {
+        const int s = kt % TC_STAGES;
+        const uint32_t n = (uint32_t)(kt / TC_STAGES);
+        if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) break;
+        mbar_expect_tx(full_a(s), L.stage_a);
+        const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
+        tma_load_2d(dst, &tmap_a, kt * BK, m0, full_a(s));
+        tma_load_2d(dst + 128u * 128u, &tmap_a, kt * BK, m0 + 128, full_a(s));
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(128, BN);
+      bool ok = true;
+      for (int kt = 0; kt < num_k && ok; kt++) {
+        const int s = kt % TC_STAGES;
+        const uint32_t n = (uint32_t)(kt / TC_STAGES);
+        if (!mbar_wait_bounded(full_a(s), n & 1u, abort_flag) || !mbar_wait_bounded(full_b(s), n & 1u, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
+        const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)s * L.stage_b);
+#pragma unroll
+        for (int k16 = 0; k16 < BK / 16; k16++) {
+          const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
+          const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
+          umma_f16(tmem_base, umma_desc_sw128(a_addr + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+          umma_f16(tmem_base + (uint32_t)BN, umma_desc_sw128(a_addr + 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+        }
+        umma_commit(empty(s));  // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  } else {
+    // ---------------- weight tiles: dequantise into swizzled shared memory ----------------
+    const int dw = warp - 2;            // 0..7
+    const int r8 = lane & 7, oct = lane >> 3;  // row within the 8-row group, byte octet of the 32-byte chunk
+    bool ok = true;
+    for (int kt = 0; kt < num_k && ok; kt++) {
+      const int s = kt % TC_STAGES;
+      const uint32_t n = (uint32_t)(kt / TC_STAGES);
+      if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) { ok = false; break; }
+      const int b = kt >> 2, chunk = kt & 3;
+      uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
+      for (int rg = dw; rg < BN / 8; rg += DQ_WARPS) {
+        const int row = n0 + rg * 8 + r8;
+        const uint32_t *blk = reinterpret_cast<const uint32_t *>(W + ((size_t)row * bpr + b) * Q4K_BLOCK_BYTES);
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+        const uint2 q = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * chunk) + oct);
+        const float2 dd = q4k_d_dmin(hdr.x);
+        const Q4KScales sc = q4k_unpack_scales(hdr.y, hdr.z, hdr.w);
+        const float s_lo = __fmul_rn(dd.x, (float)q4k_sc(sc, 2 * chunk)), m_lo = __fmul_rn(dd.y, (float)q4k_mn(sc, 2 * chunk));
+        const float s_hi = __fmul_rn(dd.x, (float)q4k_sc(sc, 2 * chunk + 1)), m_hi = __fmul_rn(dd.y, (float)q4k_mn(sc, 2 * chunk + 1));
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const uint32_t word = i < 2 ? q.x : q.y;
+          const uint32_t b0 = (word >> (16 * (i & 1))) & 0xffu, b1 = (word >> (16 * (i & 1) + 8)) & 0xffu;
+          const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, (float)(b0 & 15u), -m_lo), __fmaf_rn(s_lo, (float)(b1 & 15u), -m_lo));
+          const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, (float)(b0 >> 4), -m_hi), __fmaf_rn(s_hi, (float)(b1 >> 4), -m_hi));
+          lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
+          hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+        // row r of an 8-row group: 16-byte chunk j lives at chunk (j ^ r) of the 128-byte line
+        uint8_t *line = bt + (uint32_t)rg * 1024u + (uint32_t)r8 * 128u;
+        *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_b(s));
+    }
+    // ---------------- epilogue: tensor memory -> registers -> C ----------------
+    if (ok && mbar_wait_bounded(accum_bar, 0u, abort_flag)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quad = warp & 3;         // the 32 TMEM lanes this warp may read
+      const int half = dw >> 2;          // two warps share a quarter: each takes half of the column groups
+      constexpr int GROUPS = BN / 32;
+#pragma unroll 1
+      for (int mt = 0; mt < 2; mt++) {
+        const int row = m0 + mt * 128 + quad * 32 + lane;
+#pragma unroll 1
+        for (int cg = half; cg < GROUPS; cg += 2) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * BN + cg * 32), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row < M) {
+            OutT *dst = C + (size_t)row * N + n0 + cg * 32;
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
+                                                                   __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint32_t p[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * alpha, __uint_as_float(r[i + 2 * j + 1]) * alpha);
+                  p[j] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+  if (*abort_flag && tid == 0) atomicExch(err, 2);
+}
+
+// f32 -> f16 (round to nearest even), the cast the reference inserts in front of an f16 kernel
+// (src/gpu/kernels/matmul.js:431-450)
+__global__ void cast_f32_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, size_t n) {
+  pdl_launch();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = __float2half_rn(in[i]);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int BN, typename OutT>
+dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  const size_t smem = tc_layout(BN).total + 1024;
+  static bool attr = false;
+  if (!attr) {
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  dim3 grid(N / BN, (M + BM - 1) / BM);
+  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, OutT>), grid, TC_THREADS, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  return DP_OK;
+}
+
+}  // namespace
+
+dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
+                          int N, int K, float alpha, bool *handled) {
+  *handled = false;
+  static int enabled = -1;
+  if (enabled < 0) { const char *e = getenv("DP_GEMM_TC"); enabled = e ? atoi(e) : 1; }
+  if (!enabled || !ctx->dev_status) return DP_OK;
+  if (K % QK_K || M < 1) return DP_OK;
+  int bn = 0;
+  if (N % 192 == 0) bn = 192;
+  else if (N % 128 == 0) bn = 128;
+  if (!bn) return DP_OK;
+  EncodeTiledFn encode = get_encode();
+  if (!encode) return DP_OK;
+
+  const __half *a16 = (const __half *)A;
+  dp_buf tmp = nullptr;
+  if (a_dtype == DP_F32) {
+    DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_cast", &tmp));
+    size_t n = (size_t)M * K, grid = (n + 255) / 256;
+    if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
+    DP_LAUNCH(ctx, cast_f32_f16_kernel, (unsigned)grid, 256, 0, (const float *)A, (__half *)tmp->dptr, n);
+    a16 = (const __half *)tmp->dptr;
+  } else if (a_dtype != DP_F16) {
+    return DP_OK;
+  }
+  CUtensorMap tm;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  dp_status st = DP_OK;
+  if (r != CUDA_SUCCESS) {
+    st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
+  } else if (c_dtype == DP_F32) {
+    st = bn == 192 ? launch_tc<192, float>(ctx, tm, W, (float *)C, M, N, K, alpha) : launch_tc<128, float>(ctx, tm, W, (float *)C, M, N, K, alpha);
+  } else if (c_dtype == DP_F16) {
+    st = bn == 192 ? launch_tc<192, __half>(ctx, tm, W, (__half *)C, M, N, K, alpha) : launch_tc<128, __half>(ctx, tm, W, (__half *)C, M, N, K, alpha);
+  } else {
+    st = dp_fail(ctx, DP_ERR_INVALID, "matmul: unsupported output dtype");
+  }
+  if (tmp) dp_buf_release(ctx, tmp);  // stream ordered: reused only by later work
+  if (st == DP_OK) *handled = true;
+  return st;
+}

@@ -516,9 +516,10 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   }
   // the GEMM may not alias its output with the residual: go through the partial buffer
   float *dst = (residual && residual == y) ? m->partial : y;
-  bool handled = false;
-  DP_TRY(dpk_gemm_q4k_tc(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f, &handled));
-  if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
+  // f32 activations keep the f32-exact weight path (the reference's rule: f32 A selects the f32
+  // batched kernel, matmul.rules.json:15-22); the tensor-core kernel takes f16 activations, which
+  // the residual stream of a random-init model would overflow
+  DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
 }

@@ -104,7 +104,7 @@ extern "C" dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A
         st = dpk_gemv_q4k(ctx, (const uint8_t *)bptr, (const float *)aptr, cptr, o.out_dtype, N, K, o.alpha, nullptr);
     } else {
       bool handled = false;
-      if (!o.exact_weights && M > 1)
+      if (!o.exact_weights && M > 1 && A->dtype == DP_F16)  // f16 activations: tensor cores (matmul.rules.json:17)
         st = dpk_gemm_q4k_tc(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha, &handled);
       if (st == DP_OK && !handled)
         st = dpk_gemm_q4k_simt(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha);
