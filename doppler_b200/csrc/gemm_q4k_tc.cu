@@ -34,8 +34,7 @@
 namespace {
 
 constexpr int BM = 256, BK = 64, TC_STAGES = 3;
-constexpr int TC_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 dequant + epilogue
-constexpr int DQ_WARPS = 8;
+// warp 0: TMA, warp 1: MMA issue, warps 2 .. 2+DQ_WARPS-1: dequant + epilogue (DQ_WARPS % 4 == 0)
 
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   // K-major operand, 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO); LBO unused
@@ -96,8 +95,8 @@ __host__ __device__ inline TcSmem tc_layout(int BN) {
   return l;
 }
 
-template <int BN, typename OutT>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+template <int BN, int DQ_WARPS, typename OutT>
+__global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, float alpha, int *__restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
@@ -173,51 +172,92 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4k_tc_kernel(const __grid
     const int dw = warp - 2;            // 0..7
     const int r8 = lane & 7, oct = lane >> 3;  // row within the 8-row group, byte octet of the 32-byte chunk
     bool ok = true;
-    for (int kt = 0; kt < num_k && ok; kt++) {
-      const int s = kt % TC_STAGES;
-      const uint32_t n = (uint32_t)(kt / TC_STAGES);
-      if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) { ok = false; break; }
-      const int b = kt >> 2, chunk = kt & 3;
-      uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
-      for (int rg = dw; rg < BN / 8; rg += DQ_WARPS) {
-        const int row = n0 + rg * 8 + r8;
-        const uint32_t *blk = reinterpret_cast<const uint32_t *>(W + ((size_t)row * bpr + b) * Q4K_BLOCK_BYTES);
-        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-        const uint2 q = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * chunk) + oct);
-        const float2 dd = q4k_d_dmin(hdr.x);
-        const Q4KScales sc = q4k_unpack_scales(hdr.y, hdr.z, hdr.w);
-        const float s_lo = __fmul_rn(dd.x, (float)q4k_sc(sc, 2 * chunk)), m_lo = __fmul_rn(dd.y, (float)q4k_mn(sc, 2 * chunk));
-        const float s_hi = __fmul_rn(dd.x, (float)q4k_sc(sc, 2 * chunk + 1)), m_hi = __fmul_rn(dd.y, (float)q4k_mn(sc, 2 * chunk + 1));
-        uint32_t lo[4], hi[4];
+    constexpr int RG = BN / 8 / DQ_WARPS;  // 8-row groups per warp
+    // software pipeline at super-block granularity: while the four K steps of block b are dequantised,
+    // the header and the four quant pieces of block b+1 are already in flight
+    uint4 hdr[RG];
+    uint2 qn[RG][4];
+    const uint32_t *rowp[RG];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const uint32_t word = i < 2 ? q.x : q.y;
-          const uint32_t b0 = (word >> (16 * (i & 1))) & 0xffu, b1 = (word >> (16 * (i & 1) + 8)) & 0xffu;
-          const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, (float)(b0 & 15u), -m_lo), __fmaf_rn(s_lo, (float)(b1 & 15u), -m_lo));
-          const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, (float)(b0 >> 4), -m_hi), __fmaf_rn(s_hi, (float)(b1 >> 4), -m_hi));
-          lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
-          hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+    for (int j = 0; j < RG; j++) {
+      rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (dw + j * DQ_WARPS) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+      hdr[j] = __ldg(reinterpret_cast<const uint4 *>(rowp[j]));
+#pragma unroll
+      for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(rowp[j] + 4 + 8 * c) + oct);
+    }
+    for (int kb = 0; kb < bpr && ok; kb++) {
+      // rotate the prefetch buffers and decode the block headers once for the four K steps
+      float sc_f[RG][8], mn_f[RG][8];
+      uint2 qcur[RG][4];
+#pragma unroll
+      for (int j = 0; j < RG; j++) {
+        const float2 dd = q4k_d_dmin(hdr[j].x);
+        const Q4KScales sc = q4k_unpack_scales(hdr[j].y, hdr[j].z, hdr[j].w);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          sc_f[j][i] = __fmul_rn(dd.x, q4k_u8_to_float(q4k_sc(sc, i)));
+          mn_f[j][i] = __fmul_rn(dd.y, q4k_u8_to_float(q4k_mn(sc, i)));
         }
-        // row r of an 8-row group: 16-byte chunk j lives at chunk (j ^ r) of the 128-byte line
-        uint8_t *line = bt + (uint32_t)rg * 1024u + (uint32_t)r8 * 128u;
-        *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+#pragma unroll
+        for (int c = 0; c < 4; c++) qcur[j][c] = qn[j][c];
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_b(s));
+      if (kb + 1 < bpr) {
+#pragma unroll
+        for (int j = 0; j < RG; j++) {
+          const uint32_t *blk = rowp[j] + (size_t)(kb + 1) * Q4K_BLOCK_WORDS;
+          hdr[j] = __ldg(reinterpret_cast<const uint4 *>(blk));
+#pragma unroll
+          for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * c) + oct);
+        }
+      }
+#pragma unroll
+      for (int chunk = 0; chunk < 4; chunk++) {
+        const int kt = kb * 4 + chunk;
+        const int s = kt % TC_STAGES;
+        const uint32_t n = (uint32_t)(kt / TC_STAGES);
+        if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) { ok = false; break; }
+        uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
+#pragma unroll
+        for (int j = 0; j < RG; j++) {
+          const uint2 q = qcur[j][chunk];
+          const float s_lo = sc_f[j][2 * chunk], m_lo = mn_f[j][2 * chunk], s_hi = sc_f[j][2 * chunk + 1], m_hi = mn_f[j][2 * chunk + 1];
+          // nibble -> f32 without the conversion pipe: PRMT builds the float 2^23 + q from a byte
+          uint32_t lo[4], hi[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t word = i < 2 ? q.x : q.y;
+            const uint32_t wl = word & 0x0f0f0f0fu, wh = (word >> 4) & 0x0f0f0f0fu;
+            const uint32_t sel0 = (i & 1) ? 0x7442u : 0x7440u, sel1 = (i & 1) ? 0x7443u : 0x7441u;
+            const float ql0 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel0)) - 8388608.0f;
+            const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
+            const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
+            const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
+            const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
+            const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
+            lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+          }
+          // row r of an 8-row group: 16-byte chunk c lives at chunk (c ^ r) of the 128-byte line
+          uint8_t *line = bt + (uint32_t)(dw + j * DQ_WARPS) * 1024u + (uint32_t)r8 * 128u;
+          *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_b(s));
+      }
     }
     // ---------------- epilogue: tensor memory -> registers -> C ----------------
     if (ok && mbar_wait_bounded(accum_bar, 0u, abort_flag)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int quad = warp & 3;         // the 32 TMEM lanes this warp may read
-      const int half = dw >> 2;          // two warps share a quarter: each takes half of the column groups
+      const int half = dw >> 2;          // DQ_WARPS/4 warps share a quarter and split the column groups
       constexpr int GROUPS = BN / 32;
 #pragma unroll 1
       for (int mt = 0; mt < 2; mt++) {
         const int row = m0 + mt * 128 + quad * 32 + lane;
 #pragma unroll 1
-        for (int cg = half; cg < GROUPS; cg += 2) {
+        for (int cg = half; cg < GROUPS; cg += DQ_WARPS / 4) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * BN + cg * 32), r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -278,17 +318,25 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
-template <int BN, typename OutT>
+template <int BN, int DQ_WARPS, typename OutT>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
   const size_t smem = tc_layout(BN).total + 1024;
   static bool attr = false;
   if (!attr) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
   dim3 grid(N / BN, (M + BM - 1) / BM);
-  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, OutT>), grid, TC_THREADS, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
   return DP_OK;
+}
+
+template <typename OutT>
+dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  static int wide = -1;
+  if (wide < 0) { const char *e = getenv("DP_GEMM_DQ_WIDE"); wide = e ? atoi(e) : 0; }
+  if (bn == 192) return wide ? launch_tc<192, 24, OutT>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT>(ctx, tm, W, C, M, N, K, alpha);
+  return wide ? launch_tc<128, 16, OutT>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT>(ctx, tm, W, C, M, N, K, alpha);
 }
 
 }  // namespace
@@ -329,9 +377,9 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
   } else if (c_dtype == DP_F32) {
-    st = bn == 192 ? launch_tc<192, float>(ctx, tm, W, (float *)C, M, N, K, alpha) : launch_tc<128, float>(ctx, tm, W, (float *)C, M, N, K, alpha);
+    st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, alpha);
   } else if (c_dtype == DP_F16) {
-    st = bn == 192 ? launch_tc<192, __half>(ctx, tm, W, (__half *)C, M, N, K, alpha) : launch_tc<128, __half>(ctx, tm, W, (__half *)C, M, N, K, alpha);
+    st = dispatch_tc<__half>(ctx, bn, tm, W, (__half *)C, M, N, K, alpha);
   } else {
     st = dp_fail(ctx, DP_ERR_INVALID, "matmul: unsupported output dtype");
   }
