@@ -151,7 +151,7 @@ def bench_config(args, cfg, context):
     return {"workload": f"{args.workload}-shaped Q4_K decoder, batch 1, greedy decode at context {context}",
             "layers": cfg["n_layers"], "hidden": cfg["hidden"], "heads": f"{cfg['n_heads']}q/{cfg['n_kv_heads']}kv",
             "head_dim": cfg["head_dim"], "mlp": cfg["inter"], "vocab": cfg["vocab"], "prompt": context, "batch": 1,
-            "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2 (weights 3.9 GB + LM head 1.2 GB per step at 9b)"}
+            "parallelism": f"tp{args.gpus}" + (f" ({args.allreduce} allreduce)" if args.gpus > 1 else ""), "l2": "inputs larger than L2 (weights 3.9 GB + LM head 1.2 GB per step at 9b)"}
 
 
 # ----------------------------------------------------------------------------------------
@@ -163,6 +163,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="9b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
+                    help="N>1: one-shot peer-memory exchange fused into the decode kernels, or NCCL")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -200,21 +202,16 @@ def main():
 
     dev = Device(local_rank)
     if world > 1:
-        import torch
-        uid = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = (C.c_uint8 * 128)()
-            st = dev.lib.dp_tp_unique_id(buf)
-            if st != L.OK:
-                raise SystemExit("cannot create the NCCL unique id")
-            uid = torch.tensor(list(buf), dtype=torch.uint8)
-        dist.broadcast(uid, 0)
-        ub = (C.c_uint8 * 128)(*uid.tolist())
-        dev.check(dev.lib.dp_tp_init(dev.h, rank, world, ub))
+        from doppler_b200 import tp
+        tp.init_group(dev, rank, world)
+        if args.allreduce == "oneshot":
+            tp.setup_exchange(dev, rank, world)
 
     steps_total = args.warmup + args.steps
     max_seq = context + 2 * steps_total + 64
     model = DecoderModel(dev, cfg, max_seq=max_seq, tp_rank=rank, tp_size=world)
+    if world > 1 and args.allreduce == "oneshot":
+        model.set_allreduce_mode(1)
     model.load_synthetic()
     prompt = synthetic.make_prompt(cfg, context)
 

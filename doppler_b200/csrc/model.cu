@@ -17,6 +17,7 @@
 #include "pdl.cuh"
 #include "q4k.cuh"
 #include "actq.cuh"
+#include "tp_exchange.h"
 
 #include <cfloat>
 #include <cmath>
@@ -38,6 +39,7 @@ dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float 
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
 dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 bool dp_tp_ready(dp_ctx *ctx);
+dp_tp_exchange *dp_tp_exchange_desc(dp_ctx *ctx);
 
 struct LayerW {
   dp_buf qkv = nullptr, o = nullptr, gateup = nullptr, down = nullptr;
@@ -72,6 +74,7 @@ struct dp_model {
   double last_ms = 0;
   size_t weight_bytes = 0;
   int allreduce_mode = 0;
+  bool final_norm_done = false;  // set by run_layers when the exchange kernel already applied the final RMSNorm
 };
 
 // ---- model-specific kernels ---------------------------------------------------
@@ -284,6 +287,111 @@ __global__ void __launch_bounds__(256) attn_combine_actq_kernel(const float *__r
   actq_emit_block(o, lane, b, bpr, actq);
 }
 
+// ---- one-shot allreduce over peer memory, fused with the residual add and the next RMSNorm ----
+// (no counterpart in the reference, which has no collective backend).  One CTA per rank:
+//   1. push this rank's partial vector into its slot of EVERY rank's exchange area (plain stores
+//      over NVLink), fence, then raise this rank's epoch flag in every area;
+//   2. poll the flags of all ranks in this rank's OWN memory (bounded; on give-up a status word is
+//      raised and the kernel carries on so nothing hangs);
+//   3. h += sum of the slots in rank order (the same order on every rank, so all ranks hold the
+//      same bits), then RMSNorm with `norm_w` -> n_out and the GEMV activation digits.
+// Two parity sets of slots: a rank can be at most one exchange ahead of the slowest rank, because
+// finishing exchange e needs every rank's flag for e.
+__global__ void __launch_bounds__(256) tp_allreduce_rmsnorm_kernel(dp_tp_exchange *__restrict__ xd, const float *__restrict__ partial,
+                                                                   float *__restrict__ h, const float *__restrict__ norm_w,
+                                                                   float *__restrict__ n_out, void *__restrict__ actq, int size,
+                                                                   float eps, int *__restrict__ err) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sh[32];
+  __shared__ unsigned s_epoch;
+  __shared__ int s_bad;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, bpr = size / QK_K;
+  const int rank = xd->rank, nr = xd->size;
+  if (tid == 0) { s_epoch = ++xd->epoch; s_bad = 0; }
+  __syncthreads();
+  const unsigned e = s_epoch;
+  const size_t par_off = (size_t)(e & 1u) * DP_TP_MAX_RANKS * DP_TP_SLOT_FLOATS;
+  // 1. push
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const int off = b * QK_K + lane * 8;
+      const float4 a = *reinterpret_cast<const float4 *>(partial + off), c = *reinterpret_cast<const float4 *>(partial + off + 4);
+      for (int r = 0; r < nr; r++) {
+        float *dst = xd->area[r] + par_off + (size_t)rank * DP_TP_SLOT_FLOATS + off;
+        *reinterpret_cast<float4 *>(dst) = a;
+        *reinterpret_cast<float4 *>(dst + 4) = c;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < nr) {
+    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(xd->area[tid] + dp_tp_flags_offset_floats()) + (e & 1u) * DP_TP_MAX_RANKS + rank;
+    *flag = e;
+  }
+  // 2. wait for every rank's flag in local memory
+  if (tid < nr) {
+    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(xd->area[rank] + dp_tp_flags_offset_floats()) + (e & 1u) * DP_TP_MAX_RANKS + tid;
+    bool seen = false;
+    for (unsigned it = 0; it < (1u << 22); it++) {
+      if ((int)(*flag - e) >= 0) { seen = true; break; }
+    }
+    if (!seen) { s_bad = 1; atomicExch(err, 3); }
+  }
+  __syncthreads();
+  __threadfence_system();
+  // 3. reduce in rank order, residual add, RMSNorm, digits
+  const float *mine = xd->area[rank] + par_off;
+  float v[4][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const int off = b * QK_K + lane * 8;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < nr; r++) {
+        const float *src = mine + (size_t)r * DP_TP_SLOT_FLOATS + off;
+        const float4 a = __ldcv(reinterpret_cast<const float4 *>(src)), c = __ldcv(reinterpret_cast<const float4 *>(src + 4));  // written by peers: never from a stale L1 line
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += c.x; acc[5] += c.y; acc[6] += c.z; acc[7] += c.w;
+      }
+      const float4 ha = *reinterpret_cast<const float4 *>(h + off), hc = *reinterpret_cast<const float4 *>(h + off + 4);
+      v[i][0] = ha.x + acc[0]; v[i][1] = ha.y + acc[1]; v[i][2] = ha.z + acc[2]; v[i][3] = ha.w + acc[3];
+      v[i][4] = hc.x + acc[4]; v[i][5] = hc.y + acc[5]; v[i][6] = hc.z + acc[6]; v[i][7] = hc.w + acc[7];
+      *reinterpret_cast<float4 *>(h + off) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      *reinterpret_cast<float4 *>(h + off + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+#pragma unroll
+      for (int j = 0; j < 8; j++) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) sh[warp] = ss;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) total += sh[i];
+  const float inv_rms = 1.0f / sqrtf(total / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const int off = b * QK_K + lane * 8;
+      const float4 wa = *reinterpret_cast<const float4 *>(norm_w + off), wc = *reinterpret_cast<const float4 *>(norm_w + off + 4);
+      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) o[j] = v[i][j] * inv_rms * wv[j];
+      *reinterpret_cast<float4 *>(n_out + off) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4 *>(n_out + off + 4) = make_float4(o[4], o[5], o[6], o[7]);
+      actq_emit_block(o, lane, b, bpr, actq);
+    }
+  }
+}
+
 // ---- create / destroy -----------------------------------------------------------
 static size_t q4k_bytes(size_t n, size_t k) { return n * dp_cdiv(k, DP_QK_K) * DP_Q4K_BLOCK_BYTES; }
 static size_t align_up(size_t v, size_t a) { return dp_cdiv(v, a) * a; }
@@ -494,7 +602,14 @@ extern "C" double dp_model_last_decode_ms(dp_model *m) { return m ? m->last_ms :
 
 extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
   if (!m) return DP_ERR_INVALID;
-  if (mode != 0) return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode %d is not available", mode);
+  if (mode != 0 && mode != 1) return dp_fail(m->ctx, DP_ERR_INVALID, "model: unknown allreduce mode %d", mode);
+  if (mode == 1) {
+    if (m->cfg.tp_size > 1 && !dp_tp_exchange_desc(m->ctx))
+      return dp_fail(m->ctx, DP_ERR_STATE, "model: allreduce mode 1 needs the peer-memory exchange area (dp_tp_ipc_export / dp_tp_ipc_attach)");
+    if (m->cfg.hidden % DP_QK_K || m->cfg.hidden > DP_TP_SLOT_FLOATS)
+      return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode 1 carries hidden sizes that are multiples of 256 up to %d", DP_TP_SLOT_FLOATS);
+  }
+  for (int i = 0; i < 2; i++) if (m->graph[i]) { dp_graph_destroy(m->graph[i]); m->graph[i] = nullptr; }
   m->allreduce_mode = mode;
   return DP_OK;
 }
@@ -533,6 +648,10 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
   const int H = c.hidden, D = c.head_dim, p = c.tp_size;
   const size_t kv_seq_stride = (size_t)c.max_seq * m->kvdim;
   const int heads = m->nh + 2 * m->nkv;
+  // tensor-parallel single-token decode with the one-shot exchange: the kernel that sums the
+  // partial vectors also applies the residual and the NEXT RMSNorm (and emits its digits)
+  const bool fused_ar = decode && tokens == 1 && p > 1 && m->allreduce_mode == 1 && dp_tp_exchange_desc(ctx) != nullptr;
+  bool n_ready = false;  // m->n / digits already hold rmsnorm(h, in_norm of this layer)
   for (int l = 0; l < c.n_layers; l++) {
     LayerW &L = m->layers[l];
     // single-token decode: the producers of a GEMV's input also emit its fixed-point digits
@@ -541,12 +660,16 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     const bool fuse_gu = fuse && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
     const bool fuse_o = fuse && dpk_gemv_q4k_fast_ok(H, m->qdim) && m->attn_splits_decode > 1 && D % 8 == 0;
     const bool fuse_down = fuse && dpk_gemv_q4k_fast_ok(H, m->inter);
-    if (fuse_qkv) {
+    bool dq_qkv = fuse_qkv;  // digits of rmsnorm(h) are in m->actq
+    if (n_ready) {
+      n_ready = false;
+      dq_qkv = true;
+    } else if (fuse_qkv) {
       DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.in_norm, m->n, m->actq->dptr, H, c.eps);
     } else {
       DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
     }
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr, fuse_qkv));
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr, dq_qkv));
     {
       const int warps = tokens * heads;
       DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
@@ -582,15 +705,22 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->h, tokens, H, m->qdim, m->h, fuse_o));
     } else {
       DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, tokens, H, m->qdim, nullptr, fuse_o));
-      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
-      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+      if (fused_ar) {
+        DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h,
+                  (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps, ctx->dev_status);
+      } else {
+        DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+        DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+      }
     }
-    if (fuse_gu) {
+    if (fused_ar) {
+      // m->n and the digits were written by the exchange kernel
+    } else if (fuse_gu) {
       DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps);
     } else {
       DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
     }
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, fuse_gu));
+    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, fuse_gu || fused_ar));
     if (fuse_down) {
       const int blocks = m->inter / QK_K;
       DP_LAUNCH(ctx, silu_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->gu, m->actv, m->actq->dptr, m->inter);
@@ -604,10 +734,18 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->h, tokens, H, m->inter, m->h, fuse_down));
     } else {
       DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, tokens, H, m->inter, nullptr, fuse_down));
-      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
-      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+      if (fused_ar) {
+        const float *next_w = l + 1 < c.n_layers ? m->layers[l + 1].in_norm : m->final_norm;
+        DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h, next_w,
+                  m->n, m->actq->dptr, H, c.eps, ctx->dev_status);
+        n_ready = true;
+      } else {
+        DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+        DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
+      }
     }
   }
+  m->final_norm_done = n_ready;
   return DP_OK;
 }
 
@@ -615,7 +753,9 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
 static dp_status run_head(dp_model *m, const float *hrow, int rows) {
   dp_ctx *ctx = m->ctx;
   const dp_model_cfg &c = m->cfg;
-  DP_TRY(dpk_rmsnorm(ctx, hrow, m->final_norm, false, nullptr, false, nullptr, m->n, rows, c.hidden, c.eps, false, 1.0f));
+  if (!(m->final_norm_done && rows == 1))
+    DP_TRY(dpk_rmsnorm(ctx, hrow, m->final_norm, false, nullptr, false, nullptr, m->n, rows, c.hidden, c.eps, false, 1.0f));
+  m->final_norm_done = false;
   DP_TRY(dpk_gemv_f16w(ctx, (const __half *)m->lm_head->dptr, m->n, DP_F32, m->logits, DP_F32, rows, m->vocab_l, c.hidden, 1.0f));
   for (int b = 0; b < rows; b++)
     DP_TRY(dpk_argmax(ctx, m->logits + (size_t)b * m->vocab_l, m->vocab_l, -1, m->d_tok, b, m->am_vals + (size_t)b * 256,

@@ -7,6 +7,7 @@
 // data-path exchange of the column/row-parallel split: one sum over ranks after
 // o_proj and one after down_proj.
 #include "common.h"
+#include "tp_exchange.h"
 
 #include <dlfcn.h>
 
@@ -58,6 +59,11 @@ static bool load_nccl(std::string *why) {
 struct dp_tp_state {
   int rank = 0, size = 1;
   ncclComm_t comm = nullptr;
+  // peer-memory exchange area (one per rank, mapped into every rank with CUDA IPC)
+  void *xbuf = nullptr;             // this rank's area
+  void *peer[DP_TP_MAX_RANKS] = {}; // every rank's area as seen from this process (peer[rank] == xbuf)
+  bool attached = false;
+  dp_tp_exchange *dev_desc = nullptr;  // device copy of the descriptor handed to kernels
 };
 
 bool dp_tp_ready(dp_ctx *ctx) { return ctx && ctx->tp && ctx->tp->comm; }
@@ -95,6 +101,10 @@ extern "C" dp_status dp_tp_init(dp_ctx *ctx, int rank, int size, const void *id1
 extern "C" dp_status dp_tp_destroy(dp_ctx *ctx) {
   if (!ctx || !ctx->tp) return DP_OK;
   if (ctx->tp->comm) g_nccl.CommDestroy(ctx->tp->comm);
+  for (int r = 0; r < ctx->tp->size; r++)
+    if (ctx->tp->attached && r != ctx->tp->rank && ctx->tp->peer[r]) cudaIpcCloseMemHandle(ctx->tp->peer[r]);
+  if (ctx->tp->dev_desc) cudaFree(ctx->tp->dev_desc);
+  if (ctx->tp->xbuf) cudaFree(ctx->tp->xbuf);
   delete ctx->tp;
   ctx->tp = nullptr;
   return DP_OK;
@@ -123,10 +133,56 @@ extern "C" dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf b
   return DP_OK;
 }
 
-extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *) {
-  return dp_fail(ctx, DP_ERR_UNSUPPORTED, "peer-memory exchange area is not built into this library yet");
+// ---- peer-memory exchange area ------------------------------------------------------------
+// Each rank owns one area: two parity sets of `size` slots of DP_TP_SLOT_FLOATS floats plus one
+// epoch flag per (parity, source rank).  A rank PUSHES its partial vector into its slot of every
+// rank's area with ordinary stores over NVLink and then raises its flag there; the consumer polls
+// flags in its OWN memory only (see tp_fused.cu).
+extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *out64) {
+  if (!ctx || !out64) return DP_ERR_INVALID;
+  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_export: call dp_tp_init first");
+  dp_tp_state *tp = ctx->tp;
+  DP_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!tp->xbuf) {
+    DP_CUDA(ctx, cudaMalloc(&tp->xbuf, dp_tp_area_bytes()));
+    DP_CUDA(ctx, cudaMemset(tp->xbuf, 0, dp_tp_area_bytes()));
+    DP_CUDA(ctx, cudaDeviceSynchronize());
+  }
+  cudaIpcMemHandle_t h;
+  DP_CUDA(ctx, cudaIpcGetMemHandle(&h, tp->xbuf));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return DP_OK;
 }
 
-extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *) {
-  return dp_fail(ctx, DP_ERR_UNSUPPORTED, "peer-memory exchange area is not built into this library yet");
+extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *handles64_by_rank) {
+  if (!ctx || !handles64_by_rank) return DP_ERR_INVALID;
+  if (!dp_tp_ready(ctx) || !ctx->tp->xbuf) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_attach: export this rank's area first");
+  dp_tp_state *tp = ctx->tp;
+  if (tp->attached) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_attach: already attached");
+  DP_CUDA(ctx, cudaSetDevice(ctx->device));
+  for (int r = 0; r < tp->size; r++) {
+    if (r == tp->rank) { tp->peer[r] = tp->xbuf; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char *)handles64_by_rank + 64 * r, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(&tp->peer[r], h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return dp_fail(ctx, DP_ERR_COMM, "tp_ipc_attach: cannot map rank %d's exchange area: %s", r, cudaGetErrorString(e));
+    }
+  }
+  dp_tp_exchange d;
+  memset(&d, 0, sizeof d);
+  d.rank = tp->rank; d.size = tp->size;
+  for (int r = 0; r < tp->size; r++) d.area[r] = (float *)tp->peer[r];
+  DP_CUDA(ctx, cudaMalloc(&tp->dev_desc, sizeof d + 64));
+  DP_CUDA(ctx, cudaMemset(tp->dev_desc, 0, sizeof d + 64));
+  DP_CUDA(ctx, cudaMemcpy(tp->dev_desc, &d, sizeof d, cudaMemcpyHostToDevice));
+  tp->attached = true;
+  return DP_OK;
+}
+
+// descriptor for the fused kernels, or nullptr when the exchange area is not attached
+dp_tp_exchange *dp_tp_exchange_desc(dp_ctx *ctx) {
+  return (ctx && ctx->tp && ctx->tp->attached) ? ctx->tp->dev_desc : nullptr;
 }

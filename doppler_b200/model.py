@@ -118,6 +118,11 @@ class DecoderModel:
         self.device.check(self.device.lib.dp_model_read_hidden(self.h, out.ctypes.data_as(C.c_void_p), out.size))
         return out
 
+    def set_allreduce_mode(self, mode: int):
+        """0: NCCL allreduce + residual add; 1: one-shot peer-memory exchange fused with the residual
+        add and the next RMSNorm (single-token decode; needs tp.setup_exchange)."""
+        self.device.check(self.device.lib.dp_model_set_allreduce_mode(self.h, mode))
+
     def bench_gemv(self, reps: int = 1) -> dict:
         """Device time of all Q4_K decode GEMVs of the model, back to back (CUDA events)."""
         ms, n, b = C.c_double(), C.c_uint64(), C.c_uint64()
