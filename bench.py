@@ -154,6 +154,88 @@ def bench_config(args, cfg, context):
             "parallelism": f"tp{args.gpus}" + (f" ({args.allreduce} allreduce)" if args.gpus > 1 else ""), "l2": "inputs larger than L2 (weights 3.9 GB + LM head 1.2 GB per step at 9b)"}
 
 
+
+# ----------------------------------------------------------------------------------------
+# single-kernel cases (secondary metrics and profiler targets)
+# ----------------------------------------------------------------------------------------
+def _graph_time(dev, ops, record, n_ops, reps):
+    """Record `record(rec)` (n_ops launches of the op over distinct inputs) into one CUDA graph and time
+    `reps` replays with the host clock around a synchronise (the graph keeps the GPU busy back to back)."""
+    rec = ops.CommandRecorder(dev, "case", capture_graph=True)
+    record(rec)
+    g = rec.finish_graph()
+    for _ in range(3):
+        g.launch()
+    dev.sync()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        g.launch()
+    dev.sync()
+    dt = (time.perf_counter() - t0) / (reps * n_ops)
+    g.destroy()
+    return dt
+
+
+def kernel_case(args):
+    from doppler_b200 import ops, synthetic
+    dev = ops.Device(0)
+    peak, peak_src = measured_peaks()
+    out_lines = []
+    if args.case == "gemv":
+        shapes = [tuple(int(v) for v in args.shape.split(","))] if args.shape else [(3072, 1024), (12288, 4096), (4096, 12288), (24576, 4096)]
+        for N, K in shapes:
+            wbytes = N * ((K + 255) // 256) * 144
+            copies = args.copies or max(4, int(300e6 / wbytes))
+            ws = [dev.weight_from(synthetic.q4k_matrix(synthetic.key(5, i), N, K), "q4k", [N, K]) for i in range(copies)]
+            x = dev.tensor_from(synthetic.normal_f32(synthetic.key(5, 100), K).reshape(1, K))
+            out = dev.acquire_buffer(N * 4, "y")
+            dt = _graph_time(dev, ops, lambda rec: [ops.record_matmul(rec, x, w, 1, N, K, output_dtype="f32", output_buffer=out) for w in ws],
+                             copies, max(args.steps // 8, 3))
+            b = wbytes + 4 * K + 4 * N
+            out_lines.append({"case": "q4k_gemv", "shape": [1, N, K], "us_per_call": dt * 1e6, "GBps": b / dt / 1e9, "frac_of_measured_hbm": b / dt / 1e9 / peak,
+                              "algorithmic_bytes": b, "distinct_weight_copies": copies,
+                              "note": "one call = activation digit pre-pass + GEMV kernel, graph of `copies` calls over distinct matrices"})
+            for w in ws:
+                dev.release_buffer(w.buffer)
+            dev.release_buffer(x.buffer); dev.release_buffer(out); dev.pool_trim()
+    elif args.case == "gemm":
+        M, N, K = tuple(int(v) for v in args.shape.split(",")) if args.shape else (512, 12288, 4096)
+        copies = args.copies or 4
+        ws = [dev.weight_from(synthetic.q4k_matrix(synthetic.key(5, i), N, K), "q4k", [N, K]) for i in range(copies)]
+        a = dev.tensor_from(synthetic.normal_f16(synthetic.key(5, 100), M * K).reshape(M, K))
+        out = dev.acquire_buffer(M * N * 2, "c")
+        dt = _graph_time(dev, ops, lambda rec: [ops.record_matmul(rec, a, w, M, N, K, output_dtype="f16", output_buffer=out) for w in ws],
+                         copies, max(args.steps // 8, 3))
+        fl = 2.0 * M * N * K
+        try:
+            pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            tf_burst, tf_sus = float(pk["bf16_tflops"]), float(pk["bf16_tflops_sustained"])
+        except Exception:
+            tf_burst, tf_sus = 1590.0, 1400.0
+        out_lines.append({"case": "q4k_gemm_tcgen05", "shape": [M, N, K], "us_per_call": dt * 1e6, "TFLOPs": fl / dt / 1e12,
+                          "frac_of_measured_burst": fl / dt / 1e12 / tf_burst, "frac_of_measured_sustained": fl / dt / 1e12 / tf_sus,
+                          "frac_of_nominal_2250": fl / dt / 1e12 / 2250.0, "dtype": "f16 x q4k->f16, f32 accumulate"})
+    else:
+        B, kv = tuple(int(v) for v in args.shape.split(",")) if args.shape else (32, 8192)
+        H, Hkv, D = 32, 8, 128
+        s = synthetic.key(synthetic.DEFAULT_SEED, 20)
+        q = dev.tensor_from(synthetic.normal_f16(s, B * H * D).astype(np.float32))
+        k = dev.tensor_from(synthetic.normal_f16(s + 1, B * kv * Hkv * D))
+        v = dev.tensor_from(synthetic.normal_f16(s + 2, B * kv * Hkv * D))
+        out = dev.acquire_buffer(B * H * D * 4, "o")
+        ops.run_attention(q, k, v, None, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False, batch=B, kv_batch_stride=kv * Hkv * D, output_buffer=out)
+        dt = _graph_time(dev, ops, lambda rec: [ops.record_attention(rec, q, k, v, None, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False,
+                                                                      batch=B, kv_batch_stride=kv * Hkv * D, output_buffer=out)], 1, max(args.steps // 2, 5))
+        b = 2 * B * kv * Hkv * D * 2 + B * H * D * 2 + B * H * D * 4
+        out_lines.append({"case": "decode_attention_f16kv", "shape": {"batch": B, "heads": H, "kv_heads": Hkv, "head_dim": D, "kv_len": kv},
+                          "us_per_call": dt * 1e6, "GBps": b / dt / 1e9, "frac_of_measured_hbm": b / dt / 1e9 / peak, "algorithmic_bytes": b,
+                          "note": "KV (1.07 GB at config 2) is larger than L2"})
+    for l in out_lines:
+        l["peak_source"] = peak_src
+        print(json.dumps(l), flush=True)
+    dev.close()
+
+
 # ----------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -163,6 +245,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="9b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "attention"],
+                    help="time ONE kernel of the path on a BASELINE configuration instead of the decoder "
+                         "(gemv: configs 0 and 9B shapes, gemm: config 1, attention: config 2); also the small "
+                         "command the profiler captures use")
+    ap.add_argument("--shape", default=None, help="--case gemv/gemm: N,K or M,N,K; --case attention: batch,kv_len")
+    ap.add_argument("--copies", type=int, default=0, help="--case: distinct weight copies per pass (0 = enough to exceed L2)")
+    ap.add_argument("--only-timed", action="store_true",
+                    help="stop after the device-resident timed region (used for profiler launch lists)")
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
                     help="N>1: one-shot peer-memory exchange fused into the decode kernels, or NCCL")
     args = ap.parse_args()
@@ -175,6 +265,9 @@ def main():
 
     if args.impl == "reference":
         reference_arm(args, cfg, context)
+        return
+    if args.case:
+        kernel_case(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))
@@ -234,6 +327,19 @@ def main():
     barrier()
     launches = dev.launch_count - launches0
     nxt = int(out[-1, 0])
+
+    if args.only_timed:
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tokens_per_s", "value": args.steps / (ms / 1000.0), "unit": "tokens/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                              "gpu_launches": int(launches), "note": "timed region only"}), flush=True)
+        if sampler:
+            sampler.stop()
+        model.destroy()
+        dev.close()
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the per-token C-ABI call with host buffers -------------------
     model.reset()
