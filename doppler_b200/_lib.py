@@ -113,6 +113,9 @@ SIGNATURES = {
     "dp_dequant_q4k_rowwise": (_i, [_vp, _vp, _vp, _sz, _i, _i, _i, _vp, _T]),
     "dp_attn_opts_default": (None, [C.POINTER(AttnOpts)]),
     "dp_attention": (_i, [_vp, _vp, _T, _T, _T, _i, _i, C.POINTER(AttnOpts), _T]),
+    "dp_attention_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _sz, _f]),
+    "dp_attention_decode_static_error": (C.c_char_p, []),
+    "dp_attention_decode_static_max_scratch": (_sz, []),
     "dp_rmsnorm_opts_default": (None, [C.POINTER(RmsNormOpts)]),
     "dp_rmsnorm": (_i, [_vp, _vp, _T, _T, _f, C.POINTER(RmsNormOpts), _T]),
     "dp_rmsnorm_qk": (_i, [_vp, _vp, _T, _T, _T, _T, _i, _i, _i, _f, _i]),

@@ -177,6 +177,20 @@ dp_status dp_attention(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *Q, const 
                        const dp_tensor *V, int num_heads, int head_dim, const dp_attn_opts *opts,
                        dp_tensor *out);
 
+/* Decode attention (seq_len 1, no mask) for hosts that must not allocate device memory while
+ * they run (a plugin called under someone else's stream capture, a worker that is only handed
+ * buffers and a stream, a process with a fixed allocator budget).  No counterpart in the
+ * reference.  Raw device pointers, a cudaStream_t, no context: the split-K scratch is a fixed
+ * device array inside the library (dp_attention_decode_static_max_scratch() bytes on every GPU
+ * that loads it).  Calls needing more scratch return DP_ERR_UNSUPPORTED; overlapping calls race on
+ * the array; the first call on a device resolves the array's address and should happen outside
+ * stream capture.  The message of the last failure on this thread: ..._error(). */
+dp_status dp_attention_decode_static(void *stream, const float *q, const void *k_f16, const void *v_f16, float *out,
+                                     int batch, int num_heads, int num_kv_heads, int head_dim, int kv_len,
+                                     size_t kv_batch_stride, float scale);
+const char *dp_attention_decode_static_error(void);
+size_t dp_attention_decode_static_max_scratch(void);
+
 /* ---- small ops ---------------------------------------------------------- */
 /* reference: runRMSNorm / recordRMSNorm  src/gpu/kernels/rmsnorm.js:146,224 (rmsnorm.wgsl:119-187) */
 typedef struct {
