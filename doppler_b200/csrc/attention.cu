@@ -41,15 +41,18 @@ __device__ __forceinline__ AttnRange attn_range(int kv_len, int causal, int star
   return r;
 }
 
-template <int DPL, int GT>
-__global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params p, float *__restrict__ part, int splits,
-                                                                  int head_tiles) {
+// LPK lanes share a key (each owns DPL = D/LPK dims).  More lanes per key = fewer registers per
+// thread (q and the output accumulators shrink), which is what lets two CTAs share an SM.
+template <int DPL, int GT, int LPK>
+__global__ void __launch_bounds__(ATT_THREADS, LPK == 16 ? 2 : 1) attn_split_kernel(dpk_attn_params p, float *__restrict__ part, int splits,
+                                                                                    int head_tiles) {
   pdl_launch();
   pdl_wait();
-  constexpr int D = DPL * 8;
+  constexpr int D = DPL * LPK;
+  constexpr int KEY_GROUPS = ATT_THREADS / LPK;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int sub = lane & 7;          // which D/8 slice of the key this lane owns
-  const int grp = tid >> 3;          // 8-lane group index within the CTA
+  const int sub = lane & (LPK - 1);  // which D/LPK slice of the key this lane owns
+  const int grp = tid / LPK;         // key group index within the CTA
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y % head_tiles;
   const int z = blockIdx.z, b = z / p.seq_len, qi = z % p.seq_len;
@@ -90,9 +93,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
 
   // The four 8-lane groups of a warp may run different trip counts, so the shuffles inside
   // the loop name only the lanes of their own group.
-  const unsigned gmask = 0xFFu << (lane & 24);
+  const unsigned gmask = (LPK == 16 ? 0xFFFFu : 0xFFu) << (lane & ~(LPK - 1));
 #pragma unroll 2
-  for (int key = k_begin + grp; key < k_end; key += ATT_GROUPS) {
+  for (int key = k_begin + grp; key < k_end; key += KEY_GROUPS) {
     uint4 kraw[DPL / 8], vraw[DPL / 8];
 #pragma unroll
     for (int i = 0; i < DPL / 8; i++) {
@@ -115,6 +118,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
       a += __shfl_xor_sync(gmask, a, 1);
       a += __shfl_xor_sync(gmask, a, 2);
       a += __shfl_xor_sync(gmask, a, 4);
+      if (LPK == 16) a += __shfl_xor_sync(gmask, a, 8);
       if (p.softcap > 0.0f) a = tanhf(a / p.softcap) * p.softcap;
       s[g] = a * LOG2E;
     }
@@ -141,20 +145,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
     }
   }
 
-  // merge the four 8-lane groups of each warp
+  // merge the key groups of each warp
 #pragma unroll
   for (int g = 0; g < GT; g++) {
     float mm = m[g];
-    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 8));
+    if (LPK == 8) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 8));
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
     const float c = (m[g] == -FLT_MAX) ? 0.0f : exp2f(m[g] - mm);
     float ll = l[g] * c;
-    ll += __shfl_xor_sync(0xffffffffu, ll, 8);
+    if (LPK == 8) ll += __shfl_xor_sync(0xffffffffu, ll, 8);
     ll += __shfl_xor_sync(0xffffffffu, ll, 16);
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
       float v = o[g][i] * c;
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      if (LPK == 8) v += __shfl_xor_sync(0xffffffffu, v, 8);
       v += __shfl_xor_sync(0xffffffffu, v, 16);
       o[g][i] = v;
     }
@@ -163,7 +167,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_split_kernel(dpk_attn_params
   // merge the warps through shared memory
   __shared__ float sm_o[ATT_THREADS / 32][GT][D];
   __shared__ float sm_m[ATT_THREADS / 32][GT], sm_l[ATT_THREADS / 32][GT];
-  if (lane < 8) {
+  if (lane < LPK) {
 #pragma unroll
     for (int g = 0; g < GT; g++) {
 #pragma unroll
@@ -316,12 +320,12 @@ size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *s
   return (size_t)rows * p.num_heads * splits * (p.head_dim + 2) * sizeof(float);
 }
 
-template <int DPL, int GT>
+template <int DPL, int GT, int LPK>
 static dp_status launch_fast(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits) {
   const int G = p.num_heads / p.num_kv_heads;
   const int head_tiles = G / GT;
   dim3 grid(splits, p.num_kv_heads * head_tiles, p.batch * p.seq_len);
-  DP_LAUNCH(ctx, (attn_split_kernel<DPL, GT>), grid, ATT_THREADS, 0, p, scratch, splits, head_tiles);
+  DP_LAUNCH(ctx, (attn_split_kernel<DPL, GT, LPK>), grid, ATT_THREADS, 0, p, scratch, splits, head_tiles);
   return DP_OK;
 }
 
@@ -340,13 +344,13 @@ static dp_status attention_impl(dp_ctx *ctx, const dpk_attn_params &p, float *sc
   int gt = 1;
   if (fast_shape(p, &gt)) {
     if (p.head_dim == 128) {
-      if (gt == 1) DP_TRY((launch_fast<16, 1>(ctx, p, scratch, splits)));
-      else if (gt == 2) DP_TRY((launch_fast<16, 2>(ctx, p, scratch, splits)));
-      else DP_TRY((launch_fast<16, 4>(ctx, p, scratch, splits)));
+      if (gt == 1) DP_TRY((launch_fast<16, 1, 8>(ctx, p, scratch, splits)));
+      else if (gt == 2) DP_TRY((launch_fast<16, 2, 8>(ctx, p, scratch, splits)));
+      else DP_TRY((launch_fast<8, 4, 16>(ctx, p, scratch, splits)));  // 4 heads: 16 lanes per key keep it under 128 registers
     } else {
-      if (gt == 1) DP_TRY((launch_fast<8, 1>(ctx, p, scratch, splits)));
-      else if (gt == 2) DP_TRY((launch_fast<8, 2>(ctx, p, scratch, splits)));
-      else DP_TRY((launch_fast<8, 4>(ctx, p, scratch, splits)));
+      if (gt == 1) DP_TRY((launch_fast<8, 1, 8>(ctx, p, scratch, splits)));
+      else if (gt == 2) DP_TRY((launch_fast<8, 2, 8>(ctx, p, scratch, splits)));
+      else DP_TRY((launch_fast<8, 4, 8>(ctx, p, scratch, splits)));
     }
   } else {
     dim3 grid(splits, p.num_heads, p.batch * p.seq_len);

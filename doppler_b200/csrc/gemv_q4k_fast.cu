@@ -233,13 +233,29 @@ __host__ __device__ inline TgLayout tg_layout(int K, int cb, int stages) {
   return l;
 }
 
+// Where the GEMV's input vector comes from.  SRC_DIGITS: ready-made digits in global memory.  The
+// other modes let every CTA rebuild the digits itself from the previous op's f32 output while its
+// producer warp is already filling the weight ring, so the normalisation / activation / split merge
+// needs no kernel of its own (148 CTAs redo a few KB of work each; the latency hides under the
+// pipeline fill):
+//   SRC_RMSNORM  x = rmsnorm(h, w, eps)                 (rmsnorm.wgsl:119-187)
+//   SRC_SILU     x = silu(gate) * up, gate|up = gu[2K]   (silu.wgsl:98-104)
+//   SRC_COMBINE  x = merge of the split-K attention partials (layout of attention.cu)
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
+struct GemvSource {
+  const float *x;   // h (SRC_RMSNORM), gu (SRC_SILU), partials (SRC_COMBINE)
+  const float *w;   // norm weights
+  float eps;
+  int D, splits;    // SRC_COMBINE: head_dim and number of splits
+};
+
 // GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
 // while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
-template <typename OutT, int GROUPS>
-__global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
+template <typename OutT, int GROUPS, int SRC>
+__global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 ? 2 : 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
-    const float *__restrict__ residual, int *__restrict__ err) {
+    const float *__restrict__ residual, int *__restrict__ err, const GemvSource gs) {
   extern __shared__ __align__(128) uint8_t smem[];
   const TgLayout L = tg_layout(K, cb, stages);
   const int tid = threadIdx.x, lane = tid & 31, warp_all = tid >> 5;
@@ -268,13 +284,91 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
   if (group < GROUPS) {
     pdl_wait();
     constexpr int CT = GROUPS * TG_CONSUMERS * 32;  // consumer threads
-    const uint4 *src = reinterpret_cast<const uint4 *>(limbs);
-    uint4 *dst = reinterpret_cast<uint4 *>(smem);
-    const int total = K * 4 + (K / 32) * 4 + bpr * 4;
-    const int n16 = total / 16;
-    for (int i = tid; i < n16; i += CT) dst[i] = __ldg(src + i);
-    const int rem_words = (total - n16 * 16) / 4;
-    if (tid < rem_words) reinterpret_cast<uint32_t *>(smem)[n16 * 4 + tid] = __ldg(reinterpret_cast<const uint32_t *>(limbs) + n16 * 4 + tid);
+    constexpr int NW = CT / 32;
+    const int cw = tid >> 5;
+    if constexpr (SRC == SRC_DIGITS) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(limbs);
+      uint4 *dst = reinterpret_cast<uint4 *>(smem);
+      const int total = K * 4 + (K / 32) * 4 + bpr * 4;
+      const int n16 = total / 16;
+      for (int i = tid; i < n16; i += CT) dst[i] = __ldg(src + i);
+      const int rem_words = (total - n16 * 16) / 4;
+      if (tid < rem_words) reinterpret_cast<uint32_t *>(smem)[n16 * 4 + tid] = __ldg(reinterpret_cast<const uint32_t *>(limbs) + n16 * 4 + tid);
+    } else if constexpr (SRC == SRC_RMSNORM) {
+      float *scratch = reinterpret_cast<float *>(smem + L.red);  // free until the first tile is reduced
+      float v[2][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int b = cw + NW * i;
+        if (b < bpr) {
+          const float4 a = *reinterpret_cast<const float4 *>(gs.x + b * QK_K + lane * 8);
+          const float4 c = *reinterpret_cast<const float4 *>(gs.x + b * QK_K + lane * 8 + 4);
+          v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+#pragma unroll
+          for (int j = 0; j < 8; j++) ss = fmaf(v[i][j], v[i][j], ss);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) scratch[cw] = ss;
+      asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
+      float total = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NW; i++) total += scratch[i];
+      const float inv_rms = 1.0f / sqrtf(total / (float)K + gs.eps);
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int b = cw + NW * i;
+        if (b < bpr) {
+          const float4 wa = *reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8);
+          const float4 wc = *reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8 + 4);
+          const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) o[j] = v[i][j] * inv_rms * wv[j];
+          actq_emit_block(o, lane, b, bpr, smem);
+        }
+      }
+    } else if constexpr (SRC == SRC_SILU) {
+      for (int b = cw; b < bpr; b += NW) {
+        const float *gp = gs.x + b * QK_K + lane * 8, *up = gs.x + K + b * QK_K + lane * 8;
+        const float4 g0 = *reinterpret_cast<const float4 *>(gp), g1 = *reinterpret_cast<const float4 *>(gp + 4);
+        const float4 u0 = *reinterpret_cast<const float4 *>(up), u1 = *reinterpret_cast<const float4 *>(up + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float cl = fminf(fmaxf(g[j], -15.0f), 15.0f);
+          o[j] = (g[j] * (1.0f / (1.0f + expf(-cl)))) * u[j];
+        }
+        actq_emit_block(o, lane, b, bpr, smem);
+      }
+    } else {
+      const int D = gs.D, splits = gs.splits;
+      for (int b = cw; b < bpr; b += NW) {
+        const int e0 = b * QK_K + lane * 8, h = e0 / D, d0 = e0 % D;
+        const float *pp = gs.x + (size_t)h * splits * (D + 2);
+        float mm = -3.402823466e+38f;
+        for (int sp = 0; sp < splits; sp++) mm = fmaxf(mm, pp[sp * (D + 2) + D]);
+        float ll = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 2
+        for (int sp = 0; sp < splits; sp++) {
+          const float *ps = pp + sp * (D + 2);
+          const float ms = ps[D];
+          const float c = (ms == -3.402823466e+38f) ? 0.0f : exp2f(ms - mm);
+          ll = fmaf(ps[D + 1], c, ll);
+          const float2 a0 = *reinterpret_cast<const float2 *>(ps + d0), a1 = *reinterpret_cast<const float2 *>(ps + d0 + 2);
+          const float2 a2 = *reinterpret_cast<const float2 *>(ps + d0 + 4), a3 = *reinterpret_cast<const float2 *>(ps + d0 + 6);
+          acc[0] = fmaf(a0.x, c, acc[0]); acc[1] = fmaf(a0.y, c, acc[1]); acc[2] = fmaf(a1.x, c, acc[2]); acc[3] = fmaf(a1.y, c, acc[3]);
+          acc[4] = fmaf(a2.x, c, acc[4]); acc[5] = fmaf(a2.y, c, acc[5]); acc[6] = fmaf(a3.x, c, acc[6]); acc[7] = fmaf(a3.y, c, acc[7]);
+        }
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[j] = ll > 0.0f ? acc[j] / ll : 0.0f;
+        actq_emit_block(o, lane, b, bpr, smem);
+      }
+    }
     asm volatile("bar.sync 1, %0;" ::"r"(CT) : "memory");
   }
 
@@ -412,7 +506,10 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   for (int c = bpr; c >= 1; c--)
     if (bpr % c == 0 && 16 * (c * Q4K_BLOCK_BYTES + TG_ROW_PAD) <= limit) { cb = c; break; }
   if (cb == 0) return false;
-  const size_t budget = ctx->smem_optin < 227 * 1024 ? ctx->smem_optin : 227 * 1024;
+  static int budget_kb = -1;
+  if (budget_kb < 0) { const char *e = getenv("DP_GEMV_SMEM_KB"); budget_kb = e ? atoi(e) : 227; }
+  size_t budget = (size_t)budget_kb * 1024;
+  if (budget > ctx->smem_optin) budget = ctx->smem_optin;
   int stages = 8;
   while (stages >= 2 && tg_layout(K, cb, stages).total > budget) stages--;
   if (stages < 2) return false;
@@ -420,19 +517,19 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   return true;
 }
 
-template <typename OutT, int GROUPS>
+template <typename OutT, int GROUPS, int SRC>
 static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
-                            uint32_t smem, float alpha, const float *residual) {
-  const float *xscale = (const float *)(limbs + (size_t)K * 4);
-  const float *ssum = xscale + K / QK_K;
+                            uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
+  const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
+  const float *ssum = limbs ? xscale + K / QK_K : nullptr;
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
-            N, K, cb, stages, alpha, residual, ctx->dev_status);
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+            N, K, cb, stages, alpha, residual, ctx->dev_status, gs);
   return DP_OK;
 }
 
@@ -455,13 +552,41 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
   const int variant = gemv_variant();
   if (variant == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
   const int8_t *limbs = (const int8_t *)actq;
+  GemvSource gs{};
   if (y_dtype == DP_F32) {
-    if (variant == 1) DP_TRY((launch_tma<float, 1>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
-    else if (variant == 3) DP_TRY((launch_tma<float, 3>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
-    else DP_TRY((launch_tma<float, 2>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual)));
+    if (variant == 1) DP_TRY((launch_tma<float, 1, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
+    else if (variant == 3) DP_TRY((launch_tma<float, 3, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
+    else DP_TRY((launch_tma<float, 2, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
   } else {
-    if (variant == 1) DP_TRY((launch_tma<__half, 1>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual)));
-    else DP_TRY((launch_tma<__half, 2>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual)));
+    if (variant == 1) DP_TRY((launch_tma<__half, 1, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
+    else DP_TRY((launch_tma<__half, 2, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
+  }
+  *handled = true;
+  return DP_OK;
+}
+
+// f32 GEMV whose input is produced inside the kernel (mode = SRC_RMSNORM / SRC_SILU / SRC_COMBINE).
+// Returns handled = false when the shape has no TMA plan (the caller then runs the separate kernels).
+dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
+                                 int splits, float *y, int N, int K, const float *residual, bool *handled) {
+  *handled = false;
+  int cb, stages;
+  uint32_t smem;
+  if (gemv_variant() == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
+  if (K > 16 * 2 * QK_K && mode == SRC_RMSNORM) return DP_OK;  // the norm keeps two blocks per warp in registers
+  GemvSource gs{};
+  gs.x = x; gs.w = w; gs.eps = eps; gs.D = D; gs.splits = splits;
+  if (gemv_variant() == 1) {
+    if (K > 8 * 2 * QK_K && mode == SRC_RMSNORM) return DP_OK;
+    if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 1, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 1, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 1, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else return DP_OK;
+  } else {
+    if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+    else return DP_OK;
   }
   *handled = true;
   return DP_OK;

@@ -21,6 +21,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -34,6 +35,8 @@ dp_status dpk_gemv_q4k_actq(dp_ctx *ctx, const uint8_t *W, const void *actq, voi
 dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq, void *y, dp_dtype y_dtype, int N, int K,
                                 float alpha, const float *residual, bool *handled);
 size_t dpk_q4k_actq_bytes(int K);
+dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
+                                 int splits, float *y, int N, int K, const float *residual, bool *handled);
 bool dpk_gemv_q4k_fast_ok(int N, int K);
 dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
@@ -639,43 +642,56 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   return DP_OK;
 }
 
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
+
 // One pass over `tokens` rows already gathered in m->h.  decode: rows are
 // sequences (positions from the device arrays); prefill: rows are consecutive
 // positions of sequence `seq` starting at start_pos.
+//
+// Single-token decode takes the fused schedule: each Q4_K GEMV kernel rebuilds its own input
+// (RMSNorm, SiLU*up or the split-K merge) while its weight ring fills, so a layer is six kernels:
+//   GEMV qkv [rmsnorm]  ->  qk-norm + rope + KV append  ->  attention split
+//   -> GEMV o [split merge] + residual  ->  GEMV gate|up [rmsnorm]  ->  GEMV down [silu*up] + residual
 static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
   dp_ctx *ctx = m->ctx;
   const dp_model_cfg &c = m->cfg;
   const int H = c.hidden, D = c.head_dim, p = c.tp_size;
   const size_t kv_seq_stride = (size_t)c.max_seq * m->kvdim;
   const int heads = m->nh + 2 * m->nkv;
+  const bool single = decode && tokens == 1;
   // tensor-parallel single-token decode with the one-shot exchange: the kernel that sums the
   // partial vectors also applies the residual and the NEXT RMSNorm (and emits its digits)
-  const bool fused_ar = decode && tokens == 1 && p > 1 && m->allreduce_mode == 1 && dp_tp_exchange_desc(ctx) != nullptr;
+  const bool fused_ar = single && p > 1 && m->allreduce_mode == 1 && dp_tp_exchange_desc(ctx) != nullptr;
   bool n_ready = false;  // m->n / digits already hold rmsnorm(h, in_norm of this layer)
   for (int l = 0; l < c.n_layers; l++) {
     LayerW &L = m->layers[l];
-    // single-token decode: the producers of a GEMV's input also emit its fixed-point digits
-    const bool fuse = decode && tokens == 1 && H % QK_K == 0 && H <= 8192;
-    const bool fuse_qkv = fuse && dpk_gemv_q4k_fast_ok(m->qdim + 2 * m->kvdim, H);
-    const bool fuse_gu = fuse && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
-    const bool fuse_o = fuse && dpk_gemv_q4k_fast_ok(H, m->qdim) && m->attn_splits_decode > 1 && D % 8 == 0;
-    const bool fuse_down = fuse && dpk_gemv_q4k_fast_ok(H, m->inter);
-    bool dq_qkv = fuse_qkv;  // digits of rmsnorm(h) are in m->actq
-    if (n_ready) {
+    const int nqkv = m->qdim + 2 * m->kvdim;
+    // ---- q, k, v ----
+    bool done = false;
+    if (n_ready) {  // written by the exchange kernel of the previous layer
       n_ready = false;
-      dq_qkv = true;
-    } else if (fuse_qkv) {
-      DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.in_norm, m->n, m->actq->dptr, H, c.eps);
-    } else {
-      DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, true));
+      done = true;
+    } else if (single) {
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.qkv->dptr, SRC_RMSNORM, m->h, L.in_norm, c.eps, 0, 0, m->qkv, nqkv, H, nullptr, &done));
     }
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, m->qdim + 2 * m->kvdim, H, nullptr, dq_qkv));
+    if (!done) {
+      const bool emit = single && H % QK_K == 0 && H <= 8192 && dpk_gemv_q4k_fast_ok(nqkv, H);
+      if (emit) {
+        DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.in_norm, m->n, m->actq->dptr, H, c.eps);
+      } else {
+        DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+      }
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, emit));
+    }
+    // ---- per-head QK norm, RoPE, KV append ----
     {
       const int warps = tokens * heads;
       DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
                 (__half *)m->vc[l]->dptr, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin, decode ? m->d_pos : nullptr,
                 start_pos, seq, tokens, m->nh, m->nkv, D, c.eps, kv_seq_stride);
     }
+    // ---- attention ----
     dpk_attn_params ap{};
     ap.q = m->q; ap.out = m->att;
     ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
@@ -693,47 +709,79 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       ap.kv_batch_stride = 0; ap.kv_lens = nullptr;
       splits = 1;
     }
-    if (fuse_o) {
+    float *o_dst = p == 1 ? m->h : m->partial;
+    const float *o_res = p == 1 ? m->h : nullptr;
+    done = false;
+    const bool split_merge_ok = single && splits > 1 && D % 8 == 0 && m->qdim % QK_K == 0;
+    if (split_merge_ok) {
       DP_TRY(dpk_attention_split_only(ctx, ap, (float *)m->attn_scratch->dptr, splits));
-      const int blocks = m->qdim / QK_K;
-      DP_LAUNCH(ctx, attn_combine_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->attn_scratch->dptr, m->att,
-                m->actq->dptr, m->nh, D, splits);
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.o->dptr, SRC_COMBINE, (const float *)m->attn_scratch->dptr, nullptr, 0.0f, D,
+                                    splits, o_dst, H, m->qdim, o_res, &done));
+      if (!done) {
+        const bool emit = dpk_gemv_q4k_fast_ok(H, m->qdim);
+        const int blocks = m->qdim / QK_K;
+        if (emit) {
+          DP_LAUNCH(ctx, attn_combine_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->attn_scratch->dptr, m->att,
+                    m->actq->dptr, m->nh, D, splits);
+          DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, o_dst, tokens, H, m->qdim, o_res, true));
+          done = true;
+        }
+      }
+      if (!done) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: split attention without a merge path");
     } else {
       DP_TRY(dpk_attention_with_scratch(ctx, ap, (float *)m->attn_scratch->dptr, splits));
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, o_dst, tokens, H, m->qdim, o_res));
     }
-    if (p == 1) {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->h, tokens, H, m->qdim, m->h, fuse_o));
-    } else {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, tokens, H, m->qdim, nullptr, fuse_o));
+    // ---- exchange after o_proj (tensor parallel) and the post-attention norm ----
+    bool gu_digits = false;  // digits of rmsnorm(h, post_norm) already in m->actq
+    if (p > 1) {
       if (fused_ar) {
         DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h,
                   (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps, ctx->dev_status);
+        gu_digits = true;
       } else {
         DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
         DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
       }
     }
-    if (fused_ar) {
-      // m->n and the digits were written by the exchange kernel
-    } else if (fuse_gu) {
-      DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps);
-    } else {
-      DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+    // ---- gate | up ----
+    done = false;
+    if (gu_digits) {
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, true));
+      done = true;
+    } else if (single) {
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
+                                    nullptr, &done));
     }
-    DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, fuse_gu || fused_ar));
-    if (fuse_down) {
-      const int blocks = m->inter / QK_K;
-      DP_LAUNCH(ctx, silu_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->gu, m->actv, m->actq->dptr, m->inter);
-    } else {
-      const size_t total = (size_t)tokens * m->inter;
-      size_t grid = (total + 255) / 256;
-      if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
-      DP_LAUNCH(ctx, silu_gateup_kernel, (unsigned)grid, 256, 0, m->gu, m->actv, tokens, m->inter);
+    if (!done) {
+      const bool emit = single && H % QK_K == 0 && H <= 8192 && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
+      if (emit) {
+        DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps);
+      } else {
+        DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
+      }
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, emit));
     }
-    if (p == 1) {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->h, tokens, H, m->inter, m->h, fuse_down));
-    } else {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, tokens, H, m->inter, nullptr, fuse_down));
+    // ---- silu(gate) * up, down ----
+    float *d_dst = p == 1 ? m->h : m->partial;
+    const float *d_res = p == 1 ? m->h : nullptr;
+    done = false;
+    if (single && m->inter % QK_K == 0)
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
+    if (!done) {
+      const bool emit = single && m->inter % QK_K == 0 && dpk_gemv_q4k_fast_ok(H, m->inter);
+      if (emit) {
+        const int blocks = m->inter / QK_K;
+        DP_LAUNCH(ctx, silu_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->gu, m->actv, m->actq->dptr, m->inter);
+      } else {
+        const size_t total = (size_t)tokens * m->inter;
+        size_t grid = (total + 255) / 256;
+        if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
+        DP_LAUNCH(ctx, silu_gateup_kernel, (unsigned)grid, 256, 0, m->gu, m->actv, tokens, m->inter);
+      }
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, d_dst, tokens, H, m->inter, d_res, emit));
+    }
+    if (p > 1) {
       if (fused_ar) {
         const float *next_w = l + 1 < c.n_layers ? m->layers[l + 1].in_norm : m->final_norm;
         DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h, next_w,
@@ -832,7 +880,7 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
     if (m->graph[slot]) { dp_graph_destroy(m->graph[slot]); m->graph[slot] = nullptr; }
     dp_recorder *rec = nullptr;
     DP_TRY(dp_recorder_begin(ctx, "decode_step", 1, &rec));
-    ctx->pdl = true;  // kernels of the step overlap their launch with the predecessor's tail
+    ctx->pdl = getenv("DP_PDL") ? atoi(getenv("DP_PDL")) != 0 : true;  // kernels of the step overlap their launch with the predecessor's tail
     dp_status s = record_decode_step(m, batch);
     ctx->pdl = false;
     if (s != DP_OK) { std::string keep = ctx->err; dp_recorder_abort(rec); ctx->err = keep; return s; }
