@@ -16,6 +16,7 @@
 #include "pdl.cuh"
 
 #include <cfloat>
+#include <cstdlib>
 
 #define ATT_THREADS 256
 #define ATT_GROUPS (ATT_THREADS / 8)
@@ -301,8 +302,41 @@ static bool fast_shape(const dpk_attn_params &p, int *gt) {
   return false;
 }
 
+// tensor-core decode kernel (attention_tc.cu)
+bool dpk_attention_tc_eligible(const dpk_attn_params &p, int *gt_out);
+dp_status dpk_attention_tc_split(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);
+
+// The tensor-core kernel pays a pipeline ramp per CTA, so it takes over once every SM has a few
+// hundred keys to stream; below that the CUDA-core kernel's finer split wins.
+static bool use_tc(dp_ctx *ctx, const dpk_attn_params &p, int *gt) {
+  static const int mode = [] { const char *e = getenv("DP_ATTN_TC"); return e ? atoi(e) : 1; }();
+  if (!mode || !dpk_attention_tc_eligible(p, gt)) return false;
+  return mode == 2 || (long)p.batch * p.num_kv_heads * p.kv_len >= (long)ctx->sm_count * 256;
+}
+
+// splits for the tensor-core kernel: fewest whole waves of (two CTAs per SM) x keys per CTA
+static int tc_splits(dp_ctx *ctx, const dpk_attn_params &p, int gt) {
+  const int G = p.num_heads / p.num_kv_heads;
+  const long base = (long)p.batch * p.num_kv_heads * (G / gt);
+  const long slots = (long)ctx->sm_count * 2;
+  long best = 1, best_cost = -1;
+  for (long s = 1; s <= 32; s++) {
+    const long keys = (p.kv_len + s - 1) / s;
+    if (s > 1 && keys < 128) break;
+    const long waves = (base * s + slots - 1) / slots;
+    const long cost = waves * (keys + 64);
+    if (best_cost < 0 || cost < best_cost) { best = s; best_cost = cost; }
+  }
+  return (int)best;
+}
+
 size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *splits_out) {
   int gt = 1;
+  if (use_tc(ctx, p, &gt)) {
+    const int s = tc_splits(ctx, p, gt);
+    *splits_out = s;
+    return s == 1 ? 0 : (size_t)p.batch * p.num_heads * s * (p.head_dim + 2) * sizeof(float);
+  }
   const bool fast = fast_shape(p, &gt);
   const int G = p.num_heads / p.num_kv_heads;
   const long rows = (long)p.batch * p.seq_len;
@@ -342,7 +376,9 @@ dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float 
 
 static dp_status attention_impl(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits, bool combine) {
   int gt = 1;
-  if (fast_shape(p, &gt)) {
+  if (use_tc(ctx, p, &gt)) {
+    DP_TRY(dpk_attention_tc_split(ctx, p, scratch, splits));
+  } else if (fast_shape(p, &gt)) {
     if (p.head_dim == 128) {
       if (gt == 1) DP_TRY((launch_fast<16, 1, 8>(ctx, p, scratch, splits)));
       else if (gt == 2) DP_TRY((launch_fast<16, 2, 8>(ctx, p, scratch, splits)));

@@ -64,6 +64,63 @@ def test_config2_batch(dev):
     assert np.abs(got).max() <= vmax
 
 
+def _np_attention(q, k16, v16, H, Hkv, D, lo, hi, scale, softcap=0.0):
+    """Plain float64 restatement for options the C oracle does not take (softcap, key windows)."""
+    q = q.reshape(H, D).astype(np.float64)
+    k = k16.reshape(-1, Hkv, D)[lo:hi].astype(np.float64)
+    v = v16.reshape(-1, Hkv, D)[lo:hi].astype(np.float64)
+    out = np.zeros((H, D))
+    for h in range(H):
+        s = k[:, h // (H // Hkv), :] @ q[h] * scale
+        if softcap > 0:
+            s = np.tanh(s / softcap) * softcap
+        pr = np.exp(s - s.max())
+        out[h] = (pr / pr.sum()) @ v[:, h // (H // Hkv), :]
+    return out.ravel()
+
+
+# Shapes large enough (batch x KV heads x keys) to take the tensor-core decode kernel: GQA groups
+# of 1, 3, 4, 8 and 16 heads, both head dims, ragged key counts, several sequences.
+@pytest.mark.parametrize("B,H,Hkv,D,kv", [(4, 32, 4, 128, 2500), (8, 8, 8, 64, 777), (2, 64, 4, 128, 5001),
+                                          (4, 12, 4, 64, 2400), (5, 16, 4, 128, 2047)])
+def test_tensor_core_decode_shapes(dev, B, H, Hkv, D, kv):
+    s = synthetic.key(55, B * 100000 + H * 1000 + kv)
+    q = synthetic.normal_f32(s, B * H * D)
+    n = kv * Hkv * D
+    k16, v16 = synthetic.normal_f16(s + 1, B * n), synthetic.normal_f16(s + 2, B * n)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False, batch=B,
+                kv_batch_stride=n).reshape(B, H * D)
+    for b in range(B):
+        exp = O.attention_f16kv(q[b * H * D:(b + 1) * H * D], k16[b * n:(b + 1) * n], v16[b * n:(b + 1) * n], 1, kv, H, Hkv, D,
+                                causal=False)
+        assert_close(got[b], exp, f"tensor-core decode B{B}/H{H}/Hkv{Hkv}/D{D}/kv{kv} sequence {b}")
+
+
+def test_tensor_core_decode_options(dev):
+    """softcap, sliding window and per-sequence lengths on a shape the tensor-core kernel takes"""
+    B, H, Hkv, D, kv = 3, 32, 8, 128, 3000
+    s = synthetic.key(56, 0)
+    q = synthetic.normal_f32(s, B * H * D) * 3.0
+    n = kv * Hkv * D
+    k16, v16 = synthetic.normal_f16(s + 1, B * n), synthetic.normal_f16(s + 2, B * n)
+    scale = 1.0 / np.sqrt(D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, start_pos=kv - 1, sliding_window=1001,
+                attn_softcap=5.0, batch=B, kv_batch_stride=n).reshape(B, H * D)
+    for b in range(B):
+        exp = _np_attention(q[b * H * D:(b + 1) * H * D], k16[b * n:(b + 1) * n], v16[b * n:(b + 1) * n], H, Hkv, D, kv - 1001, kv,
+                            scale, softcap=5.0)
+        assert_close(got[b], exp.astype(np.float32), f"softcap + sliding window, sequence {b}")
+    lens_np = np.array([3000, 1, 1777], np.int32)
+    lens = dev.tensor_from(lens_np)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=1, kv_len=kv, num_kv_heads=Hkv, causal=False, batch=B, kv_batch_stride=n,
+                kv_len_buffer=lens.buffer).reshape(B, H * D)
+    for b in range(B):
+        exp = O.attention_f16kv(q[b * H * D:(b + 1) * H * D], k16[b * n:(b + 1) * n], v16[b * n:(b + 1) * n], 1, int(lens_np[b]), H,
+                                Hkv, D, causal=False)
+        assert_close(got[b], exp, f"per-sequence kv length {lens_np[b]}")
+    dev.release_buffer(lens.buffer)
+
+
 def test_kv_len_zero_and_kv_len_buffer(dev):
     H, Hkv, D, kv = 8, 2, 128, 512
     s = synthetic.key(52, 0)
