@@ -33,7 +33,10 @@
 
 namespace {
 
-constexpr int BM = 256, BK = 64, TC_STAGES = 3;
+constexpr int BM = 256, BK = 64;
+// The activation ring (filled by TMA) and the weight ring (filled by the dequant warps) have their own
+// depths and barriers: weight stages are smaller, so more of them fit, and the dequant warps can run
+// further ahead of the tensor core than the TMA needs to.
 // warp 0: TMA, warp 1: MMA issue, warps 2 .. 2+DQ_WARPS-1: dequant + epilogue (DQ_WARPS % 4 == 0)
 
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -82,26 +85,26 @@ struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
 };
-__host__ __device__ inline TcSmem tc_layout(int BN) {
+__host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB) {
   TcSmem l;
   l.stage_a = 2u * 128u * 128u;      // two 128-row tiles of 64 f16
   l.stage_b = (uint32_t)BN * 128u;
   l.a = 0;
-  l.b = TC_STAGES * l.stage_a;
-  l.bars = l.b + TC_STAGES * l.stage_b;  // full_a[S], full_b[S], empty[S], accum
-  l.tmem_slot = l.bars + (3 * TC_STAGES + 1) * 8;
+  l.b = (uint32_t)SA * l.stage_a;
+  l.bars = l.b + (uint32_t)SB * l.stage_b;  // full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], accum
+  l.tmem_slot = l.bars + (2 * SA + 2 * SB + 1) * 8;
   l.abort_flag = l.tmem_slot + 8;
   l.total = l.abort_flag + 8;
   return l;
 }
 
-template <int BN, int DQ_WARPS, typename OutT>
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, float alpha, int *__restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(BN);
+  const TcSmem L = tc_layout(BN, SA, SB);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int bpr = K / QK_K, num_k = K / BK;
@@ -109,15 +112,17 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
   auto full_a = [&](int s) { return bars + 8u * (uint32_t)s; };
-  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(TC_STAGES + s); };
-  auto empty = [&](int s) { return bars + 8u * (uint32_t)(2 * TC_STAGES + s); };
-  const uint32_t accum_bar = bars + 8u * (uint32_t)(3 * TC_STAGES);
+  auto empty_a = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
+  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + s); };
+  auto empty_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + SB + s); };
+  const uint32_t accum_bar = bars + 8u * (uint32_t)(2 * SA + 2 * SB);
   constexpr uint32_t TMEM_COLS = 512;  // two accumulators of BN columns, rounded up to a power of two
 
   pdl_launch();
   pdl_wait();
   if (tid == 0) {
-    for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_a(s), 1); mbar_init(full_b(s), DQ_WARPS); mbar_init(empty(s), 1); }
+    for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
+    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), DQ_WARPS); mbar_init(empty_b(s), 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -135,9 +140,9 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     // ---------------- activation tiles: TMA ----------------
     if (lane == 0) {
       for (int kt = 0; kt < num_k; kt++) {
-        const int s = kt % TC_STAGES;
-        const uint32_t n = (uint32_t)(kt / TC_STAGES);
-        if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) break;
+        const int s = kt % SA;
+        const uint32_t n = (uint32_t)(kt / SA);
+        if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
         mbar_expect_tx(full_a(s), L.stage_a);
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
         tma_load_2d(dst, &tmap_a, kt * BK, m0, full_a(s));
@@ -150,12 +155,12 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       const uint32_t idesc = umma_idesc_f16(128, BN);
       bool ok = true;
       for (int kt = 0; kt < num_k && ok; kt++) {
-        const int s = kt % TC_STAGES;
-        const uint32_t n = (uint32_t)(kt / TC_STAGES);
-        if (!mbar_wait_bounded(full_a(s), n & 1u, abort_flag) || !mbar_wait_bounded(full_b(s), n & 1u, abort_flag)) { ok = false; break; }
+        const int sa = kt % SA, sb = kt % SB;
+        if (!mbar_wait_bounded(full_a(sa), (uint32_t)(kt / SA) & 1u, abort_flag) ||
+            !mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
-        const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)s * L.stage_b);
+        const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)sa * L.stage_a);
+        const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)sb * L.stage_b);
 #pragma unroll
         for (int k16 = 0; k16 < BK / 16; k16++) {
           const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
@@ -163,7 +168,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           umma_f16(tmem_base, umma_desc_sw128(a_addr + (uint32_t)k16 * 32u), bdesc, idesc, acc);
           umma_f16(tmem_base + (uint32_t)BN, umma_desc_sw128(a_addr + 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
-        umma_commit(empty(s));  // the stage is free once these MMAs have read it
+        umma_commit(empty_a(sa));  // both stages are free once these MMAs have read them
+        umma_commit(empty_b(sb));
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -186,18 +192,22 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(rowp[j] + 4 + 8 * c) + oct);
     }
     for (int kb = 0; kb < bpr && ok; kb++) {
-      // rotate the prefetch buffers and decode the block headers once for the four K steps
-      float sc_f[RG][8], mn_f[RG][8];
+      // rotate the prefetch buffers; decode the block header once for the four K steps.  The four
+      // lanes that share a weight row (oct = 0..3) split the work: lane oct decodes sub-blocks 2*oct and
+      // 2*oct+1, K step c then takes its two (scale, min) pairs from lane oct == c by shuffle.
+      float my_sc0[RG], my_sc1[RG], my_mn0[RG], my_mn1[RG];
       uint2 qcur[RG][4];
 #pragma unroll
       for (int j = 0; j < RG; j++) {
         const float2 dd = q4k_d_dmin(hdr[j].x);
         const Q4KScales sc = q4k_unpack_scales(hdr[j].y, hdr[j].z, hdr[j].w);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          sc_f[j][i] = __fmul_rn(dd.x, q4k_u8_to_float(q4k_sc(sc, i)));
-          mn_f[j][i] = __fmul_rn(dd.y, q4k_u8_to_float(q4k_mn(sc, i)));
-        }
+        const uint32_t sh = (uint32_t)(oct & 1) * 16u;
+        const uint32_t scp = ((oct < 2 ? sc.sc03 : sc.sc47) >> sh) & 0xffffu;
+        const uint32_t mnp = ((oct < 2 ? sc.mn03 : sc.mn47) >> sh) & 0xffffu;
+        my_sc0[j] = __fmul_rn(dd.x, q4k_u8_to_float(scp & 0xffu));
+        my_sc1[j] = __fmul_rn(dd.x, q4k_u8_to_float(scp >> 8));
+        my_mn0[j] = __fmul_rn(dd.y, q4k_u8_to_float(mnp & 0xffu));
+        my_mn1[j] = __fmul_rn(dd.y, q4k_u8_to_float(mnp >> 8));
 #pragma unroll
         for (int c = 0; c < 4; c++) qcur[j][c] = qn[j][c];
       }
@@ -213,14 +223,18 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
 #pragma unroll
       for (int chunk = 0; chunk < 4; chunk++) {
         const int kt = kb * 4 + chunk;
-        const int s = kt % TC_STAGES;
-        const uint32_t n = (uint32_t)(kt / TC_STAGES);
-        if (n > 0 && !mbar_wait_bounded(empty(s), (n - 1) & 1u, abort_flag)) { ok = false; break; }
+        const int s = kt % SB;
+        const uint32_t n = (uint32_t)(kt / SB);
+        bool stage_free = true;
+        if (n > 0) stage_free = mbar_wait_bounded(empty_b(s), (n - 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }  // leave together: the shuffles below name every lane
         uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
+        const int src_lane = (chunk << 3) | r8;
 #pragma unroll
         for (int j = 0; j < RG; j++) {
           const uint2 q = qcur[j][chunk];
-          const float s_lo = sc_f[j][2 * chunk], m_lo = mn_f[j][2 * chunk], s_hi = sc_f[j][2 * chunk + 1], m_hi = mn_f[j][2 * chunk + 1];
+          const float s_lo = __shfl_sync(0xffffffffu, my_sc0[j], src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1[j], src_lane);
+          const float m_lo = __shfl_sync(0xffffffffu, my_mn0[j], src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1[j], src_lane);
           // nibble -> f32 without the conversion pipe: PRMT builds the float 2^23 + q from a byte
           uint32_t lo[4], hi[4];
 #pragma unroll
@@ -248,7 +262,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       }
     }
     // ---------------- epilogue: tensor memory -> registers -> C ----------------
-    if (ok && mbar_wait_bounded(accum_bar, 0u, abort_flag)) {
+    const bool accum_ready = ok && mbar_wait_bounded(accum_bar, 0u, abort_flag);
+    if (__all_sync(0xffffffffu, accum_ready)) {  // tcgen05.ld is warp-wide: enter together or not at all
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int quad = warp & 3;         // the 32 TMEM lanes this warp may read
       const int half = dw >> 2;          // DQ_WARPS/4 warps share a quarter and split the column groups
@@ -318,25 +333,25 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
-template <int BN, int DQ_WARPS, typename OutT>
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
-  const size_t smem = tc_layout(BN).total + 1024;
-  static bool attr = false;
-  if (!attr) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  const size_t smem = tc_layout(BN, SA, SB).total + 1024;
+  static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
+  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(N / BN, (M + BM - 1) / BM);
-  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
   return DP_OK;
 }
 
 template <typename OutT>
 dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
-  static int wide = -1;
-  if (wide < 0) { const char *e = getenv("DP_GEMM_DQ_WIDE"); wide = e ? atoi(e) : 0; }
-  if (bn == 192) return wide ? launch_tc<192, 24, OutT>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT>(ctx, tm, W, C, M, N, K, alpha);
-  return wide ? launch_tc<128, 16, OutT>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT>(ctx, tm, W, C, M, N, K, alpha);
+  // Equal depths (3 + 3) measured fastest on the 512 x 12288 x 4096 case: 65.1 us against 69.7 us with a
+  // five-deep weight ring, whose extra 50 KB of shared memory come out of the L1 the weight loads use.
+  // DP_GEMM_RINGS=1 selects the deeper weight ring.
+  static int rings = -1;
+  if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
+  if (bn == 192) return rings ? launch_tc<192, 12, OutT, 3, 5>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  return rings ? launch_tc<128, 8, OutT, 4, 6>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
 }
 
 }  // namespace
