@@ -58,6 +58,10 @@ class RmsNormOpts(C.Structure):
                 ("output_scale", C.c_float), ("out_buf", C.c_void_p)]
 
 
+class FfnOpts(C.Structure):
+    _fields_ = [("batch_size", C.c_int), ("alpha", C.c_float), ("swiglu_limit", C.c_float), ("out_buf", C.c_void_p)]
+
+
 class RopeOpts(C.Structure):
     _fields_ = [("num_heads", C.c_int), ("head_dim", C.c_int), ("rotary_dim", C.c_int), ("pair_span_dim", C.c_int),
                 ("interleaved", C.c_int), ("start_pos", C.c_int)]
@@ -126,6 +130,12 @@ SIGNATURES = {
     "dp_gather_f16": (_i, [_vp, _vp, _T, _T, _i, _i, _vp, _T]),
     "dp_kv_write_f32_to_f16": (_i, [_vp, _vp, _T, _vp, _sz, _sz]),
     "dp_argmax": (_i, [_vp, _vp, _T, _i, _i, _vp, _i]),
+    "dp_quantize_q4k": (_i, [_vp, _vp, _T, C.c_int64, C.c_int64, _i, _vp, C.POINTER(WeightS)]),
+    "dp_ffn_opts_default": (None, [C.POINTER(FfnOpts)]),
+    "dp_fused_ffn": (_i, [_vp, _vp, _T, C.POINTER(WeightS), C.POINTER(WeightS), _i, _i, C.POINTER(FfnOpts), _T]),
+    "dp_matmul_residual": (_i, [_vp, _vp, _T, C.POINTER(WeightS), _T, _i, _i, _f, _vp, _T]),
+    "dp_matmul_rmsnorm": (_i, [_vp, _vp, _T, C.POINTER(WeightS), _T, _i, _i, _f, _T, _i, _vp, _T]),
+    "dp_lm_head_argmax": (_i, [_vp, _vp, _T, C.POINTER(WeightS), _i, _i, _i, _vp, _i]),
     "dp_kv_cache_create": (_i, [_vp, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "dp_kv_cache_destroy": (None, [_vp]),
     "dp_kv_layer": (_i, [_vp, _i, C.POINTER(_vp), C.POINTER(_vp)]),

@@ -390,6 +390,206 @@ extern "C" dp_status dp_argmax(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *l
   return DP_OK;
 }
 
+// ---- quantizer -----------------------------------------------------------------------------
+dp_status dpk_quantize_q4k(dp_ctx *ctx, const float *data, uint8_t *out, size_t rows, size_t cols, bool full_pad);
+
+extern "C" dp_status dp_quantize_q4k(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *src, int64_t rows, int64_t cols, int full_pad,
+                                     dp_buf out_buf, dp_weight *out) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  DP_CHECK(ctx, out != nullptr, "quantize: out is null");
+  DP_CHECK(ctx, rows > 0 && cols > 0, "quantize: invalid shape [%lld,%lld]", (long long)rows, (long long)cols);
+  DP_CHECK(ctx, src && src->dtype == DP_F32, "quantize: source must be f32");
+  DP_TRY(check_tensor(ctx, src, "quantize", "source", (size_t)rows * cols * 4));
+  const size_t bytes = (size_t)rows * dp_cdiv((size_t)cols, DP_QK_K) * DP_Q4K_BLOCK_BYTES;
+  dp_buf obuf = nullptr;
+  DP_TRY(dp_out_buffer(ctx, out_buf, 0, bytes, "q4k_quantized", &obuf));
+  dp_status st = dpk_quantize_q4k(ctx, (const float *)dp_tptr(src), (uint8_t *)obuf->dptr, (size_t)rows, (size_t)cols, full_pad != 0);
+  if (st != DP_OK) { if (!out_buf) dp_buf_release(ctx, obuf); return st; }
+  dp_note_op(ctx, rec);
+  memset(out, 0, sizeof *out);
+  out->buf = obuf; out->offset = 0; out->dtype = DP_Q4K; out->layout = 0;
+  out->shape[0] = rows; out->shape[1] = cols;
+  return DP_OK;
+}
+
+// ---- fused decode ops ------------------------------------------------------------------
+extern "C" void dp_ffn_opts_default(dp_ffn_opts *o) {
+  if (!o) return;
+  memset(o, 0, sizeof *o);
+  o->batch_size = 1;
+  o->alpha = 1.0f;
+}
+
+// fused_ffn_q4k.wgsl:115-117,241-246
+__global__ void ffn_activate_kernel(const float *__restrict__ g, const float *__restrict__ u, float *__restrict__ out, size_t n,
+                                    float alpha, float clamp_max) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float x = g[i];
+    float v = (x / (1.0f + expf(-x))) * u[i] * alpha;
+    if (clamp_max > 0.0f) v = fminf(fmaxf(v, -clamp_max), clamp_max);
+    out[i] = v;
+  }
+}
+
+// validated device pointer of a row-layout [N,K] weight (Q4_K or f16)
+static dp_status fused_weight(dp_ctx *ctx, const dp_weight *B, const char *op, const char *name, int N, int K, const char **ptr) {
+  if (!B || !B->buf) return dp_fail(ctx, DP_ERR_INVALID, "%s: %s is null", op, name);
+  if (B->layout != 0) return dp_fail(ctx, DP_ERR_UNSUPPORTED, "%s: %s must use the row layout [N,K]", op, name);
+  if (B->shape[0] != N || B->shape[1] != K)
+    return dp_fail(ctx, DP_ERR_INVALID, "%s: %s shape [%lld,%lld] does not match [%d,%d]", op, name, (long long)B->shape[0],
+                   (long long)B->shape[1], N, K);
+  size_t need;
+  if (B->dtype == DP_Q4K) need = (size_t)N * dp_cdiv((size_t)K, DP_QK_K) * DP_Q4K_BLOCK_BYTES;
+  else if (B->dtype == DP_F16) need = (size_t)N * K * 2;
+  else return dp_fail(ctx, DP_ERR_UNSUPPORTED, "%s: %s dtype %s is outside this path (q4k or f16)", op, name, dp_dtype_name(B->dtype));
+  dp_tensor t;
+  memset(&t, 0, sizeof t);
+  t.buf = B->buf; t.offset = B->offset;
+  DP_TRY(check_tensor(ctx, &t, op, name, need));
+  *ptr = dp_tptr(&t);
+  return DP_OK;
+}
+
+// y[M,N] (f32) = alpha * x[M,K] . W^T (+ residual, M == 1 only)
+static dp_status fused_matvec(dp_ctx *ctx, dp_dtype wdtype, const char *w, const float *x, float *y, int M, int N, int K, float alpha,
+                              const float *residual) {
+  if (wdtype == DP_Q4K) {
+    if (M == 1) {
+      bool handled = false;
+      DP_TRY(dpk_gemv_q4k_fast(ctx, (const uint8_t *)w, x, y, DP_F32, N, K, alpha, residual, &handled));
+      if (!handled) DP_TRY(dpk_gemv_q4k(ctx, (const uint8_t *)w, x, y, DP_F32, N, K, alpha, residual));
+      return DP_OK;
+    }
+    return dpk_gemm_q4k_simt(ctx, (const uint8_t *)w, x, DP_F32, y, DP_F32, M, N, K, alpha);
+  }
+  DP_TRY(dpk_gemv_f16w(ctx, (const __half *)w, x, DP_F32, y, DP_F32, M, N, K, alpha));
+  if (residual) DP_TRY(dpk_residual_add(ctx, y, residual, y, (size_t)N, 1.0f));
+  return DP_OK;
+}
+
+extern "C" dp_status dp_fused_ffn(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *w_gate,
+                                  const dp_weight *w_up, int hidden, int inter, const dp_ffn_opts *opts_in, dp_tensor *out) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  dp_ffn_opts o;
+  if (opts_in) o = *opts_in; else dp_ffn_opts_default(&o);
+  DP_CHECK(ctx, out != nullptr, "fused_ffn: out is null");
+  DP_CHECK(ctx, hidden > 0 && inter > 0 && o.batch_size > 0, "fused_ffn: invalid hiddenSize=%d intermediateSize=%d batchSize=%d", hidden,
+           inter, o.batch_size);
+  DP_CHECK(ctx, w_gate && w_up, "fused_ffn: gate/up weights are null");
+  DP_CHECK(ctx, w_gate->dtype == w_up->dtype, "Fused FFN requires matching gate/up dtypes (gate=%s, up=%s)", dp_dtype_name(w_gate->dtype),
+           dp_dtype_name(w_up->dtype));
+  DP_CHECK(ctx, input && input->dtype == DP_F32, "Fused FFN requires f32 activations");
+  const int M = o.batch_size;
+  DP_TRY(check_tensor(ctx, input, "fused_ffn", "input", (size_t)M * hidden * 4));
+  const char *wg = nullptr, *wu = nullptr;
+  DP_TRY(fused_weight(ctx, w_gate, "fused_ffn", "W_gate", inter, hidden, &wg));
+  DP_TRY(fused_weight(ctx, w_up, "fused_ffn", "W_up", inter, hidden, &wu));
+  const size_t n = (size_t)M * inter;
+  dp_buf obuf = nullptr, tmp = nullptr;
+  DP_TRY(dp_out_buffer(ctx, o.out_buf, 0, n * 4, "fused_ffn_output", &obuf));
+  dp_status st = dp_buf_acquire(ctx, 2 * n * 4, "fused_ffn_gate_up", &tmp);
+  if (st == DP_OK) {
+    float *g = (float *)tmp->dptr, *u = g + n;
+    const float *x = (const float *)dp_tptr(input);
+    st = fused_matvec(ctx, w_gate->dtype, wg, x, g, M, inter, hidden, 1.0f, nullptr);
+    if (st == DP_OK) st = fused_matvec(ctx, w_up->dtype, wu, x, u, M, inter, hidden, 1.0f, nullptr);
+    if (st == DP_OK) {
+      size_t grid = (n + 255) / 256;
+      if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
+      cudaError_t e = dp_launch_impl(ctx, ffn_activate_kernel, dim3((unsigned)grid), dim3(256), 0, (const float *)g, (const float *)u,
+                                     (float *)obuf->dptr, n, o.alpha, o.swiglu_limit);
+      ctx->launches++;
+      if (e != cudaSuccess) st = dp_fail(ctx, DP_ERR_CUDA, "launch of ffn_activate_kernel failed: %s", cudaGetErrorString(e));
+    }
+    dp_buf_release(ctx, tmp);  // stream ordered: reused only by later work
+  }
+  if (st != DP_OK) { if (!o.out_buf) dp_buf_release(ctx, obuf); return st; }
+  dp_note_op(ctx, rec);
+  fill_tensor(out, obuf, 0, DP_F32, 2, M, inter, 0);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_matmul_residual(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *weight,
+                                        const dp_tensor *residual, int N, int K, float alpha, dp_buf out_buf, dp_tensor *out) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  DP_CHECK(ctx, out != nullptr, "matmul_residual: out is null");
+  DP_CHECK(ctx, N > 0 && K > 0, "matmul_residual: invalid N=%d K=%d", N, K);
+  DP_CHECK(ctx, input && input->dtype == DP_F32, "matmul_residual: input must be f32");
+  DP_CHECK(ctx, residual && residual->dtype == DP_F32, "matmul_residual: residual must be f32");
+  DP_TRY(check_tensor(ctx, input, "matmul_residual", "input", (size_t)K * 4));
+  DP_TRY(check_tensor(ctx, residual, "matmul_residual", "residual", (size_t)N * 4));
+  const char *w = nullptr;
+  DP_TRY(fused_weight(ctx, weight, "matmul_residual", "weight", N, K, &w));
+  dp_buf obuf = nullptr;
+  DP_TRY(dp_out_buffer(ctx, out_buf, 0, (size_t)N * 4, "matmul_residual_output", &obuf));
+  dp_status st = fused_matvec(ctx, weight->dtype, w, (const float *)dp_tptr(input), (float *)obuf->dptr, 1, N, K,
+                              alpha == 0.0f ? 1.0f : alpha, (const float *)dp_tptr(residual));
+  if (st != DP_OK) { if (!out_buf) dp_buf_release(ctx, obuf); return st; }
+  dp_note_op(ctx, rec);
+  fill_tensor(out, obuf, 0, DP_F32, 2, 1, N, 0);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_matmul_rmsnorm(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *weight,
+                                       const dp_tensor *norm_weight, int N, int K, float eps, const dp_tensor *residual,
+                                       int weight_offset, dp_buf out_buf, dp_tensor *out) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  DP_CHECK(ctx, out != nullptr, "matmul_rmsnorm: out is null");
+  DP_CHECK(ctx, N > 0 && K > 0, "matmul_rmsnorm: invalid N=%d K=%d", N, K);
+  DP_CHECK(ctx, eps > 0.0f, "[MatmulRMSNormFused] eps is required.");
+  DP_CHECK(ctx, input && input->dtype == DP_F32, "matmul_rmsnorm: input must be f32");
+  DP_TRY(check_tensor(ctx, input, "matmul_rmsnorm", "input", (size_t)K * 4));
+  DP_CHECK(ctx, norm_weight && (norm_weight->dtype == DP_F32 || norm_weight->dtype == DP_F16), "matmul_rmsnorm: norm weight must be f32 or f16");
+  DP_TRY(check_tensor(ctx, norm_weight, "matmul_rmsnorm", "normWeight", (size_t)N * dp_dtype_size(norm_weight->dtype)));
+  if (residual) {
+    DP_CHECK(ctx, residual->dtype == DP_F32, "matmul_rmsnorm: residual must be f32");
+    DP_TRY(check_tensor(ctx, residual, "matmul_rmsnorm", "residual", (size_t)N * 4));
+  }
+  const char *w = nullptr;
+  DP_TRY(fused_weight(ctx, weight, "matmul_rmsnorm", "weight", N, K, &w));
+  dp_buf obuf = nullptr, tmp = nullptr;
+  DP_TRY(dp_out_buffer(ctx, out_buf, 0, (size_t)N * 4, "matmul_rmsnorm_output", &obuf));
+  dp_status st = dp_buf_acquire(ctx, (size_t)N * 4, "matmul_rmsnorm_projection", &tmp);
+  if (st == DP_OK) {
+    st = fused_matvec(ctx, weight->dtype, w, (const float *)dp_tptr(input), (float *)tmp->dptr, 1, N, K, 1.0f, nullptr);
+    if (st == DP_OK)
+      st = dpk_rmsnorm(ctx, (const float *)tmp->dptr, dp_tptr(norm_weight), norm_weight->dtype == DP_F16,
+                       residual ? (const float *)dp_tptr(residual) : nullptr, false, nullptr, (float *)obuf->dptr, 1, N, eps,
+                       weight_offset != 0, 1.0f);
+    dp_buf_release(ctx, tmp);
+  }
+  if (st != DP_OK) { if (!out_buf) dp_buf_release(ctx, obuf); return st; }
+  dp_note_op(ctx, rec);
+  fill_tensor(out, obuf, 0, DP_F32, 2, 1, N, 0);
+  return DP_OK;
+}
+
+extern "C" dp_status dp_lm_head_argmax(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *lm_head, int vocab,
+                                       int hidden, int pad_id, dp_buf out_tokens, int output_index) {
+  DP_TRY(dp_check_rec(ctx, rec));
+  DP_CHECK(ctx, vocab > 0 && hidden > 0, "[LmHeadArgmax] invalid vocabSize=%d hiddenSize=%d", vocab, hidden);
+  DP_CHECK(ctx, input && input->dtype == DP_F32, "[LmHeadArgmax] input tensor must be f32, got \"%s\".",
+           input ? dp_dtype_name(input->dtype) : "unknown");
+  DP_TRY(check_tensor(ctx, input, "lm_head_argmax", "input", (size_t)hidden * 4));
+  DP_CHECK(ctx, out_tokens && out_tokens->active && output_index >= 0 && (size_t)(output_index + 1) * 4 <= out_tokens->bytes,
+           "[LmHeadArgmax] output buffer too small for outputIndex %d", output_index);
+  const char *w = nullptr;
+  DP_TRY(fused_weight(ctx, lm_head, "lm_head_argmax", "lmHead", vocab, hidden, &w));
+  DP_TRY(dp_scratch(ctx, &ctx->argmax_scratch, 256 * 8, "argmax_partials"));
+  dp_buf logits = nullptr;
+  DP_TRY(dp_buf_acquire(ctx, (size_t)vocab * 4, "lm_head_argmax_temp_logits", &logits));
+  dp_status st = fused_matvec(ctx, lm_head->dtype, w, (const float *)dp_tptr(input), (float *)logits->dptr, 1, vocab, hidden, 1.0f, nullptr);
+  if (st == DP_OK) {
+    float *vals = (float *)ctx->argmax_scratch->dptr;
+    st = dpk_argmax(ctx, (const float *)logits->dptr, vocab, pad_id, (int *)out_tokens->dptr, output_index, vals, (int *)(vals + 256), 0,
+                    nullptr);
+  }
+  dp_buf_release(ctx, logits);
+  if (st != DP_OK) return st;
+  dp_note_op(ctx, rec);
+  return DP_OK;
+}
+
 // ---- KV cache ------------------------------------------------------------------------
 struct dp_kv_cache {
   dp_ctx *ctx;

@@ -454,6 +454,106 @@ def run_argmax(logits: Tensor, vocab_size: int, *, pad_token_id: int = -1, outpu
     return out
 
 
+def quantize_to_q4km_rowwise(data: Tensor, shape, *, output_buffer: Optional[Buffer] = None, recorder=None) -> WeightBuffer:
+    """reference: quantizeToQ4KMRowWise(data, shape), src/converter/quantizer.js:253-288 (bit-exact, on the device)"""
+    dev = data.buffer.device
+    rows, cols = int(shape[0]), int(shape[1])
+    d, out = data.c(), L.WeightS()
+    dev.check(dev.lib.dp_quantize_q4k(dev.h, _rec(recorder), C.byref(d), rows, cols, 0,
+                                      output_buffer.h if output_buffer is not None else None, C.byref(out)))
+    nbytes = rows * ((cols + 255) // 256) * 144
+    buf = output_buffer if output_buffer is not None else Buffer(dev, C.c_void_p(out.buf), nbytes, "q4k_quantized")
+    return create_weight_buffer(buf, "q4k", "row", [rows, cols], "q4k_quantized")
+
+
+def quantize_to_q4km(data: Tensor, num_elements: int, *, output_buffer: Optional[Buffer] = None, recorder=None) -> WeightBuffer:
+    """reference: quantizeToQ4KM(data), src/converter/quantizer.js:223-251 (flat; a short tail is zero padded)"""
+    dev = data.buffer.device
+    d, out = data.c(), L.WeightS()
+    dev.check(dev.lib.dp_quantize_q4k(dev.h, _rec(recorder), C.byref(d), 1, int(num_elements), 1,
+                                      output_buffer.h if output_buffer is not None else None, C.byref(out)))
+    nbytes = ((num_elements + 255) // 256) * 144
+    buf = output_buffer if output_buffer is not None else Buffer(dev, C.c_void_p(out.buf), nbytes, "q4k_quantized")
+    return create_weight_buffer(buf, "q4k", "row", [1, int(num_elements)], "q4k_quantized")
+
+
+# ------------------------------------------------------------------------------
+# fused decode ops (src/gpu/kernels/index.js:300-330)
+# ------------------------------------------------------------------------------
+def record_fused_ffn(recorder, input: Tensor, W_gate: WeightBuffer, W_up: WeightBuffer, hidden_size: int, intermediate_size: int, *,
+                     batch_size: int = 1, activation: str = "silu", alpha: float = 1.0, output_buffer: Optional[Buffer] = None,
+                     swiglu_limit: Optional[float] = None, **_ignored) -> Tensor:
+    """reference: recordFusedFFN, src/gpu/kernels/fused_ffn.js:605"""
+    dev = input.buffer.device
+    if activation != "silu":
+        raise DopplerError(L.ERR_UNSUPPORTED, f"Fused FFN: activation '{activation}' is outside this path (silu)")
+    o = L.FfnOpts()
+    dev.lib.dp_ffn_opts_default(C.byref(o))
+    o.batch_size, o.alpha, o.swiglu_limit = batch_size, alpha, float(swiglu_limit or 0.0)
+    o.out_buf = output_buffer.h if output_buffer is not None else None
+    i, g, u, out = input.c(), W_gate.c(), W_up.c(), L.TensorS()
+    dev.check(dev.lib.dp_fused_ffn(dev.h, _rec(recorder), C.byref(i), C.byref(g), C.byref(u), hidden_size, intermediate_size,
+                                   C.byref(o), C.byref(out)))
+    return _wrap(dev, out, output_buffer, "fused_ffn_output")
+
+
+def run_fused_ffn(input, W_gate, W_up, hidden_size, intermediate_size, **options) -> Tensor:
+    """reference: runFusedFFN, src/gpu/kernels/fused_ffn.js:501"""
+    return record_fused_ffn(None, input, W_gate, W_up, hidden_size, intermediate_size, **options)
+
+
+def record_matmul_residual_fused(recorder, input: Tensor, weight: WeightBuffer, residual: Tensor, *, N: int, K: int,
+                                 alpha: float = 1.0, output_buffer: Optional[Buffer] = None, **_ignored) -> Tensor:
+    """reference: recordMatmulResidualFused, src/gpu/kernels/fused_matmul_residual.js:105"""
+    dev = input.buffer.device
+    i, w, r, out = input.c(), weight.c(), residual.c(), L.TensorS()
+    dev.check(dev.lib.dp_matmul_residual(dev.h, _rec(recorder), C.byref(i), C.byref(w), C.byref(r), N, K, alpha,
+                                         output_buffer.h if output_buffer is not None else None, C.byref(out)))
+    return _wrap(dev, out, output_buffer, "matmul_residual_output")
+
+
+def run_matmul_residual_fused(input, weight, residual, **options) -> Tensor:
+    """reference: runMatmulResidualFused, src/gpu/kernels/fused_matmul_residual.js:27"""
+    return record_matmul_residual_fused(None, input, weight, residual, **options)
+
+
+def record_matmul_rmsnorm_fused(recorder, input: Tensor, weight: WeightBuffer, norm_weight: Tensor, *, N: int, K: int,
+                                eps: Optional[float] = None, residual: Optional[Tensor] = None,
+                                output_buffer: Optional[Buffer] = None, rms_norm_weight_offset: bool = False, **_ignored) -> Tensor:
+    """reference: recordMatmulRMSNormFused, src/gpu/kernels/fused_matmul_rmsnorm.js:171"""
+    dev = input.buffer.device
+    if eps is None:
+        raise DopplerError(L.ERR_INVALID, "[MatmulRMSNormFused] eps is required.")
+    i, w, nw, out = input.c(), weight.c(), norm_weight.c(), L.TensorS()
+    r = residual.c() if residual is not None else None
+    dev.check(dev.lib.dp_matmul_rmsnorm(dev.h, _rec(recorder), C.byref(i), C.byref(w), C.byref(nw), N, K, eps,
+                                        C.byref(r) if r is not None else None, 1 if rms_norm_weight_offset else 0,
+                                        output_buffer.h if output_buffer is not None else None, C.byref(out)))
+    return _wrap(dev, out, output_buffer, "matmul_rmsnorm_output")
+
+
+def run_matmul_rmsnorm_fused(input, weight, norm_weight, **options) -> Tensor:
+    """reference: runMatmulRMSNormFused, src/gpu/kernels/fused_matmul_rmsnorm.js:52"""
+    return record_matmul_rmsnorm_fused(None, input, weight, norm_weight, **options)
+
+
+def record_lm_head_argmax(recorder, input: Tensor, lm_head: WeightBuffer, *, vocab_size: int, hidden_size: int,
+                          pad_token_id: int = -1, output_buffer: Optional[Buffer] = None, output_index: int = 0,
+                          **_ignored) -> Buffer:
+    """reference: recordLmHeadArgmax, src/gpu/kernels/lm-head-argmax.js:292 (returns the token buffer)"""
+    dev = input.buffer.device
+    out = output_buffer if output_buffer is not None else dev.acquire_buffer(max(4, 4 * (output_index + 1)), "lm_head_argmax_output")
+    i, w = input.c(), lm_head.c()
+    try:
+        dev.check(dev.lib.dp_lm_head_argmax(dev.h, _rec(recorder), C.byref(i), C.byref(w), vocab_size, hidden_size, pad_token_id,
+                                            out.h, output_index))
+    except DopplerError:
+        if output_buffer is None:
+            dev.release_buffer(out)
+        raise
+    return out
+
+
 # ------------------------------------------------------------------------------
 # KV cache
 # ------------------------------------------------------------------------------

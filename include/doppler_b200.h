@@ -235,6 +235,47 @@ dp_status dp_kv_write_f32_to_f16(dp_ctx *ctx, dp_recorder *rec, const dp_tensor 
 dp_status dp_argmax(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *logits, int n, int pad_id,
                     dp_buf out_tokens_i32, int output_index);
 
+/* ---- quantizer ---------------------------------------------------------- */
+/* reference: quantizeToQ4KMRowWise  src/converter/quantizer.js:253-288 (full_pad = 0: the tail of a
+ * row's last block is left out of the ranges) and quantizeToQ4KM :223-251 (rows = 1, full_pad = 1:
+ * the tail is zero padded and quantised as a full block).  Bit-exact with the reference's
+ * double-precision arithmetic.  src f32 [rows, cols]; out: packed blocks, dtype q4k, layout row. */
+dp_status dp_quantize_q4k(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *src_f32, int64_t rows, int64_t cols,
+                          int full_pad, dp_buf out_buf, dp_weight *out);
+
+/* ---- fused decode ops ---------------------------------------------------
+ * The reference exposes these as ops of their own (src/gpu/kernels/index.js:300-330); they keep
+ * the reference's argument meaning so that a pipeline that records them needs no other change. */
+/* reference: runFusedFFN / recordFusedFFN  src/gpu/kernels/fused_ffn.js:501,605 (fused_ffn_q4k.wgsl:
+ * 115-117,241-246): out[b,i] = clamp(silu(Wgate.x_b)_i * (Wup.x_b)_i * alpha, +-swiglu_limit),
+ * silu(x) = x / (1 + exp(-x)); f32 input [batch, hidden], f32 output [batch, inter]. */
+typedef struct {
+  int batch_size;       /* default 1 */
+  float alpha;          /* default 1 */
+  float swiglu_limit;   /* 0 = no clamp */
+  dp_buf out_buf;
+} dp_ffn_opts;
+void dp_ffn_opts_default(dp_ffn_opts *o);
+dp_status dp_fused_ffn(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *w_gate,
+                       const dp_weight *w_up, int hidden_size, int intermediate_size,
+                       const dp_ffn_opts *opts, dp_tensor *out);
+/* reference: runMatmulResidualFused  src/gpu/kernels/fused_matmul_residual.js:27 (M = 1):
+ * out[N] = alpha * (W.x) + residual */
+dp_status dp_matmul_residual(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *weight,
+                             const dp_tensor *residual, int N, int K, float alpha, dp_buf out_buf,
+                             dp_tensor *out);
+/* reference: runMatmulRMSNormFused  src/gpu/kernels/fused_matmul_rmsnorm.js:52
+ * (fused_matmul_rmsnorm.wgsl:1-12,161): out[N] = rmsnorm(W.x, norm_weight, eps) + residual (M = 1) */
+dp_status dp_matmul_rmsnorm(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *weight,
+                            const dp_tensor *norm_weight, int N, int K, float eps,
+                            const dp_tensor *residual, int weight_offset, dp_buf out_buf, dp_tensor *out);
+/* reference: recordLmHeadArgmax  src/gpu/kernels/lm-head-argmax.js:292 (lm_head_argmax_q4k.wgsl):
+ * token = argmax_v (lm_head[v,:] . x), pad_token_id excluded, ties to the lower index; the id is
+ * written to out_tokens_i32[output_index].  lm_head is f16 or Q4_K [vocab, hidden]. */
+dp_status dp_lm_head_argmax(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *input, const dp_weight *lm_head,
+                            int vocab_size, int hidden_size, int pad_token_id, dp_buf out_tokens_i32,
+                            int output_index);
+
 /* ---- KV cache ----------------------------------------------------------- */
 /* reference: KVCache (contiguous f16)  src/inference/kv-cache/base.js:18,99-153;
  * truncate :962; clone :829.  Per layer two buffers [batch][max_seq, n_kv_heads, head_dim] f16. */

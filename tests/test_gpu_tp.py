@@ -1,5 +1,5 @@
-"""Tensor-parallel decode on two GPUs (one process per GPU, NCCL over NVLink): tokens must be
-identical to the single-model oracle.  Skipped on a box with fewer than two GPUs."""
+"""Tensor-parallel decode on 2, 4 and 8 GPUs (one process per GPU, NCCL over NVLink): tokens must be
+identical to the single-model oracle.  Each case is skipped on a box with fewer GPUs than ranks."""
 import os
 import socket
 import subprocess
@@ -23,6 +23,8 @@ dist.init_process_group("gloo", rank=rank, world_size=world)
 dev = Device(rank)
 tp.init_group(dev, rank, world)
 cfg = dict(synthetic.MODEL_CONFIGS["small"])
+if world == 8:
+    cfg["inter"] = 4096   # the row-parallel K slice (inter / world) must be whole 256-weight super-blocks
 w = gaussian_model_weights(cfg, 2468)
 prompt = synthetic.make_prompt(cfg, 48, seed=2468)
 m = DecoderModel(dev, cfg, max_seq=1024, tp_rank=rank, tp_size=world)
@@ -61,15 +63,16 @@ def _gpu_count():
         return 0
 
 
-def test_two_gpu_tokens_identical(tmp_path):
-    if _gpu_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_tokens_identical(tmp_path, world):
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = str(s.getsockname()[1]); s.close()
     procs = []
-    for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=port, DP_ROOT=ROOT,
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=port, DP_ROOT=ROOT,
                    NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
