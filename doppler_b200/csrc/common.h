@@ -40,6 +40,11 @@ struct dp_ctx {
   dp_buf argmax_scratch = nullptr;
   dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
   bool pdl = false;  // launch with programmatic dependent launch (set while the decode step is recorded)
+  // Weight matrix of the NEXT Q4_K GEMV in program order (set by the decode schedule, consumed by the
+  // next TMA GEMV launch): that launch's producer warps pull its first row tiles into L2 once their own
+  // copies are issued, so the next kernel's pipeline fills from L2 instead of HBM.
+  const void *gemv_next_w = nullptr;
+  int gemv_next_rows = 0, gemv_next_k = 0;
   int *dev_status = nullptr;  // device word raised by a kernel whose bounded wait gave up
   dp_recorder *active_recorder = nullptr;
   dp_tp_state *tp = nullptr;

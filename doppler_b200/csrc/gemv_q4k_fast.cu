@@ -247,6 +247,9 @@ struct GemvSource {
   const float *w;   // norm weights
   float eps;
   int D, splits;    // SRC_COMBINE: head_dim and number of splits
+  // the next GEMV's matrix (may be null): rows, bytes per row, CTAs of that launch, row tiles to pull into L2 per CTA
+  const uint8_t *next_w;
+  int next_rows, next_row_bytes, next_grid, next_tiles;
 };
 
 // GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
@@ -394,6 +397,16 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
         }
       }
     }
+    if (ok && gs.next_w && (int)blockIdx.x < gs.next_grid && lane < 16) {
+      // all copies of this launch are issued; warm L2 with the row tiles this CTA index streams first next time
+      const int tiles_n = gs.next_rows / 16;
+      for (int j = 0; j < gs.next_tiles; j++) {
+        const int rt = (int)blockIdx.x + j * gs.next_grid;
+        if (rt >= tiles_n) break;
+        const uint8_t *row = gs.next_w + (size_t)(rt * 16 + lane) * (size_t)gs.next_row_bytes;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"((uint32_t)gs.next_row_bytes) : "memory");
+      }
+    }
     if (!ok && lane == 0) {  // gave up: let the copies already issued land before the CTA exits
       const uint32_t first = u > (uint32_t)stages ? u - (uint32_t)stages : 0u;
       for (uint32_t v = first; v < u; v++) {
@@ -523,13 +536,24 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
   const float *ssum = limbs ? xscale + K / QK_K : nullptr;
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
+  GemvSource src = gs;
+  src.next_w = nullptr;
+  if (ctx->gemv_next_w && ctx->gemv_next_rows >= 16 && ctx->gemv_next_k % QK_K == 0) {
+    src.next_w = (const uint8_t *)ctx->gemv_next_w;
+    src.next_rows = ctx->gemv_next_rows;
+    src.next_row_bytes = ctx->gemv_next_k / QK_K * Q4K_BLOCK_BYTES;
+    src.next_grid = ctx->gemv_next_rows / 16 < ctx->sm_count ? ctx->gemv_next_rows / 16 : ctx->sm_count;
+    const int tile_bytes = 16 * src.next_row_bytes;
+    src.next_tiles = (192 * 1024 + tile_bytes - 1) / tile_bytes;  // about one ring's worth per SM
+  }
+  ctx->gemv_next_w = nullptr;  // a hint serves one launch
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
   DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
-            N, K, cb, stages, alpha, residual, ctx->dev_status, gs);
+            N, K, cb, stages, alpha, residual, ctx->dev_status, src);
   return DP_OK;
 }
 

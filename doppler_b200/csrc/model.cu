@@ -70,6 +70,10 @@ struct dp_model {
   dp_buf attn_scratch = nullptr;
   dp_buf actq = nullptr;  // fixed-point activation digits of the decode GEMV (sized for the largest K)
   int attn_splits_decode = 1;
+  // GEMV launches can warm L2 with the next matrix (DP_GEMV_PREFETCH=1).  Off by default: measured on the
+  // 9B-shaped step it costs more than it saves (2.113 ms with, 2.082 ms without; the prefetch traffic
+  // lands on the current kernel's tail).
+  bool prefetch_next = false;
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
   int graph_batch[2] = {0, 0};
@@ -416,6 +420,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   DP_CHECK(ctx, p == 1 || dp_tp_ready(ctx), "model: tp_size %d needs dp_tp_init on this context first", p);
   dp_model *m = new dp_model();
   m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
+  if (const char *e = getenv("DP_GEMV_PREFETCH")) m->prefetch_next = atoi(e) != 0;
   if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
   DP_CHECK(ctx, m->cfg.max_batch <= 256, "model: max_batch %d > 256", m->cfg.max_batch);
   m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
@@ -652,6 +657,13 @@ enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
 // (RMSNorm, SiLU*up or the split-K merge) while its weight ring fills, so a layer is six kernels:
 //   GEMV qkv [rmsnorm]  ->  qk-norm + rope + KV append  ->  attention split
 //   -> GEMV o [split merge] + residual  ->  GEMV gate|up [rmsnorm]  ->  GEMV down [silu*up] + residual
+// tell the next Q4_K GEMV launch which matrix follows it (see dp_ctx::gemv_next_w)
+static inline void hint_next(dp_model *m, const dp_buf w, int rows, int k) {
+  m->ctx->gemv_next_w = (m->prefetch_next && w) ? w->dptr : nullptr;
+  m->ctx->gemv_next_rows = rows;
+  m->ctx->gemv_next_k = k;
+}
+
 static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
   dp_ctx *ctx = m->ctx;
   const dp_model_cfg &c = m->cfg;
@@ -668,6 +680,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     const int nqkv = m->qdim + 2 * m->kvdim;
     // ---- q, k, v ----
     bool done = false;
+    if (single) hint_next(m, L.o, H, m->qdim);
     if (n_ready) {  // written by the exchange kernel of the previous layer
       n_ready = false;
       DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, true));
@@ -712,6 +725,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     float *o_dst = p == 1 ? m->h : m->partial;
     const float *o_res = p == 1 ? m->h : nullptr;
     done = false;
+    if (single) hint_next(m, L.gateup, 2 * m->inter, H);
     const bool split_merge_ok = single && splits > 1 && D % 8 == 0 && m->qdim % QK_K == 0;
     if (split_merge_ok) {
       DP_TRY(dpk_attention_split_only(ctx, ap, (float *)m->attn_scratch->dptr, splits));
@@ -746,6 +760,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     }
     // ---- gate | up ----
     done = false;
+    if (single) hint_next(m, L.down, H, m->inter);
     if (gu_digits) {
       DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, true));
       done = true;
@@ -766,6 +781,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     float *d_dst = p == 1 ? m->h : m->partial;
     const float *d_res = p == 1 ? m->h : nullptr;
     done = false;
+    if (single) hint_next(m, l + 1 < c.n_layers ? m->layers[l + 1].qkv : nullptr, nqkv, H);
     if (single && m->inter % QK_K == 0)
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
     if (!done) {
@@ -936,7 +952,10 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
                              (const uint8_t *)L.down->dptr};
       const float *X[4] = {m->n, m->att, m->n, m->actv};
       float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
+      const dp_buf next_qkv = l + 1 < c.n_layers ? m->layers[l + 1].qkv : (r + 1 < reps ? m->layers[0].qkv : nullptr);
+      const dp_buf NW[4] = {L.o, L.gateup, L.down, next_qkv};
       for (int i = 0; i < 4; i++) {
+        hint_next(m, NW[i], sh[(i + 1) & 3].N, sh[(i + 1) & 3].K);  // as the decode schedule does
         // digits_ready: in the decode step the producer kernel has already written them
         DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K)));
         n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;

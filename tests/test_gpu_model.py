@@ -99,3 +99,28 @@ def test_decode_resumes_and_resets(dev):
     with pytest.raises(Exception):
         m.decode([0], 1000)  # beyond max_seq
     m.destroy()
+
+
+def test_batched_decode_is_independent_sequences(dev):
+    """Batch is an extension of the reference (which decodes one sequence): its oracle is the
+    same number of independent single-sequence runs.  Different prompt lengths per sequence."""
+    cfg = dict(synthetic.MODEL_CONFIGS["small"])
+    w = gaussian_model_weights(cfg, 4321)
+    lens = [33, 7, 64, 20]
+    steps, max_seq = 24, 128
+    m = DecoderModel(dev, cfg, max_seq=max_seq, max_batch=len(lens))
+    m.load_all(w)
+    prompts = [synthetic.make_prompt(cfg, n, seed=4321, seq=i) for i, n in enumerate(lens)]
+    firsts = [m.prefill(p, seq=i) for i, p in enumerate(prompts)]
+    out = m.decode(firsts, steps)  # [steps, batch]
+    assert out.shape == (steps, len(lens))
+    for i, p in enumerate(prompts):
+        om = O.OracleModel(dict(cfg, max_seq=max_seq), w)
+        tok, margin = om.forward(p)
+        assert firsts[i] == tok, f"sequence {i}: prefill token {firsts[i]} vs oracle {tok} (margin {margin:.3e})"
+        cur = tok
+        for s in range(steps):
+            cur, margin = om.forward([cur])
+            assert int(out[s, i]) == cur, f"sequence {i} step {s}: {int(out[s, i])} vs oracle {cur} (margin {margin:.3e})"
+        assert m.seq_len(i) == lens[i] + steps
+    m.destroy()
