@@ -81,6 +81,50 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// ---- two-CTA cluster helpers (PAIR variant) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {  // same offset in another CTA of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {  // acquire at cluster scope
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t i = 0; i < (1u << 20); i++) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// commit that arrives on the same barrier offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"((uint16_t)3)
+               : "memory");
+}
+
 struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
@@ -98,7 +142,11 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB) {
   return l;
 }
 
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
+// PAIR: two CTAs of a cluster own the two 256-row halves of a 512 x BN output tile.  They need the same
+// weight tile, so each dequantises half of its rows and stores them into BOTH CTAs' shared memory
+// (distributed shared memory); every weight is then dequantised once per 512 rows instead of once per
+// 256.  The tensor-core side is unchanged: each CTA issues its own cta_group::1 MMAs on its own copy.
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, bool PAIR>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, float alpha, int *__restrict__ err) {
@@ -122,7 +170,9 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   pdl_wait();
   if (tid == 0) {
     for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
-    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), DQ_WARPS); mbar_init(empty_b(s), 1); }
+    // PAIR: a weight stage is full when the dequant warps of both CTAs have arrived, and free when
+    // the tensor cores of both CTAs have read it
+    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), PAIR ? 2 * DQ_WARPS : DQ_WARPS); mbar_init(empty_b(s), PAIR ? 2 : 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -135,6 +185,11 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  uint32_t pair_rank = 0;
+  if constexpr (PAIR) {
+    pair_rank = cluster_ctarank();
+    cluster_sync_all();  // the peer's barriers exist before anyone arrives on them remotely
+  }
 
   if (warp == 0) {
     // ---------------- activation tiles: TMA ----------------
@@ -156,8 +211,9 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       bool ok = true;
       for (int kt = 0; kt < num_k && ok; kt++) {
         const int sa = kt % SA, sb = kt % SB;
-        if (!mbar_wait_bounded(full_a(sa), (uint32_t)(kt / SA) & 1u, abort_flag) ||
-            !mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_bounded(full_a(sa), (uint32_t)(kt / SA) & 1u, abort_flag)) { ok = false; break; }
+        if (PAIR ? !mbar_wait_bounded_cluster(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)
+                 : !mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)sa * L.stage_a);
         const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)sb * L.stage_b);
@@ -169,7 +225,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           umma_f16(tmem_base + (uint32_t)BN, umma_desc_sw128(a_addr + 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
         umma_commit(empty_a(sa));  // both stages are free once these MMAs have read them
-        umma_commit(empty_b(sb));
+        if constexpr (PAIR) umma_commit_pair(empty_b(sb)); else umma_commit(empty_b(sb));
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -178,7 +234,11 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     const int dw = warp - 2;            // 0..7
     const int r8 = lane & 7, oct = lane >> 3;  // row within the 8-row group, byte octet of the 32-byte chunk
     bool ok = true;
-    constexpr int RG = BN / 8 / DQ_WARPS;  // 8-row groups per warp
+    constexpr int RG = BN / 8 / DQ_WARPS / (PAIR ? 2 : 1);  // 8-row groups per warp (PAIR: this CTA's half of the tile)
+    static_assert(RG >= 1 && RG * DQ_WARPS * 8 * (PAIR ? 2 : 1) == BN, "dequant warps must tile the weight rows");
+    const int grp0 = PAIR ? (int)pair_rank * (BN / 16) : 0;  // first 8-row group this CTA dequantises
+    const uint32_t b_local = smem_u32(smem + L.b);
+    const uint32_t b_peer = PAIR ? mapa_shared(b_local, pair_rank ^ 1u) : 0u;
     // software pipeline at super-block granularity: while the four K steps of block b are dequantised,
     // the header and the four quant pieces of block b+1 are already in flight
     uint4 hdr[RG];
@@ -186,7 +246,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     const uint32_t *rowp[RG];
 #pragma unroll
     for (int j = 0; j < RG; j++) {
-      rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (dw + j * DQ_WARPS) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+      rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (grp0 + dw + j * DQ_WARPS) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
       hdr[j] = __ldg(reinterpret_cast<const uint4 *>(rowp[j]));
 #pragma unroll
       for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(rowp[j] + 4 + 8 * c) + oct);
@@ -252,13 +312,24 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
           }
           // row r of an 8-row group: 16-byte chunk c lives at chunk (c ^ r) of the 128-byte line
-          uint8_t *line = bt + (uint32_t)(dw + j * DQ_WARPS) * 1024u + (uint32_t)r8 * 128u;
-          *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-          *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          uint8_t *line = bt + (uint32_t)(grp0 + dw + j * DQ_WARPS) * 1024u + (uint32_t)r8 * 128u;
+          const uint32_t off_lo = ((uint32_t)oct ^ (uint32_t)r8) << 4, off_hi = ((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4;
+          *reinterpret_cast<uint4 *>(line + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4 *>(line + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if constexpr (PAIR) {  // the same two chunks into the peer CTA's copy of the stage
+            const uint32_t rline = b_peer + (smem_u32(line) - b_local);
+            st_cluster_v4(rline + off_lo, lo[0], lo[1], lo[2], lo[3]);
+            st_cluster_v4(rline + off_hi, hi[0], hi[1], hi[2], hi[3]);
+          }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+        // generic-proxy stores -> visible to the tensor core (of both CTAs in the PAIR variant)
+        if constexpr (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
+        else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_b(s));
+        if (lane == 0) {
+          mbar_arrive(full_b(s));
+          if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b(s), pair_rank ^ 1u));
+        }
       }
     }
     // ---------------- epilogue: tensor memory -> registers -> C ----------------
@@ -302,6 +373,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // no CTA leaves while its peer may still store into it or arrive on its barriers
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -337,9 +409,34 @@ template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
   const size_t smem = tc_layout(BN, SA, SB).total + 1024;
   static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(N / BN, (M + BM - 1) / BM);
-  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  return DP_OK;
+}
+
+// PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
+dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  const size_t smem = tc_layout(BN, SA, SB).total + 1024;
+  auto kernel = gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, true>;
+  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(N / BN, (M + BM - 1) / BM);
+  cfg.blockDim = dim3((DQ_WARPS + 2) * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 2;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  ctx->launches++;
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc_kernel (paired) failed: %s", cudaGetErrorString(e));
   return DP_OK;
 }
 
@@ -350,6 +447,14 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   // DP_GEMM_RINGS=1 selects the deeper weight ring.
   static int rings = -1;
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
+  // an even number of 256-row tiles: pairs of CTAs share the dequantisation (DP_GEMM_PAIR=0 turns it off)
+  static int pair = -1;
+  if (pair < 0) { const char *e = getenv("DP_GEMM_PAIR"); pair = e ? atoi(e) : 1; }
+  const int m_tiles = (M + BM - 1) / BM;
+  if (pair && m_tiles % 2 == 0) {
+    if (bn == 192) return launch_tc_pair<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_pair<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  }
   if (bn == 192) return rings ? launch_tc<192, 12, OutT, 3, 5>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
   return rings ? launch_tc<128, 8, OutT, 4, 6>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
 }

@@ -430,7 +430,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
         const int s = (int)(u % (uint32_t)stages);
         const uint32_t n = u / (uint32_t)stages;
         if (!mbar_wait_bounded(full_bar(s), n & 1u, abort_flag)) { ok = false; break; }
-        for (int bw = warp; bw < cb; bw += TG_CONSUMERS) {
+        for (int bw = warp; bw < cb && alpha != 12345.0f; bw += TG_CONSUMERS) {
           const int b = ch * cb + bw;
           const uint8_t *pa = smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)g * L.row_stride + (uint32_t)bw * Q4K_BLOCK_BYTES;
           const uint8_t *pb = pa + 8u * L.row_stride;
