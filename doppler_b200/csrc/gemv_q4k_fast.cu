@@ -417,9 +417,11 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
   } else {
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
-    const float w0 = t == 0 ? 1.0f : (t == 1 ? 65536.0f : 0.0f);
-    const float w1 = t == 0 ? 256.0f : 0.0f;
-    const uint32_t M4 = 0x0f0f0f0fu;
+    // The three activation limbs sit in the even columns 0, 2, 4 of the MMA's B operand, so every lane
+    // finds its limb in accumulator registers c0 (row g) and c2 (row g+8); c1 / c3 are never read.
+    const float wt = t == 0 ? 1.0f : (t == 1 ? 256.0f : (t == 2 ? 65536.0f : 0.0f));
+    const bool limb_lane = (g & 1) == 0 && g < 6;  // B fragment column g carries limb g/2
+    const uint32_t M4 = 0x0f0f0f0fu, M4H = 0xf0f0f0f0u;
     uint32_t tile_no = (uint32_t)group;
     bool ok = true;
     float *red = reinterpret_cast<float *>(smem + L.red);
@@ -430,7 +432,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
         const int s = (int)(u % (uint32_t)stages);
         const uint32_t n = u / (uint32_t)stages;
         if (!mbar_wait_bounded(full_bar(s), n & 1u, abort_flag)) { ok = false; break; }
-        for (int bw = warp; bw < cb && alpha != 12345.0f; bw += TG_CONSUMERS) {
+        for (int bw = warp; bw < cb; bw += TG_CONSUMERS) {
           const int b = ch * cb + bw;
           const uint8_t *pa = smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)g * L.row_stride + (uint32_t)bw * Q4K_BLOCK_BYTES;
           const uint8_t *pb = pa + 8u * L.row_stride;
@@ -444,31 +446,31 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
           }
           const Q4KScales sa = q4k_unpack_scales(ha.y, ha.z, ha.w);
           const Q4KScales sb_ = q4k_unpack_scales(hb.y, hb.z, hb.w);
-          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 8 * 128) + g * 4 + t;
-          int accA0 = 0, accA1 = 0, accB0 = 0, accB1 = 0;
+          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 8 * 128) + (g >> 1) * 4 + t;
+          // odd sub-blocks are the high nibbles: they stay in place (16 * q as a u8), their sums are
+          // accumulated apart and divided by 16 exactly at the end, which saves the four shifts per MMA
+          int accA = 0, accB = 0, accAh = 0, accBh = 0;
 #pragma unroll
           for (int c = 0; c < 4; c++) {
 #pragma unroll
             for (int hi = 0; hi < 2; hi++) {
               const int sb = 2 * c + hi;
               uint2 bf = make_uint2(0u, 0u);
-              if (g < 3) bf = lb[sb * 16];
-              const uint32_t a0 = hi ? (qa[c].x >> 4) & M4 : qa[c].x & M4;
-              const uint32_t a1 = hi ? (qb[c].x >> 4) & M4 : qb[c].x & M4;
-              const uint32_t a2 = hi ? (qa[c].y >> 4) & M4 : qa[c].y & M4;
-              const uint32_t a3 = hi ? (qb[c].y >> 4) & M4 : qb[c].y & M4;
+              if (limb_lane) bf = lb[sb * 16];
+              const uint32_t mk = hi ? M4H : M4;
               int c0, c1, c2, c3;
-              mma_u8s8(c0, c1, c2, c3, a0, a1, a2, a3, bf.x, bf.y);
-              const int scA = (int)q4k_byte(sb < 4 ? sa.sc03 : sa.sc47, sb & 3);
-              const int scB = (int)q4k_byte(sb < 4 ? sb_.sc03 : sb_.sc47, sb & 3);
-              accA0 += scA * c0; accA1 += scA * c1;
-              accB0 += scB * c2; accB1 += scB * c3;
+              mma_u8s8(c0, c1, c2, c3, qa[c].x & mk, qb[c].x & mk, qa[c].y & mk, qb[c].y & mk, bf.x, bf.y);
+              (void)c1; (void)c3;
+              const int scA = (int)__byte_perm(sb < 4 ? sa.sc03 : sa.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
+              const int scB = (int)__byte_perm(sb < 4 ? sb_.sc03 : sb_.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
+              if (hi) { accAh += scA * c0; accBh += scB * c2; }
+              else { accA += scA * c0; accB += scB * c2; }
             }
           }
           const float xs = sm_xscale[b];
           const float2 dA = q4k_d_dmin(ha.x), dB = q4k_d_dmin(hb.x);
-          const float fa = fmaf((float)accA1, w1, (float)accA0 * w0);
-          const float fb = fmaf((float)accB1, w1, (float)accB0 * w0);
+          const float fa = (float)(accA + (accAh >> 4)) * wt;
+          const float fb = (float)(accB + (accBh >> 4)) * wt;
           const float s0 = sm_ssum[b * 8 + 2 * t], s1 = sm_ssum[b * 8 + 2 * t + 1];
           const uint32_t mwA = t < 2 ? sa.mn03 : sa.mn47, mwB = t < 2 ? sb_.mn03 : sb_.mn47;
           const int sh = (t & 1) * 16;
