@@ -204,6 +204,7 @@ dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void 
 #include <cstdlib>
 
 #define TG_CONSUMERS 8  // warps per consumer group (one per super-block column of a chunk)
+#define TG_MAX_BW 2     // super-block columns of a stage per consumer warp: a stage holds at most 16 blocks per row
 #define TG_ROW_PAD 32
 #define TG_RED_SLOTS 16
 
@@ -432,20 +433,36 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
         const int s = (int)(u % (uint32_t)stages);
         const uint32_t n = u / (uint32_t)stages;
         if (!mbar_wait_bounded(full_bar(s), n & 1u, abort_flag)) { ok = false; break; }
-        for (int bw = warp; bw < cb; bw += TG_CONSUMERS) {
-          const int b = ch * cb + bw;
-          const uint8_t *pa = smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)g * L.row_stride + (uint32_t)bw * Q4K_BLOCK_BYTES;
-          const uint8_t *pb = pa + 8u * L.row_stride;
-          const uint4 ha = *reinterpret_cast<const uint4 *>(pa);
-          const uint4 hb = *reinterpret_cast<const uint4 *>(pb);
-          uint2 qa[4], qb[4];
+        // Phase 1: pull this warp's share of the stage (up to TG_MAX_BW super-block columns of the 16 rows)
+        // into registers and hand the stage back to the producer at once.  The arithmetic below then runs
+        // while the ring slot is already being refilled, so nearly the whole ring stays in flight.
+        uint4 ha[TG_MAX_BW], hb[TG_MAX_BW];
+        uint2 qa[TG_MAX_BW][4], qb[TG_MAX_BW][4];
 #pragma unroll
-          for (int c = 0; c < 4; c++) {
-            qa[c] = *reinterpret_cast<const uint2 *>(pa + 16 + 32 * c + 8 * t);
-            qb[c] = *reinterpret_cast<const uint2 *>(pb + 16 + 32 * c + 8 * t);
+        for (int i = 0; i < TG_MAX_BW; i++) {
+          const int bw = warp + i * TG_CONSUMERS;
+          if (bw < cb) {
+            const uint8_t *pa = smem + L.stages + (uint32_t)s * L.stage_bytes + (uint32_t)g * L.row_stride + (uint32_t)bw * Q4K_BLOCK_BYTES;
+            const uint8_t *pb = pa + 8u * L.row_stride;
+            ha[i] = *reinterpret_cast<const uint4 *>(pa);
+            hb[i] = *reinterpret_cast<const uint4 *>(pb);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              qa[i][c] = *reinterpret_cast<const uint2 *>(pa + 16 + 32 * c + 8 * t);
+              qb[i][c] = *reinterpret_cast<const uint2 *>(pb + 16 + 32 * c + 8 * t);
+            }
           }
-          const Q4KScales sa = q4k_unpack_scales(ha.y, ha.z, ha.w);
-          const Q4KScales sb_ = q4k_unpack_scales(hb.y, hb.z, hb.w);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+        // Phase 2: arithmetic from registers
+#pragma unroll
+        for (int i = 0; i < TG_MAX_BW; i++) {
+          const int bw = warp + i * TG_CONSUMERS;
+          if (bw >= cb) break;
+          const int b = ch * cb + bw;
+          const Q4KScales sa = q4k_unpack_scales(ha[i].y, ha[i].z, ha[i].w);
+          const Q4KScales sb_ = q4k_unpack_scales(hb[i].y, hb[i].z, hb[i].w);
           const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 8 * 128) + (g >> 1) * 4 + t;
           // odd sub-blocks are the high nibbles: they stay in place (16 * q as a u8), their sums are
           // accumulated apart and divided by 16 exactly at the end, which saves the four shifts per MMA
@@ -459,7 +476,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
               if (limb_lane) bf = lb[sb * 16];
               const uint32_t mk = hi ? M4H : M4;
               int c0, c1, c2, c3;
-              mma_u8s8(c0, c1, c2, c3, qa[c].x & mk, qb[c].x & mk, qa[c].y & mk, qb[c].y & mk, bf.x, bf.y);
+              mma_u8s8(c0, c1, c2, c3, qa[i][c].x & mk, qb[i][c].x & mk, qa[i][c].y & mk, qb[i][c].y & mk, bf.x, bf.y);
               (void)c1; (void)c3;
               const int scA = (int)__byte_perm(sb < 4 ? sa.sc03 : sa.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
               const int scB = (int)__byte_perm(sb < 4 ? sb_.sc03 : sb_.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
@@ -468,7 +485,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
             }
           }
           const float xs = sm_xscale[b];
-          const float2 dA = q4k_d_dmin(ha.x), dB = q4k_d_dmin(hb.x);
+          const float2 dA = q4k_d_dmin(ha[i].x), dB = q4k_d_dmin(hb[i].x);
           const float fa = (float)(accA + (accAh >> 4)) * wt;
           const float fb = (float)(accB + (accBh >> 4)) * wt;
           const float s0 = sm_ssum[b * 8 + 2 * t], s1 = sm_ssum[b * 8 + 2 * t + 1];
@@ -479,8 +496,6 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
           resA = fmaf(xs, fmaf(dA.x, fa, -dA.y * mA), resA);
           resB = fmaf(xs, fmaf(dB.x, fb, -dB.y * mB), resB);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
       }
       if (!ok) break;
       // sum the eight warps' partial rows through a ring of reduction slots
@@ -519,7 +534,7 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   if (limit < 0) { const char *e = getenv("DP_GEMV_STAGE_KB"); limit = (e ? atoi(e) : 56) * 1024; }
   int cb = 0;
   for (int c = bpr; c >= 1; c--)
-    if (bpr % c == 0 && 16 * (c * Q4K_BLOCK_BYTES + TG_ROW_PAD) <= limit) { cb = c; break; }
+    if (bpr % c == 0 && c <= TG_MAX_BW * TG_CONSUMERS && 16 * (c * Q4K_BLOCK_BYTES + TG_ROW_PAD) <= limit) { cb = c; break; }
   if (cb == 0) return false;
   static int budget_kb = -1;
   if (budget_kb < 0) { const char *e = getenv("DP_GEMV_SMEM_KB"); budget_kb = e ? atoi(e) : 227; }
@@ -565,7 +580,7 @@ static int gemv_variant() {
   if (v < 0) {
     const char *e = getenv("DP_GEMV_VARIANT");
     v = e ? atoi(e) : 2;
-    if (v < 0 || v > 3) v = 2;
+    if (v < 0 || v > 2) v = 2;
   }
   return v;
 }
@@ -581,7 +596,6 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
   GemvSource gs{};
   if (y_dtype == DP_F32) {
     if (variant == 1) DP_TRY((launch_tma<float, 1, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
-    else if (variant == 3) DP_TRY((launch_tma<float, 3, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
     else DP_TRY((launch_tma<float, 2, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
   } else {
     if (variant == 1) DP_TRY((launch_tma<__half, 1, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
