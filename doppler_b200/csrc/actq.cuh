@@ -36,12 +36,15 @@ __device__ __forceinline__ void actq_emit_block(const float v[8], int lane, int 
     d[1][i >> 2] |= (uint32_t)(l1 & 255) << (8 * (i & 3));
     d[2][i >> 2] |= (uint32_t)(l2 & 255) << (8 * (i & 3));
   }
-  const int sb = b * 8 + (lane >> 2);
-  uint2 *dst = reinterpret_cast<uint2 *>(limbs + (size_t)sb * 128) + (lane & 3);
+  // Digit layout per block (1024 bytes): four chunks (sub-block pairs) of eight 32-byte columns; column
+  // 2*limb + (sub-block & 1) holds that limb of that sub-block, columns 6 and 7 are never read.  A lane of
+  // the GEMV that loads column g of a chunk once has the B operand of both MMAs of the chunk.
+  const int sbl = lane >> 2;
+  const int sb = b * 8 + sbl;
+  uint2 *dst = reinterpret_cast<uint2 *>(limbs + (size_t)b * 1024 + (size_t)(sbl >> 1) * 256 + (size_t)(sbl & 1) * 32) + (lane & 3);
   dst[0] = make_uint2(d[0][0], d[0][1]);
-  dst[4] = make_uint2(d[1][0], d[1][1]);
-  dst[8] = make_uint2(d[2][0], d[2][1]);
-  dst[12] = make_uint2(0u, 0u);
+  dst[8] = make_uint2(d[1][0], d[1][1]);
+  dst[16] = make_uint2(d[2][0], d[2][1]);
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
   if ((lane & 3) == 0) ssum[sb] = (float)s;

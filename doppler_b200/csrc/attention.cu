@@ -315,10 +315,17 @@ static bool use_tc(dp_ctx *ctx, const dpk_attn_params &p, int *gt) {
   return mode && dpk_attention_tc_eligible(p, gt);
 }
 
+// whether a call with these parameters runs on the tensor-core kernel (the decode schedule asks before it
+// hands the kernel the QK-norm / RoPE / KV-append fusion)
+bool dpk_attention_uses_tc(dp_ctx *ctx, const dpk_attn_params &p) {
+  int gt = 0;
+  return use_tc(ctx, p, &gt);
+}
+
 // splits for the tensor-core kernel: fewest whole waves of (two CTAs per SM) x keys per CTA
 static int tc_splits(dp_ctx *ctx, const dpk_attn_params &p, int gt) {
   const int G = p.num_heads / p.num_kv_heads;
-  const long base = (long)p.batch * p.num_kv_heads * (G / gt);
+  const long base = (long)p.batch * p.seq_len * p.num_kv_heads * (G / gt);
   const long slots = (long)ctx->sm_count * 2;
   long best = 1, best_cost = -1;
   for (long s = 1; s <= 32; s++) {
@@ -338,7 +345,7 @@ size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *s
   if (use_tc(ctx, p, &gt)) {
     const int s = tc_splits(ctx, p, gt);
     *splits_out = s;
-    return s == 1 ? 0 : (size_t)p.batch * p.num_heads * s * (p.head_dim + 2) * sizeof(float);
+    return s == 1 ? 0 : (size_t)p.batch * p.seq_len * p.num_heads * s * (p.head_dim + 2) * sizeof(float);
   }
   const bool fast = fast_shape(p, &gt);
   const int G = p.num_heads / p.num_kv_heads;

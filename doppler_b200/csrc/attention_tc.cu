@@ -69,14 +69,14 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y % head_tiles;
-  const int b = blockIdx.z;  // seq_len == 1: one query row per sequence
+  const int z = blockIdx.z, b = z / p.seq_len, qi = z % p.seq_len;  // one query row per CTA (prefill rows are independent)
   const int G = p.num_heads / p.num_kv_heads;
   const int h0 = kvh * G + ht * gt;
 
   int kv_len = p.kv_lens ? p.kv_lens[b] : p.kv_len;
   int lo = 0, hi = kv_len;
   {
-    const int abs_q = p.start_pos;
+    const int abs_q = p.start_pos + qi;
     if (p.causal) { const int lim = abs_q - p.kv_start + 1; if (lim < hi) hi = lim; }
     if (p.sliding_window > 0 && abs_q >= p.sliding_window) { const int first = abs_q - p.sliding_window + 1 - p.kv_start; if (first > lo) lo = first; }
     if (hi < lo) hi = lo;
@@ -91,23 +91,60 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
   const bool capped = p.softcap > 0.0f;
   const float qmul = capped ? p.scale : p.scale * LOG2E;
 
-  // A fragments of Q for every k-step: rows g (hi) and g+8 (lo)
+  // A fragments of Q for every k-step: rows g (hi) and g+8 (lo).  This lane owns dims 16ks + 2t + {0,1,8,9}.
+  const bool fused = p.fuse.qkv != nullptr;
+  const int new_pos = fused ? p.fuse.pos[b] : -1;  // the key that is not in the cache yet
   uint32_t qa[KS][4];
-#pragma unroll
-  for (int ks = 0; ks < KS; ks++) {
+  {
+    float x[KS][4];
     if (g < gt) {
-      const float *qp = p.q + ((size_t)b * p.num_heads + h0 + g) * D + 16 * ks + 2 * t;
-      const float2 x0 = *reinterpret_cast<const float2 *>(qp);
-      const float2 x1 = *reinterpret_cast<const float2 *>(qp + 8);
-      const __half2 h0v = __floats2half2_rn(x0.x * qmul, x0.y * qmul);
-      const __half2 h1v = __floats2half2_rn(x1.x * qmul, x1.y * qmul);
+      const float *qrow = fused ? p.fuse.qkv + ((size_t)b * (p.fuse.nh + 2 * p.fuse.nkv) + h0 + g) * D
+                                : p.q + ((size_t)z * p.num_heads + h0 + g) * D;
+#pragma unroll
+      for (int ks = 0; ks < KS; ks++) {
+        const float2 x0 = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * t);
+        const float2 x1 = *reinterpret_cast<const float2 *>(qrow + 16 * ks + 2 * t + 8);
+        x[ks][0] = x0.x; x[ks][1] = x0.y; x[ks][2] = x1.x; x[ks][3] = x1.y;
+      }
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < KS; ks++) x[ks][0] = x[ks][1] = x[ks][2] = x[ks][3] = 0.0f;
+    }
+    if (fused) {
+      // per-head RMSNorm (rmsnorm_qk.wgsl:75-118) and rotate-half RoPE (rope.wgsl:62-106): the four lanes
+      // of a head hold all its dims, and the partner of dim d (d + D/2) sits KS/2 k-steps further in the
+      // same lane
+      float ss = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) ss = fmaf(x[ks][j], x[ks][j], ss);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float inv = 1.0f / sqrtf(ss / (float)D + p.fuse.eps);
+      constexpr int HALF = D / 2;
+      if (g < gt) {
+#pragma unroll
+        for (int ks = 0; ks < KS / 2; ks++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int d = 16 * ks + 2 * t + (j & 1) + (j >> 1) * 8;
+            const float a = x[ks][j] * inv * p.fuse.q_norm[d], bb = x[ks + KS / 2][j] * inv * p.fuse.q_norm[d + HALF];
+            const float c = p.fuse.cos_t[(size_t)new_pos * HALF + d], sn = p.fuse.sin_t[(size_t)new_pos * HALF + d];
+            x[ks][j] = a * c - bb * sn;
+            x[ks + KS / 2][j] = a * sn + bb * c;
+          }
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+      const __half2 h0v = __floats2half2_rn(x[ks][0] * qmul, x[ks][1] * qmul);
+      const __half2 h1v = __floats2half2_rn(x[ks][2] * qmul, x[ks][3] * qmul);
       const float2 f0 = __half22float2(h0v), f1 = __half22float2(h1v);
       qa[ks][0] = atc_pack(h0v);
-      qa[ks][1] = atc_pack(__floats2half2_rn(x0.x * qmul - f0.x, x0.y * qmul - f0.y));
+      qa[ks][1] = atc_pack(__floats2half2_rn(x[ks][0] * qmul - f0.x, x[ks][1] * qmul - f0.y));
       qa[ks][2] = atc_pack(h1v);
-      qa[ks][3] = atc_pack(__floats2half2_rn(x1.x * qmul - f1.x, x1.y * qmul - f1.y));
-    } else {
-      qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+      qa[ks][3] = atc_pack(__floats2half2_rn(x[ks][2] * qmul - f1.x, x[ks][3] * qmul - f1.y));
     }
   }
 
@@ -133,7 +170,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
       const int piece = c * 32 + lane;
       const int key = piece / CH, ch = piece % CH;
       const int kk = key0 + key;
-      const bool ok = kk < k_end;
+      const bool ok = kk < k_end && kk != new_pos;  // the new token's row is built in place below
       const size_t off = (size_t)(ok ? kk : k_begin) * row_stride + ch * 8;
       const uint32_t dst = sK + key * ROWB + ((ch ^ (key & 7)) << 4);
       atc_cp_async16(dst, kbase + off, ok ? 16 : 0);          // rows past the range are zero filled
@@ -159,6 +196,45 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
     const int stage = i % ATC_STAGES;
     const uint32_t sK = ring_u32 + stage * STAGE, sV = sK + TILE;
     const int key0 = k_begin + (warp + i * ATC_WARPS) * 16;
+    if (fused && new_pos >= key0 && new_pos < key0 + 16 && new_pos < k_end) {
+      // This warp's block holds the position of the new token: build its K row (per-head RMSNorm + RoPE,
+      // rounded to f16 as the cache write does) and V row, put them into the stage and, once per KV head,
+      // append them to the cache (kv_cache_write_f32_to_f16.wgsl:19).
+      constexpr int HALF = D / 2, PER = HALF / 32;
+      const int heads_all = p.fuse.nh + 2 * p.fuse.nkv;
+      const float *ksrc = p.fuse.qkv + ((size_t)b * heads_all + p.fuse.nh + kvh) * D;
+      const float *vsrc = ksrc + (size_t)p.fuse.nkv * D;
+      float k0[PER], k1[PER], v0[PER], v1[PER];
+      float ss = 0.0f;
+#pragma unroll
+      for (int e = 0; e < PER; e++) {
+        k0[e] = ksrc[lane + 32 * e]; k1[e] = ksrc[lane + 32 * e + HALF];
+        v0[e] = vsrc[lane + 32 * e]; v1[e] = vsrc[lane + 32 * e + HALF];
+        ss = fmaf(k0[e], k0[e], fmaf(k1[e], k1[e], ss));
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+      const float inv = 1.0f / sqrtf(ss / (float)D + p.fuse.eps);
+      unsigned char *rowK = ring + (size_t)stage * STAGE + (size_t)(new_pos - key0) * ROWB, *rowV = rowK + TILE;
+      const int rsw = (new_pos - key0) & 7;
+      __half *kdst = p.fuse.kc + (size_t)b * p.kv_batch_stride + ((size_t)new_pos * p.num_kv_heads + kvh) * D;
+      __half *vdst = p.fuse.vc + (size_t)b * p.kv_batch_stride + ((size_t)new_pos * p.num_kv_heads + kvh) * D;
+#pragma unroll
+      for (int e = 0; e < PER; e++) {
+        const int d = lane + 32 * e;
+        const float a = k0[e] * inv * p.fuse.k_norm[d], bb = k1[e] * inv * p.fuse.k_norm[d + HALF];
+        const float c = p.fuse.cos_t[(size_t)new_pos * HALF + d], sn = p.fuse.sin_t[(size_t)new_pos * HALF + d];
+        const __half ka = __float2half_rn(a * c - bb * sn), kb = __float2half_rn(a * sn + bb * c);
+        const __half va = __float2half_rn(v0[e]), vb = __float2half_rn(v1[e]);
+        const int d2 = d + HALF;
+        *reinterpret_cast<__half *>(rowK + ((((d >> 3) ^ rsw)) << 4) + (d & 7) * 2) = ka;
+        *reinterpret_cast<__half *>(rowK + ((((d2 >> 3) ^ rsw)) << 4) + (d2 & 7) * 2) = kb;
+        *reinterpret_cast<__half *>(rowV + ((((d >> 3) ^ rsw)) << 4) + (d & 7) * 2) = va;
+        *reinterpret_cast<__half *>(rowV + ((((d2 >> 3) ^ rsw)) << 4) + (d2 & 7) * 2) = vb;
+        if (ht == 0) { kdst[d] = ka; kdst[d2] = kb; vdst[d] = va; vdst[d2] = vb; }
+      }
+      __syncwarp();
+    }
 
     // ---- scores of 16 keys for head g: s[2nb], s[2nb+1] = keys 8nb+2t, 8nb+2t+1 ----
     float s[4];
@@ -265,19 +341,20 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
     }
     const int h = h0 + hh;
     if (splits == 1) {
-      p.out[((size_t)b * p.num_heads + h) * D + d] = ll > 0.0f ? acc / ll : 0.0f;
+      p.out[((size_t)z * p.num_heads + h) * D + d] = ll > 0.0f ? acc / ll : 0.0f;
     } else {
-      float *pp = part + (((size_t)b * p.num_heads + h) * splits + split) * (D + 2);
+      float *pp = part + (((size_t)z * p.num_heads + h) * splits + split) * (D + 2);
       pp[d] = acc;
       if (d == 0) { pp[D] = mm; pp[D + 1] = ll; }
     }
   }
 }
 
-// Shapes the tensor-core kernel takes: one query row per sequence, head_dim 64 or 128, GQA
-// groups of up to 8 heads (or a multiple of 8), 16-byte aligned rows.
+// Shapes the tensor-core kernel takes: head_dim 64 or 128, GQA groups of up to 8 heads (or a multiple
+// of 8), 16-byte aligned rows.  Every query row (decode: one per sequence; prefill: seq_len per
+// sequence, each with its own causal limit) is one grid.z slice.
 bool dpk_attention_tc_eligible(const dpk_attn_params &p, int *gt_out) {
-  if (p.seq_len != 1) return false;
+  if (p.seq_len < 1) return false;
   if (p.head_dim != 128 && p.head_dim != 64) return false;
   if (p.num_kv_heads <= 0 || p.num_heads % p.num_kv_heads) return false;
   const int G = p.num_heads / p.num_kv_heads;
@@ -298,7 +375,7 @@ static dp_status launch_tc(dp_ctx *ctx, const dpk_attn_params &p, float *scratch
   const int head_tiles = G / gt;
   const size_t smem = (size_t)ATC_WARPS * ATC_STAGES * 2 * 16 * D * 2;
   DP_CUDA(ctx, cudaFuncSetAttribute(attn_tc_kernel<D, PLO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(splits, p.num_kv_heads * head_tiles, p.batch);
+  dim3 grid(splits, p.num_kv_heads * head_tiles, p.batch * p.seq_len);
   DP_LAUNCH(ctx, (attn_tc_kernel<D, PLO>), grid, ATC_THREADS, smem, p, scratch, splits, head_tiles, gt);
   return DP_OK;
 }

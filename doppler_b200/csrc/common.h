@@ -166,7 +166,21 @@ dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_
                         dp_dtype c_dtype, int M, int N, int K, float alpha);
 dp_status dpk_gemv_f32w(dp_ctx *ctx, const float *W, const float *A, float *C, int M, int N, int K,
                         float alpha);
+// Optional fusion of the decode step's per-head QK RMSNorm + RoPE + KV append into the attention
+// kernel (tensor-core kernel, one new token per sequence).  qkv holds the raw projections
+// [sequence][nh q heads | nkv k heads | nkv v heads][head_dim]; the kernel normalises and rotates its
+// own q heads, and the CTA whose key range ends at the new position builds the new K/V row, uses it
+// and appends it to the cache (kc / vc, same layout and batch stride as k / v).
+struct dpk_attn_fuse {
+  const float *qkv = nullptr;
+  const float *q_norm = nullptr, *k_norm = nullptr, *cos_t = nullptr, *sin_t = nullptr;
+  const int *pos = nullptr;  // position of the new token of each sequence
+  __half *kc = nullptr, *vc = nullptr;
+  float eps = 0.0f;
+  int nh = 0, nkv = 0;
+};
 struct dpk_attn_params {
+  dpk_attn_fuse fuse;
   const float *q;
   const __half *k, *v;
   float *out;
@@ -177,6 +191,7 @@ struct dpk_attn_params {
   const int *kv_lens;
 };
 dp_status dpk_attention(dp_ctx *ctx, const dpk_attn_params &p);
+bool dpk_attention_uses_tc(dp_ctx *ctx, const dpk_attn_params &p);
 // variant with caller-provided scratch (no allocation); scratch_bytes must cover dpk_attention_scratch_bytes
 size_t dpk_attention_scratch_bytes(dp_ctx *ctx, const dpk_attn_params &p, int *splits_out);
 dp_status dpk_attention_with_scratch(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);

@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_q4k_mma_kernel(
     }
     const Q4KScales sa = q4k_unpack_scales(ha.y, ha.z, ha.w);
     const Q4KScales sb_ = q4k_unpack_scales(hb.y, hb.z, hb.w);
-    const uint2 *lb = reinterpret_cast<const uint2 *>(limbs + (size_t)b * 8 * 128) + g * 4 + t;
+    const uint2 *lb = reinterpret_cast<const uint2 *>(limbs + (size_t)b * 1024) + t;  // digit layout: actq.cuh
     int accA0 = 0, accA1 = 0, accB0 = 0, accB1 = 0;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_q4k_mma_kernel(
       for (int hi = 0; hi < 2; hi++) {
         const int sb = 2 * c + hi;
         uint2 bf = make_uint2(0u, 0u);
-        if (g < 3) bf = __ldg(lb + sb * 16);
+        if (g < 3) bf = __ldg(lb + c * 32 + (2 * g + hi) * 4);
         const uint32_t a0 = hi ? (qa[c].x >> 4) & M4 : qa[c].x & M4;
         const uint32_t a1 = hi ? (qb[c].x >> 4) & M4 : qb[c].x & M4;
         const uint32_t a2 = hi ? (qa[c].y >> 4) & M4 : qa[c].y & M4;
@@ -418,10 +418,10 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
   } else {
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
-    // The three activation limbs sit in the even columns 0, 2, 4 of the MMA's B operand, so every lane
-    // finds its limb in accumulator registers c0 (row g) and c2 (row g+8); c1 / c3 are never read.
+    // B operand columns 2l and 2l+1 carry activation limb l (of the even / odd sub-block of a chunk), so
+    // lane t reads limb t from its accumulator registers (columns 2t and 2t+1); t == 3 holds nothing.
     const float wt = t == 0 ? 1.0f : (t == 1 ? 256.0f : (t == 2 ? 65536.0f : 0.0f));
-    const bool limb_lane = (g & 1) == 0 && g < 6;  // B fragment column g carries limb g/2
+    const bool limb_lane = g < 6;  // B fragment columns 6 and 7 are zero
     const uint32_t M4 = 0x0f0f0f0fu, M4H = 0xf0f0f0f0u;
     uint32_t tile_no = (uint32_t)group;
     bool ok = true;
@@ -463,26 +463,27 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
           const int b = ch * cb + bw;
           const Q4KScales sa = q4k_unpack_scales(ha[i].y, ha[i].z, ha[i].w);
           const Q4KScales sb_ = q4k_unpack_scales(hb[i].y, hb[i].z, hb[i].w);
-          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 8 * 128) + (g >> 1) * 4 + t;
-          // odd sub-blocks are the high nibbles: they stay in place (16 * q as a u8), their sums are
-          // accumulated apart and divided by 16 exactly at the end, which saves the four shifts per MMA
+          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 1024) + g * 4 + t;  // column g of a chunk
+          // One B fragment per chunk serves both of its MMAs: even columns carry the limbs of sub-block 2c
+          // (low nibbles, read back from c0 / c2), odd columns those of sub-block 2c+1 (high nibbles, c1 / c3).
+          // The high nibbles stay in place (16 * q as a u8); their sums are accumulated apart and divided
+          // by 16 exactly at the end, which saves the four shifts per MMA.
           int accA = 0, accB = 0, accAh = 0, accBh = 0;
 #pragma unroll
           for (int c = 0; c < 4; c++) {
-#pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-              const int sb = 2 * c + hi;
-              uint2 bf = make_uint2(0u, 0u);
-              if (limb_lane) bf = lb[sb * 16];
-              const uint32_t mk = hi ? M4H : M4;
-              int c0, c1, c2, c3;
-              mma_u8s8(c0, c1, c2, c3, qa[i][c].x & mk, qb[i][c].x & mk, qa[i][c].y & mk, qb[i][c].y & mk, bf.x, bf.y);
-              (void)c1; (void)c3;
-              const int scA = (int)__byte_perm(sb < 4 ? sa.sc03 : sa.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
-              const int scB = (int)__byte_perm(sb < 4 ? sb_.sc03 : sb_.sc47, 0u, 0x4440u + (uint32_t)(sb & 3));
-              if (hi) { accAh += scA * c0; accBh += scB * c2; }
-              else { accA += scA * c0; accB += scB * c2; }
-            }
+            uint2 bf = make_uint2(0u, 0u);
+            if (limb_lane) bf = lb[c * 32];
+            int c0, c1, c2, c3;
+            mma_u8s8(c0, c1, c2, c3, qa[i][c].x & M4, qb[i][c].x & M4, qa[i][c].y & M4, qb[i][c].y & M4, bf.x, bf.y);
+            (void)c1; (void)c3;
+            const uint32_t wsa = c < 2 ? sa.sc03 : sa.sc47, wsb = c < 2 ? sb_.sc03 : sb_.sc47;
+            accA += (int)__byte_perm(wsa, 0u, 0x4440u + (uint32_t)((2 * c) & 3)) * c0;
+            accB += (int)__byte_perm(wsb, 0u, 0x4440u + (uint32_t)((2 * c) & 3)) * c2;
+            int h0, h1, h2, h3;
+            mma_u8s8(h0, h1, h2, h3, qa[i][c].x & M4H, qb[i][c].x & M4H, qa[i][c].y & M4H, qb[i][c].y & M4H, bf.x, bf.y);
+            (void)h0; (void)h2;
+            accAh += (int)__byte_perm(wsa, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h1;
+            accBh += (int)__byte_perm(wsb, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h3;
           }
           const float xs = sm_xscale[b];
           const float2 dA = q4k_d_dmin(ha[i].x), dB = q4k_d_dmin(hb[i].x);
@@ -508,7 +509,9 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
       if (t == 0) { rs[warp * 16 + g] = resA; rs[warp * 16 + g + 8] = resB; }
       __syncwarp();
       if (lane == 0) mbar_arrive(red_bar(slot));
-      if (warp == 0) {
+      // The reducing warp of group g is warp g+1: with 17 warps on four schedulers the producer (warp 16)
+      // shares scheduler 0 with consumer warps 0, 4, 8, 12; the extra work goes to other schedulers.
+      if (warp == group + 1) {
         if (!mbar_wait_bounded(red_bar(slot), (tile_no / TG_RED_SLOTS) & 1u, abort_flag)) { ok = false; break; }
         if (lane < 16) {
           float v = 0.0f;

@@ -74,6 +74,7 @@ struct dp_model {
   // 9B-shaped step it costs more than it saves (2.113 ms with, 2.082 ms without; the prefetch traffic
   // lands on the current kernel's tail).
   bool prefetch_next = false;
+  bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel (DP_ATTN_FUSE_QK=0: separate kernel)
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
   int graph_batch[2] = {0, 0};
@@ -421,6 +422,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   dp_model *m = new dp_model();
   m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
   if (const char *e = getenv("DP_GEMV_PREFETCH")) m->prefetch_next = atoi(e) != 0;
+  if (const char *e = getenv("DP_ATTN_FUSE_QK")) m->fuse_qk = atoi(e) != 0;
   if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
   DP_CHECK(ctx, m->cfg.max_batch <= 256, "model: max_batch %d > 256", m->cfg.max_batch);
   m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
@@ -697,14 +699,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       }
       DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, emit));
     }
-    // ---- per-head QK norm, RoPE, KV append ----
-    {
-      const int warps = tokens * heads;
-      DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
-                (__half *)m->vc[l]->dptr, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin, decode ? m->d_pos : nullptr,
-                start_pos, seq, tokens, m->nh, m->nkv, D, c.eps, kv_seq_stride);
-    }
-    // ---- attention ----
+    // ---- attention parameters ----
     dpk_attn_params ap{};
     ap.q = m->q; ap.out = m->att;
     ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
@@ -721,6 +716,21 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       ap.batch = 1; ap.seq_len = tokens; ap.kv_len = start_pos + tokens; ap.causal = 1; ap.start_pos = start_pos;
       ap.kv_batch_stride = 0; ap.kv_lens = nullptr;
       splits = 1;
+    }
+    // ---- per-head QK norm, RoPE, KV append ----
+    // Decode on the tensor-core attention kernel: that kernel does it itself (one launch less per layer).
+    if (decode && m->fuse_qk && dpk_attention_uses_tc(ctx, ap)) {
+      ap.fuse.qkv = m->qkv;
+      ap.fuse.q_norm = L.q_norm; ap.fuse.k_norm = L.k_norm;
+      ap.fuse.cos_t = m->rope_cos; ap.fuse.sin_t = m->rope_sin;
+      ap.fuse.pos = m->d_pos;
+      ap.fuse.kc = (__half *)m->kc[l]->dptr; ap.fuse.vc = (__half *)m->vc[l]->dptr;
+      ap.fuse.eps = c.eps; ap.fuse.nh = m->nh; ap.fuse.nkv = m->nkv;
+    } else {
+      const int warps = tokens * heads;
+      DP_LAUNCH(ctx, qk_norm_rope_kv_kernel, (warps + 7) / 8, 256, 0, m->qkv, m->q, (__half *)m->kc[l]->dptr,
+                (__half *)m->vc[l]->dptr, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin, decode ? m->d_pos : nullptr,
+                start_pos, seq, tokens, m->nh, m->nkv, D, c.eps, kv_seq_stride);
     }
     float *o_dst = p == 1 ? m->h : m->partial;
     const float *o_res = p == 1 ? m->h : nullptr;

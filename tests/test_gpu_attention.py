@@ -154,6 +154,18 @@ def test_prefill_causal(dev):
     assert_close(got, exp, "prefill attention, causal with startPos")
 
 
+@pytest.mark.parametrize("H,Hkv,D,T,start", [(32, 8, 128, 130, 0), (8, 8, 64, 33, 17), (16, 2, 128, 64, 500)])
+def test_prefill_rows_on_tensor_cores(dev, H, Hkv, D, T, start):
+    """seq_len > 1: every query row is its own causal problem (attention_streaming_f16kv.wgsl:96)"""
+    s = synthetic.key(57, H * 1000 + T)
+    kv = start + T
+    q = synthetic.normal_f32(s, T * H * D)
+    k16, v16 = synthetic.normal_f16(s + 1, kv * Hkv * D), synthetic.normal_f16(s + 2, kv * Hkv * D)
+    got = _attn(dev, q, k16, v16, H, D, seq_len=T, kv_len=kv, num_kv_heads=Hkv, causal=True, start_pos=start)
+    exp = O.attention_f16kv(q, k16, v16, T, kv, H, Hkv, D, causal=True, start_pos=start)
+    assert_close(got, exp, f"prefill rows H{H}/Hkv{Hkv}/D{D}/T{T}/start{start}")
+
+
 def test_attention_argument_errors(dev):
     q = dev.tensor_from(np.zeros(8 * 128, np.float32))
     kv = dev.tensor_from(np.zeros(16 * 2 * 128, np.float16))
