@@ -129,9 +129,9 @@ struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
 };
-__host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB) {
+__host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) {
   TcSmem l;
-  l.stage_a = 2u * 128u * 128u;      // two 128-row tiles of 64 f16
+  l.stage_a = (uint32_t)MT * 128u * 128u;  // MT 128-row tiles of 64 f16
   l.stage_b = (uint32_t)BN * 128u;
   l.a = 0;
   l.b = (uint32_t)SA * l.stage_a;
@@ -146,15 +146,18 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB) {
 // weight tile, so each dequantises half of its rows and stores them into BOTH CTAs' shared memory
 // (distributed shared memory); every weight is then dequantised once per 512 rows instead of once per
 // 256.  The tensor-core side is unchanged: each CTA issues its own cta_group::1 MMAs on its own copy.
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, bool PAIR>
+// MT = number of 128-row accumulators per CTA (output tile 128*MT x BN).  MT = 4 with BN = 96 covers 512
+// rows per CTA, so that at M = 512 every weight is dequantised by one CTA only.
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, bool PAIR, int MT = 2>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, float alpha, int *__restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(BN, SA, SB);
+  const TcSmem L = tc_layout(BN, SA, SB, MT);
+  static_assert(MT * BN <= 512, "accumulators exceed tensor memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
   const int bpr = K / QK_K, num_k = K / BK;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
@@ -200,8 +203,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
         mbar_expect_tx(full_a(s), L.stage_a);
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
-        tma_load_2d(dst, &tmap_a, kt * BK, m0, full_a(s));
-        tma_load_2d(dst + 128u * 128u, &tmap_a, kt * BK, m0 + 128, full_a(s));
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, kt * BK, m0 + 128 * mt, full_a(s));
       }
     }
   } else if (warp == 1) {
@@ -221,8 +224,9 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         for (int k16 = 0; k16 < BK / 16; k16++) {
           const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
           const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
-          umma_f16(tmem_base, umma_desc_sw128(a_addr + (uint32_t)k16 * 32u), bdesc, idesc, acc);
-          umma_f16(tmem_base + (uint32_t)BN, umma_desc_sw128(a_addr + 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+#pragma unroll
+          for (int mt = 0; mt < MT; mt++)
+            umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
         umma_commit(empty_a(sa));  // both stages are free once these MMAs have read them
         if constexpr (PAIR) umma_commit_pair(empty_b(sb)); else umma_commit(empty_b(sb));
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       const int half = dw >> 2;          // DQ_WARPS/4 warps share a quarter and split the column groups
       constexpr int GROUPS = BN / 32;
 #pragma unroll 1
-      for (int mt = 0; mt < 2; mt++) {
+      for (int mt = 0; mt < MT; mt++) {
         const int row = m0 + mt * 128 + quad * 32 + lane;
 #pragma unroll 1
         for (int cg = half; cg < GROUPS; cg += DQ_WARPS / 4) {
@@ -415,6 +419,19 @@ dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *
   return DP_OK;
 }
 
+// 512 x 96 tiles (four accumulators): one CTA covers 512 rows, so at M <= 512 each weight is dequantised once
+template <typename OutT>
+dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  constexpr int BN = 96, DQ = 12, SA = 2, SB = 4, MT = 4;
+  const size_t smem = tc_layout(BN, SA, SB, MT).total + 1024;
+  static_assert(MT * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc_kernel<BN, DQ, OutT, SA, SB, false, MT>;
+  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(N / BN, (M + 128 * MT - 1) / (128 * MT));
+  DP_LAUNCH(ctx, kernel, grid, (DQ + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  return DP_OK;
+}
+
 // PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
@@ -447,6 +464,13 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   // DP_GEMM_RINGS=1 selects the deeper weight ring.
   static int rings = -1;
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
+  // DP_GEMM_WIDE_M=1: 512 x 96 tiles when M > 256 (each weight dequantised once per 512 rows).  Off by
+  // default: measured slower (512 x 12288 x 4096: 71.7 us against 65.9 us; M = 2048: 273.8 us against 243 us):
+  // halving the dequantisation does not pay for N = 96 MMAs, which read more shared memory per flop, and
+  // for twice the activation traffic from L2.
+  static int wide_m = -1;
+  if (wide_m < 0) { const char *e = getenv("DP_GEMM_WIDE_M"); wide_m = e ? atoi(e) : 0; }
+  if (wide_m && M > 256 && N % 96 == 0) return launch_tc_wide_m<OutT>(ctx, tm, W, C, M, N, K, alpha);
   // DP_GEMM_PAIR=1: with an even number of 256-row tiles, pairs of CTAs share the dequantisation through
   // distributed shared memory.  Correct (same parity tests), but measured slower on 512 x 12288 x 4096:
   // 101.6 us against 66.5 us, because the proxy fence in front of each stage's arrive has to wait for the

@@ -255,7 +255,11 @@ struct GemvSource {
 
 // GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
 // while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
-template <typename OutT, int GROUPS, int SRC>
+// BREG (rows that fit one ring stage, i.e. one chunk per tile): a consumer warp then meets the same
+// super-block columns in every tile, so it keeps their B fragments (activation digits), block scales
+// and sub-block sums in registers for the whole launch instead of re-reading them from shared memory
+// for every tile.
+template <typename OutT, int GROUPS, int SRC, bool BREG>
 __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 ? 2 : 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
@@ -426,6 +430,27 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
     uint32_t tile_no = (uint32_t)group;
     bool ok = true;
     float *red = reinterpret_cast<float *>(smem + L.red);
+    uint2 bfr[TG_MAX_BW][4];
+    float xsr[TG_MAX_BW], s0r[TG_MAX_BW], s1r[TG_MAX_BW];
+    if constexpr (BREG) {
+#pragma unroll
+      for (int i = 0; i < TG_MAX_BW; i++) {
+        const int b = warp + i * TG_CONSUMERS;  // chunks == 1: block column of the row
+        xsr[i] = s0r[i] = s1r[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; c++) bfr[i][c] = make_uint2(0u, 0u);
+        if (b < cb) {
+          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 1024) + g * 4 + t;
+          if (limb_lane) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) bfr[i][c] = lb[c * 32];
+          }
+          xsr[i] = sm_xscale[b];
+          s0r[i] = sm_ssum[b * 8 + 2 * t];
+          s1r[i] = sm_ssum[b * 8 + 2 * t + 1];
+        }
+      }
+    }
     for (int rt = blockIdx.x + group * gridDim.x; rt < tiles && ok; rt += GROUPS * gridDim.x, tile_no += GROUPS) {
       float resA = 0.0f, resB = 0.0f;
       uint32_t u = tile_no * (uint32_t)chunks;
@@ -472,7 +497,8 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
 #pragma unroll
           for (int c = 0; c < 4; c++) {
             uint2 bf = make_uint2(0u, 0u);
-            if (limb_lane) bf = lb[c * 32];
+            if constexpr (BREG) bf = bfr[i][c];
+            else if (limb_lane) bf = lb[c * 32];
             int c0, c1, c2, c3;
             mma_u8s8(c0, c1, c2, c3, qa[i][c].x & M4, qb[i][c].x & M4, qa[i][c].y & M4, qb[i][c].y & M4, bf.x, bf.y);
             (void)c1; (void)c3;
@@ -485,11 +511,11 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
             accAh += (int)__byte_perm(wsa, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h1;
             accBh += (int)__byte_perm(wsb, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h3;
           }
-          const float xs = sm_xscale[b];
+          const float xs = BREG ? xsr[i] : sm_xscale[b];
           const float2 dA = q4k_d_dmin(ha[i].x), dB = q4k_d_dmin(hb[i].x);
           const float fa = (float)(accA + (accAh >> 4)) * wt;
           const float fb = (float)(accB + (accBh >> 4)) * wt;
-          const float s0 = sm_ssum[b * 8 + 2 * t], s1 = sm_ssum[b * 8 + 2 * t + 1];
+          const float s0 = BREG ? s0r[i] : sm_ssum[b * 8 + 2 * t], s1 = BREG ? s1r[i] : sm_ssum[b * 8 + 2 * t + 1];
           const uint32_t mwA = t < 2 ? sa.mn03 : sa.mn47, mwB = t < 2 ? sb_.mn03 : sb_.mn47;
           const int sh = (t & 1) * 16;
           const float mA = fmaf((float)((mwA >> (sh + 8)) & 0xffu), s1, (float)((mwA >> sh) & 0xffu) * s0);
@@ -550,8 +576,8 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   return true;
 }
 
-template <typename OutT, int GROUPS, int SRC>
-static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
+template <typename OutT, int GROUPS, int SRC, bool BREG>
+static dp_status launch_tma_impl(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
                             uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
   const float *ssum = limbs ? xscale + K / QK_K : nullptr;
@@ -569,12 +595,22 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
   ctx->gemv_next_w = nullptr;  // a hint serves one launch
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, BREG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, BREG>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
             N, K, cb, stages, alpha, residual, ctx->dev_status, src);
   return DP_OK;
+}
+
+template <typename OutT, int GROUPS, int SRC>
+static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
+                            uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
+  // Off by default: measured slower (9B-shaped step 2.007 ms against 1.931 ms; 227 MB matrix 55.0 us against
+  // 52.2 us) because the extra 22 registers per thread push the kernel into spills at its 120-register cap.
+  static const bool breg = [] { const char *e = getenv("DP_GEMV_BREG"); return e ? atoi(e) != 0 : false; }();
+  if (breg && cb == K / QK_K) return launch_tma_impl<OutT, GROUPS, SRC, true>(ctx, W, limbs, y, N, K, cb, stages, smem, alpha, residual, gs);
+  return launch_tma_impl<OutT, GROUPS, SRC, false>(ctx, W, limbs, y, N, K, cb, stages, smem, alpha, residual, gs);
 }
 
 // 0 = plain MMA kernel, 1 / 2 = TMA kernel with one / two consumer groups
