@@ -66,3 +66,28 @@ def test_rope_tables_match_oracle():
     c, s = rope_tables(1e6, 128, 64)
     oc, os_ = O.rope_tables(1e6, 128, 64)
     assert np.array_equal(c, oc) and np.array_equal(s, os_)
+
+
+def test_header_is_plain_c_and_links(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 and as C++ without CUDA headers, and a C
+    program must link against the library (it only asks for the version string: no GPU needed)."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    inc = os.path.join(root, "include")
+    lib_dir = os.path.join(root, "doppler_b200")
+    gcc = shutil.which("gcc", path="/usr/bin") or shutil.which("gcc")
+    gxx = shutil.which("g++", path="/usr/bin") or shutil.which("g++")
+    src = tmp_path / "use_abi.c"
+    src.write_text('#include "doppler_b200.h"\n#include <stdio.h>\n'
+                   'int main(void) { dp_matmul_opts o; dp_matmul_opts_default(&o);\n'
+                   '  printf("%s %d\\n", dp_version(), (int)(o.alpha == 1.0f)); return 0; }\n')
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", inc, str(src)], check=True)
+    cpp = tmp_path / "use_abi.cc"
+    cpp.write_text('#include "doppler_b200.h"\nint main() { return dp_version() ? 0 : 1; }\n')
+    subprocess.run([gxx, "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(cpp)], check=True)
+    exe = tmp_path / "use_abi"
+    subprocess.run([gcc, "-std=c99", "-I", inc, str(src), "-o", str(exe), "-L", lib_dir, "-ldoppler_b200",
+                    f"-Wl,-rpath,{lib_dir}"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
+    assert len(out) >= 2 and out[-1] == "1"
