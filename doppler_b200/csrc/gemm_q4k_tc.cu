@@ -384,6 +384,235 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   if (*abort_flag && tid == 0) atomicExch(err, 2);
 }
 
+// =================================================================================================
+// Two-SM variant: tcgen05.mma.cta_group::2
+// =================================================================================================
+// A cluster of two CTAs owns a 512 x BN output tile.  Each MMA is 256 x BN x 16 across the pair: CTA r
+// holds rows r*128 .. r*128+127 of the 256 in its own tensor memory, supplies those rows of A from its
+// own shared memory and HALF of the B tile (BN/2 weight rows) from its own shared memory; the tensor
+// cores fetch the other half from the peer.  So every CTA dequantises only BN/2 weight rows per K step
+// (a quarter of the 1-SM kernel's work per output), writes half as much B into shared memory, and B is
+// read from shared memory once per pair.  Two passes (rows 0..255 and 256..511 of the tile) share each
+// B stage.  CTA 0 issues all MMAs; all "stage full" barriers live in CTA 0 (CTA 1's TMA and dequant
+// warps signal them across the cluster), "stage free" and "accumulators ready" are multicast to both.
+__device__ __forceinline__ void umma_f16_2sm(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {  // arrives on this barrier offset in both CTAs
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"((uint16_t)3)
+               : "memory");
+}
+// tensor copy into this CTA's shared memory whose completion bytes are counted on a barrier of CTA 0
+__device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+               : "memory");
+}
+
+template <int BN, typename OutT, int SA, int SB>
+__global__ void __launch_bounds__(14 * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
+                                                               OutT *__restrict__ C, int M, int N, int K, float alpha,
+                                                               int *__restrict__ err) {
+  constexpr int DQ_WARPS = 12, HB = BN / 2;  // HB weight rows of the tile are this CTA's
+  static_assert(HB == DQ_WARPS * 8, "one 8-row group per dequant warp");
+  static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const TcSmem L = tc_layout(HB, SA, SB, 2);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();
+  const int n0 = (blockIdx.x >> 1) * BN, m0 = blockIdx.y * 512;
+  const int bpr = K / QK_K, num_k = K / BK;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
+  const uint32_t bars = smem_u32(smem + L.bars);
+  auto full_a = [&](int s) { return bars + 8u * (uint32_t)s; };
+  auto empty_a = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
+  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + s); };
+  auto empty_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + SB + s); };
+  const uint32_t accum_bar = bars + 8u * (uint32_t)(2 * SA + 2 * SB);
+  constexpr uint32_t TMEM_COLS = 512;
+
+  pdl_launch();
+  pdl_wait();
+  if (tid == 0) {
+    for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
+    // "weights full": CTA 0 waits for its own twelve dequant warps plus one arrival relayed from CTA 1,
+    // whose twelve warps arrive on CTA 1's own barrier first (one cross-SM arrive per stage, not twelve)
+    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), rank == 0 ? DQ_WARPS + 1 : DQ_WARPS); mbar_init(empty_b(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates the pair's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem + L.tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist and both allocations are done before anyone signals across
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- activation tiles: this CTA's rows of both passes ----------------
+    if (lane == 0) {
+      for (int kt = 0; kt < num_k; kt++) {
+        const int s = kt % SA;
+        const uint32_t n = (uint32_t)(kt / SA);
+        if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
+        if (rank == 0) mbar_expect_tx(full_a(s), 2u * L.stage_a);  // both CTAs' bytes are counted on CTA 0's barrier
+        const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
+        const uint32_t bar0 = mapa_shared(full_a(s), 0u);
+#pragma unroll
+        for (int ps = 0; ps < 2; ps++) tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, kt * BK, m0 + ps * 256 + (int)rank * 128, bar0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issue: CTA 0 only ----------------
+    if (lane == 0 && rank == 1) {
+      // CTA 1: relay "this CTA's half of the weight stage is written" to CTA 0
+      const uint32_t full_b0 = mapa_shared(full_b(0), 0u);
+      for (int kt = 0; kt < num_k; kt++) {
+        const int sb = kt % SB;
+        if (!mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) break;
+        mbar_arrive_remote(full_b0 + 8u * (uint32_t)sb);
+      }
+    }
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_f16(256, BN);
+      bool ok = true;
+      for (int kt = 0; kt < num_k && ok; kt++) {
+        const int sa = kt % SA, sb = kt % SB;
+        if (!mbar_wait_bounded_cluster(full_a(sa), (uint32_t)(kt / SA) & 1u, abort_flag) ||
+            !mbar_wait_bounded_cluster(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)sa * L.stage_a);
+        const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)sb * L.stage_b);
+#pragma unroll
+        for (int k16 = 0; k16 < BK / 16; k16++) {
+          const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
+          const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
+#pragma unroll
+          for (int ps = 0; ps < 2; ps++)
+            umma_f16_2sm(tmem_base + (uint32_t)(ps * BN), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+        }
+        umma_commit_2sm(empty_a(sa));
+        umma_commit_2sm(empty_b(sb));
+      }
+      if (ok) umma_commit_2sm(accum_bar);
+    }
+  } else {
+    // ---------------- this CTA's half of the weight tile ----------------
+    const int dw = warp - 2;
+    const int r8 = lane & 7, oct = lane >> 3;
+    bool ok = true;
+    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (int)rank * HB + dw * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+    uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(rowp));
+    uint2 qn[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) qn[c] = __ldg(reinterpret_cast<const uint2 *>(rowp + 4 + 8 * c) + oct);
+    for (int kb = 0; kb < bpr && ok; kb++) {
+      const float2 dd = q4k_d_dmin(hdr.x);
+      const Q4KScales sc = q4k_unpack_scales(hdr.y, hdr.z, hdr.w);
+      const uint32_t sh = (uint32_t)(oct & 1) * 16u;
+      const uint32_t scp = ((oct < 2 ? sc.sc03 : sc.sc47) >> sh) & 0xffffu;
+      const uint32_t mnp = ((oct < 2 ? sc.mn03 : sc.mn47) >> sh) & 0xffffu;
+      const float my_sc0 = __fmul_rn(dd.x, q4k_u8_to_float(scp & 0xffu)), my_sc1 = __fmul_rn(dd.x, q4k_u8_to_float(scp >> 8));
+      const float my_mn0 = __fmul_rn(dd.y, q4k_u8_to_float(mnp & 0xffu)), my_mn1 = __fmul_rn(dd.y, q4k_u8_to_float(mnp >> 8));
+      uint2 qcur[4];
+#pragma unroll
+      for (int c = 0; c < 4; c++) qcur[c] = qn[c];
+      if (kb + 1 < bpr) {
+        const uint32_t *blk = rowp + (size_t)(kb + 1) * Q4K_BLOCK_WORDS;
+        hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+#pragma unroll
+        for (int c = 0; c < 4; c++) qn[c] = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * c) + oct);
+      }
+#pragma unroll
+      for (int chunk = 0; chunk < 4; chunk++) {
+        const int kt = kb * 4 + chunk;
+        const int s = kt % SB;
+        const uint32_t n = (uint32_t)(kt / SB);
+        bool stage_free = true;
+        if (n > 0) stage_free = mbar_wait_bounded(empty_b(s), (n - 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }
+        const int src_lane = (chunk << 3) | r8;
+        const float s_lo = __shfl_sync(0xffffffffu, my_sc0, src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1, src_lane);
+        const float m_lo = __shfl_sync(0xffffffffu, my_mn0, src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1, src_lane);
+        const uint2 q = qcur[chunk];
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const uint32_t word = i < 2 ? q.x : q.y;
+          const uint32_t wl = word & 0x0f0f0f0fu, wh = (word >> 4) & 0x0f0f0f0fu;
+          const uint32_t sel0 = (i & 1) ? 0x7442u : 0x7440u, sel1 = (i & 1) ? 0x7443u : 0x7441u;
+          const float ql0 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel0)) - 8388608.0f;
+          const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
+          const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
+          const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
+          const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
+          const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
+          lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
+          hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+        }
+        uint8_t *line = smem + L.b + (uint32_t)s * L.stage_b + (uint32_t)dw * 1024u + (uint32_t)r8 * 128u;
+        *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this CTA's stores -> visible to the tensor cores
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_b(s));
+      }
+    }
+    // ---------------- epilogue: this CTA's 128 rows of both passes ----------------
+    const bool accum_ready = ok && mbar_wait_bounded(accum_bar, 0u, abort_flag);
+    if (__all_sync(0xffffffffu, accum_ready)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int quad = warp & 3, third = dw >> 2;
+      constexpr int GROUPS = BN / 32;
+#pragma unroll 1
+      for (int ps = 0; ps < 2; ps++) {
+        const int row = m0 + ps * 256 + (int)rank * 128 + quad * 32 + lane;
+#pragma unroll 1
+        for (int cg = third; cg < GROUPS; cg += DQ_WARPS / 4) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BN + cg * 32), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (row < M) {
+            OutT *dst = C + (size_t)row * N + n0 + cg * 32;
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
+                                                                   __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * alpha, __uint_as_float(r[i + 2 * j + 1]) * alpha);
+                  pk[j] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or leaves while the peer still uses the pair's resources
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  if (*abort_flag && tid == 0) atomicExch(err, 2);
+}
+
 // f32 -> f16 (round to nearest even), the cast the reference inserts in front of an f16 kernel
 // (src/gpu/kernels/matmul.js:431-450)
 __global__ void cast_f32_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, size_t n) {
@@ -432,6 +661,33 @@ dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W,
   return DP_OK;
 }
 
+// two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
+template <typename OutT, int SA, int SB>
+dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  constexpr int BN = 192;
+  const size_t smem = tc_layout(BN / 2, SA, SB, 2).total + 1024;
+  static_assert(2 * 128 * 128 * SA + (BN / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc2_kernel<BN, OutT, SA, SB>;
+  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (N / BN), (M + 511) / 512);
+  cfg.blockDim = dim3(14 * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  ctx->launches++;
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc2_kernel failed: %s", cudaGetErrorString(e));
+  return DP_OK;
+}
+
 // PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
@@ -464,6 +720,17 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   // DP_GEMM_RINGS=1 selects the deeper weight ring.
   static int rings = -1;
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
+  // DP_GEMM_2SM=1|2|3: tcgen05.mma.cta_group::2 on 512 x 192 pair tiles (M > 256, N a multiple of 192), with
+  // activation / weight rings of 4+7, 3+4 or 5+4 stages.  Parity-green and as fast as the one-SM kernel
+  // (512 x 12288 x 4096: 65.8 us against 65.1 us) although every CTA dequantises half as much: the
+  // dequantisation is not what bounds this GEMM.  Off by default.
+  static int two_sm = -1;
+  if (two_sm < 0) { const char *e = getenv("DP_GEMM_2SM"); two_sm = e ? atoi(e) : 0; }
+  if (two_sm && M > 256 && N % 192 == 0) {
+    if (two_sm == 2) return launch_tc_2sm<OutT, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+    if (two_sm == 3) return launch_tc_2sm<OutT, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_2sm<OutT, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
+  }
   // DP_GEMM_WIDE_M=1: 512 x 96 tiles when M > 256 (each weight dequantised once per 512 rows).  Off by
   // default: measured slower (512 x 12288 x 4096: 71.7 us against 65.9 us; M = 2048: 273.8 us against 243 us):
   // halving the dequantisation does not pay for N = 96 MMAs, which read more shared memory per flop, and

@@ -49,7 +49,7 @@ print("ok")
 @pytest.mark.parametrize("env", [
     {"DP_GEMV_BREG": "1"}, {"DP_GEMV_VARIANT": "0"}, {"DP_GEMV_VARIANT": "1"}, {"DP_GEMV_PREFETCH": "1"},
     {"DP_ATTN_TC": "0"}, {"DP_ATTN_FUSE_QK": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_PAIR": "1"}, {"DP_GEMM_RINGS": "1"},
-    {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"},
+    {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"}, {"DP_GEMM_2SM": "1"},
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_alternative_kernels_stay_correct(tmp_path, env):
     script = tmp_path / "child.py"
