@@ -414,10 +414,10 @@ __device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap 
 }
 
 template <int BN, typename OutT, int SA, int SB>
-__global__ void __launch_bounds__(14 * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
+__global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
                                                                OutT *__restrict__ C, int M, int N, int K, float alpha,
                                                                int *__restrict__ err) {
-  constexpr int DQ_WARPS = 12, HB = BN / 2;  // HB weight rows of the tile are this CTA's
+  constexpr int HB = BN / 2, DQ_WARPS = HB / 8;  // HB weight rows of the tile are this CTA's, one 8-row group per warp
   static_assert(HB == DQ_WARPS * 8, "one 8-row group per dequant warp");
   static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
   extern __shared__ uint8_t smem_raw[];
@@ -662,16 +662,15 @@ dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W,
 }
 
 // two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
-template <typename OutT, int SA, int SB>
+template <typename OutT, int BN, int SA, int SB>
 dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
-  constexpr int BN = 192;
   const size_t smem = tc_layout(BN / 2, SA, SB, 2).total + 1024;
   static_assert(2 * 128 * 128 * SA + (BN / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
   auto kernel = gemm_q4k_tc2_kernel<BN, OutT, SA, SB>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (N / BN), (M + 511) / 512);
-  cfg.blockDim = dim3(14 * 32);
+  cfg.blockDim = dim3((BN / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
@@ -720,16 +719,29 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   // DP_GEMM_RINGS=1 selects the deeper weight ring.
   static int rings = -1;
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
-  // DP_GEMM_2SM=1|2|3: tcgen05.mma.cta_group::2 on 512 x 192 pair tiles (M > 256, N a multiple of 192), with
-  // activation / weight rings of 4+7, 3+4 or 5+4 stages.  Parity-green and as fast as the one-SM kernel
-  // (512 x 12288 x 4096: 65.8 us against 65.1 us) although every CTA dequantises half as much: the
-  // dequantisation is not what bounds this GEMM.  Off by default.
-  static int two_sm = -1;
-  if (two_sm < 0) { const char *e = getenv("DP_GEMM_2SM"); two_sm = e ? atoi(e) : 0; }
-  if (two_sm && M > 256 && N % 192 == 0) {
-    if (two_sm == 2) return launch_tc_2sm<OutT, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
-    if (two_sm == 3) return launch_tc_2sm<OutT, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_2sm<OutT, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
+  // Two-SM kernel (tcgen05.mma.cta_group::2).  On 512 x 256 pair tiles its 256-wide MMAs fetch 8 KB of
+  // operands per SM and 128 cycles instead of 10 KB per 96, and the tensor pipe runs about 1.3x faster per
+  // SM (M = 2048, N = 12288, K = 4096: 203.7 us = 1012 TFLOP/s against 243 us).  It needs whole waves of
+  // 74 clusters to win: at M = 512 its 48 tiles occupy 96 SMs (67.7 us against 65.1 us on 128 SMs), so
+  // the choice compares waves x measured time per tile.  DP_GEMM_2SM=0 never, 4 / 5 always (ring depths
+  // 3+4 / 4+5), 1 / 2 / 3 the 512 x 192 variant (as fast as the one-SM kernel: dequantisation, which it
+  // halves, is not what bounds this GEMM).
+  static int two_sm = -2;
+  if (two_sm == -2) { const char *e = getenv("DP_GEMM_2SM"); two_sm = e ? atoi(e) : -1; }
+  if (two_sm == -1 && M > 256 && N % 256 == 0) {
+    const long clusters = ctx->sm_count / 2, sms = ctx->sm_count;
+    const long waves2 = ((long)(N / 256) * ((M + 511) / 512) + clusters - 1) / clusters;
+    const long waves1 = ((long)(N / bn) * ((M + BM - 1) / BM) + sms - 1) / sms;
+    if (waves2 * 677 < waves1 * 651) return launch_tc_2sm<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+  }
+  if (two_sm >= 4 && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
+    if (two_sm == 5) return launch_tc_2sm<OutT, 256, 4, 5>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_2sm<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+  }
+  if (two_sm >= 1 && two_sm <= 3 && M > 256 && N % 192 == 0) {
+    if (two_sm == 2) return launch_tc_2sm<OutT, 192, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+    if (two_sm == 3) return launch_tc_2sm<OutT, 192, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_2sm<OutT, 192, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
   }
   // DP_GEMM_WIDE_M=1: 512 x 96 tiles when M > 256 (each weight dequantised once per 512 rows).  Off by
   // default: measured slower (512 x 12288 x 4096: 71.7 us against 65.9 us; M = 2048: 273.8 us against 243 us):

@@ -158,3 +158,20 @@ def test_matmul_argument_errors(dev):
     assert dev.pool_stats()["bytes_in_use"] == stats0["bytes_in_use"]  # nothing leaked on the error path
     for b in (small, at.buffer, wb.buffer):
         dev.release_buffer(b)
+
+
+def test_large_m_gemm_takes_the_two_sm_kernel(dev):
+    """M = 2048 on N = 12288 is several waves of tiles: the dispatcher then picks the two-SM kernel
+    (tcgen05.mma.cta_group::2, 512 x 256 pair tiles); a ragged M checks the rows beyond the last tile.
+    Oracle: the reference's tiled prefill kernel rounds the dequantised weight to f16 before the
+    product (fused_matmul_q4_prefill_tiled_f16.wgsl:118-201), so the expectation is the float64 product
+    with f16-rounded weights, at the 1e-3 gate; against exact weights the same output differs by up to
+    4e-3 of the rms at K = 512 (both tensor-core kernels give bit-identical results)."""
+    N, K = 12288, 512
+    W = synthetic.q4k_matrix(synthetic.key(91, 0), N, K)
+    w16 = O.q4k_dequant_flat(W, N * K).reshape(N, K).astype(np.float16).astype(np.float64)
+    for M in (2048, 1300):
+        A = synthetic.normal_f16(synthetic.key(92, M), M * K)
+        exp = A.astype(np.float64).reshape(M, K) @ w16.T
+        got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
+        assert_close(got, exp, f"two-SM gemm [{M},{K}]x[{N},{K}] vs f16-weight product")

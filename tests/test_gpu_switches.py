@@ -24,7 +24,7 @@ for (N, K) in [(3072, 1024), (4096, 4096), (1024, 12288)]:
     x = synthetic.normal_f32(synthetic.key(82, K), K)
     y = dev.read_tensor(ops.run_matmul(dev.tensor_from(x.reshape(1, K)), dev.weight_from(W, "q4k", [N, K]), 1, N, K, output_dtype="f32"))
     assert_close(y, O.q4k_gemv(W, N, K, x), f"gemv [{N},{K}]")
-M, N, K = 512, 384, 512
+M, N, K = 512, 768, 512
 W = synthetic.q4k_matrix(synthetic.key(83, 1), N, K)
 A = synthetic.normal_f16(synthetic.key(83, 2), M * K)
 c = dev.read_tensor(ops.run_matmul(dev.tensor_from(A.reshape(M, K)), dev.weight_from(W, "q4k", [N, K]), M, N, K, output_dtype="f32"))
@@ -49,7 +49,7 @@ print("ok")
 @pytest.mark.parametrize("env", [
     {"DP_GEMV_BREG": "1"}, {"DP_GEMV_VARIANT": "0"}, {"DP_GEMV_VARIANT": "1"}, {"DP_GEMV_PREFETCH": "1"},
     {"DP_ATTN_TC": "0"}, {"DP_ATTN_FUSE_QK": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_PAIR": "1"}, {"DP_GEMM_RINGS": "1"},
-    {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"}, {"DP_GEMM_2SM": "1"},
+    {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"}, {"DP_GEMM_2SM": "1"}, {"DP_GEMM_2SM": "4"}, {"DP_GEMM_2SM": "0"},
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_alternative_kernels_stay_correct(tmp_path, env):
     script = tmp_path / "child.py"
