@@ -125,6 +125,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
@@ -159,6 +168,10 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
   const int bpr = K / QK_K, num_k = K / BK;
+  // Every CTA walks K in its own rotation (by whole super-blocks).  All CTAs of a grid row need the same
+  // activation tiles; in lockstep they would all ask the same few L2 lines for them at the same time, and
+  // the L2 slices holding those lines, not the tensor pipe, would set the pace of every K step.
+  const int rot_b = (int)(blockIdx.x % (unsigned)bpr);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
@@ -204,7 +217,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         mbar_expect_tx(full_a(s), L.stage_a);
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, kt * BK, m0 + 128 * mt, full_a(s));
+        for (int mt = 0; mt < MT; mt++)
+          tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, (((kt >> 2) + rot_b) % bpr * 4 + (kt & 3)) * BK, m0 + 128 * mt, full_a(s));
       }
     }
   } else if (warp == 1) {
@@ -251,9 +265,10 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
 #pragma unroll
     for (int j = 0; j < RG; j++) {
       rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (grp0 + dw + j * DQ_WARPS) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
-      hdr[j] = __ldg(reinterpret_cast<const uint4 *>(rowp[j]));
+      const uint32_t *blk0 = rowp[j] + (size_t)rot_b * Q4K_BLOCK_WORDS;
+      hdr[j] = __ldg(reinterpret_cast<const uint4 *>(blk0));
 #pragma unroll
-      for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(rowp[j] + 4 + 8 * c) + oct);
+      for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(blk0 + 4 + 8 * c) + oct);
     }
     for (int kb = 0; kb < bpr && ok; kb++) {
       // rotate the prefetch buffers; decode the block header once for the four K steps.  The four
@@ -278,7 +293,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       if (kb + 1 < bpr) {
 #pragma unroll
         for (int j = 0; j < RG; j++) {
-          const uint32_t *blk = rowp[j] + (size_t)(kb + 1) * Q4K_BLOCK_WORDS;
+          const uint32_t *blk = rowp[j] + (size_t)((kb + 1 + rot_b) % bpr) * Q4K_BLOCK_WORDS;
           hdr[j] = __ldg(reinterpret_cast<const uint4 *>(blk));
 #pragma unroll
           for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * c) + oct);
@@ -413,20 +428,29 @@ __device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap 
                : "memory");
 }
 
-template <int BN, typename OutT, int SA, int SB>
-__global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
-                                                               OutT *__restrict__ C, int M, int N, int K, float alpha,
-                                                               int *__restrict__ err) {
-  constexpr int HB = BN / 2, DQ_WARPS = HB / 8;  // HB weight rows of the tile are this CTA's, one 8-row group per warp
-  static_assert(HB == DQ_WARPS * 8, "one 8-row group per dequant warp");
-  static_assert(2 * BN <= 512, "two accumulators must fit tensor memory");
+// The tile width is a run-time value (a multiple of 16 up to BNMAX): the first `wide_tiles` clusters of a
+// grid row take `bn_wide` columns, the others `bn_narrow`.  With 28 tiles of 176 and 46 of 160 columns the
+// 74 clusters of a B200 cover N = 12288 in one even wave, where uniform 256-wide tiles fill only 48.
+template <int BNMAX, typename OutT, int SA, int SB, int CH>
+__global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
+                                                                  OutT *__restrict__ C, int M, int N, int K, float alpha,
+                                                                  int *__restrict__ err, int wide_tiles, int bn_wide, int bn_narrow) {
+  constexpr int HBMAX = BNMAX / 2, DQ_WARPS = HBMAX / 8;  // warps 2 .. 2+DQ_WARPS-1: one 8-row group of weights each, then the epilogue
+  static_assert(DQ_WARPS % 4 == 0, "the epilogue needs whole sets of four warps (one per 32 tensor-memory lanes)");
+  static_assert(2 * BNMAX <= 512, "two accumulators must fit tensor memory");
+  static_assert((CH == 1 || CH == 2 || CH == 4) && SB >= 2 * CH, "the weight ring must hold two groups of CH stages");
+  const int cluster_x = blockIdx.x >> 1;
+  const int bn = cluster_x < wide_tiles ? bn_wide : bn_narrow;  // columns of this pair tile
+  const int hb = bn / 2, dq = hb / 8;                            // this CTA's weight rows, its active dequant warps
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(HB, SA, SB, 2);
+  const TcSmem L = tc_layout(HBMAX, SA, SB, 2);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();
-  const int n0 = (blockIdx.x >> 1) * BN, m0 = blockIdx.y * 512;
+  const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
+  const int m0 = blockIdx.y * 512;
   const int bpr = K / QK_K, num_k = K / BK;
+  const int rot_b = cluster_x % bpr;  // K rotation of this pair (see the one-SM kernel)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
@@ -443,7 +467,7 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
     for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
     // "weights full": CTA 0 waits for its own twelve dequant warps plus one arrival relayed from CTA 1,
     // whose twelve warps arrive on CTA 1's own barrier first (one cross-SM arrive per stage, not twelve)
-    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), rank == 0 ? DQ_WARPS + 1 : DQ_WARPS); mbar_init(empty_b(s), 1); }
+    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), rank == 0 ? dq + 1 : dq); mbar_init(empty_b(s), 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -469,7 +493,8 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
         const uint32_t bar0 = mapa_shared(full_a(s), 0u);
 #pragma unroll
-        for (int ps = 0; ps < 2; ps++) tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, kt * BK, m0 + ps * 256 + (int)rank * 128, bar0);
+        for (int ps = 0; ps < 2; ps++)
+          tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, (((kt >> 2) + rot_b) % bpr * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
       }
     }
   } else if (warp == 1) {
@@ -484,7 +509,7 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
       }
     }
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc_f16(256, BN);
+      const uint32_t idesc = umma_idesc_f16(256, bn);
       bool ok = true;
       for (int kt = 0; kt < num_k && ok; kt++) {
         const int sa = kt % SA, sb = kt % SB;
@@ -499,7 +524,7 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
           const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
 #pragma unroll
           for (int ps = 0; ps < 2; ps++)
-            umma_f16_2sm(tmem_base + (uint32_t)(ps * BN), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+            umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
         umma_commit_2sm(empty_a(sa));
         umma_commit_2sm(empty_b(sb));
@@ -511,12 +536,14 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
     const int dw = warp - 2;
     const int r8 = lane & 7, oct = lane >> 3;
     bool ok = true;
-    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (int)rank * HB + dw * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
-    uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(rowp));
+    const bool active = dw < dq;  // narrower tiles leave the last dequant warps without rows (they still do the epilogue)
+    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (int)rank * hb + (active ? dw : 0) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+    const uint32_t *blk0 = rowp + (size_t)rot_b * Q4K_BLOCK_WORDS;
+    uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk0));
     uint2 qn[4];
 #pragma unroll
-    for (int c = 0; c < 4; c++) qn[c] = __ldg(reinterpret_cast<const uint2 *>(rowp + 4 + 8 * c) + oct);
-    for (int kb = 0; kb < bpr && ok; kb++) {
+    for (int c = 0; c < 4; c++) qn[c] = __ldg(reinterpret_cast<const uint2 *>(blk0 + 4 + 8 * c) + oct);
+    for (int kb = 0; kb < bpr && ok && active; kb++) {
       const float2 dd = q4k_d_dmin(hdr.x);
       const Q4KScales sc = q4k_unpack_scales(hdr.y, hdr.z, hdr.w);
       const uint32_t sh = (uint32_t)(oct & 1) * 16u;
@@ -528,70 +555,84 @@ __global__ void __launch_bounds__((BN / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(con
 #pragma unroll
       for (int c = 0; c < 4; c++) qcur[c] = qn[c];
       if (kb + 1 < bpr) {
-        const uint32_t *blk = rowp + (size_t)(kb + 1) * Q4K_BLOCK_WORDS;
+        const uint32_t *blk = rowp + (size_t)((kb + 1 + rot_b) % bpr) * Q4K_BLOCK_WORDS;
         hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
 #pragma unroll
         for (int c = 0; c < 4; c++) qn[c] = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * c) + oct);
       }
+      // CH K steps per synchronisation: the CH dequantisations are independent instruction streams, so one
+      // warp overlaps their latencies, and the stage waits, the proxy fence and the arrives are paid once
+      // per CH steps.  (One step at a time, every warp needs about a microsecond per K step whatever the
+      // tile width, and that, not the tensor pipe, set the pace.)
 #pragma unroll
-      for (int chunk = 0; chunk < 4; chunk++) {
-        const int kt = kb * 4 + chunk;
-        const int s = kt % SB;
-        const uint32_t n = (uint32_t)(kt / SB);
+      for (int c0 = 0; c0 < 4; c0 += CH) {
         bool stage_free = true;
-        if (n > 0) stage_free = mbar_wait_bounded(empty_b(s), (n - 1) & 1u, abort_flag);
-        if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }
-        const int src_lane = (chunk << 3) | r8;
-        const float s_lo = __shfl_sync(0xffffffffu, my_sc0, src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1, src_lane);
-        const float m_lo = __shfl_sync(0xffffffffu, my_mn0, src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1, src_lane);
-        const uint2 q = qcur[chunk];
-        uint32_t lo[4], hi[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const uint32_t word = i < 2 ? q.x : q.y;
-          const uint32_t wl = word & 0x0f0f0f0fu, wh = (word >> 4) & 0x0f0f0f0fu;
-          const uint32_t sel0 = (i & 1) ? 0x7442u : 0x7440u, sel1 = (i & 1) ? 0x7443u : 0x7441u;
-          const float ql0 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel0)) - 8388608.0f;
-          const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
-          const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
-          const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
-          const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
-          const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
-          lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
-          hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+        for (int u = 0; u < CH; u++) {
+          const int kt = kb * 4 + c0 + u;
+          const uint32_t n = (uint32_t)(kt / SB);
+          if (n > 0) stage_free = stage_free && mbar_wait_bounded(empty_b(kt % SB), (n - 1) & 1u, abort_flag);
         }
-        uint8_t *line = smem + L.b + (uint32_t)s * L.stage_b + (uint32_t)dw * 1024u + (uint32_t)r8 * 128u;
-        *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }
+#pragma unroll
+        for (int u = 0; u < CH; u++) {
+          const int chunk = c0 + u;
+          const int s = (kb * 4 + chunk) % SB;
+          const int src_lane = (chunk << 3) | r8;
+          const float s_lo = __shfl_sync(0xffffffffu, my_sc0, src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1, src_lane);
+          const float m_lo = __shfl_sync(0xffffffffu, my_mn0, src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1, src_lane);
+          const uint2 q = qcur[chunk];
+          uint32_t lo[4], hi[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t word = i < 2 ? q.x : q.y;
+            const uint32_t wl = word & 0x0f0f0f0fu, wh = (word >> 4) & 0x0f0f0f0fu;
+            const uint32_t sel0 = (i & 1) ? 0x7442u : 0x7440u, sel1 = (i & 1) ? 0x7443u : 0x7441u;
+            const float ql0 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel0)) - 8388608.0f;
+            const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
+            const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
+            const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
+            const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
+            const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
+            lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+          }
+          uint8_t *line = smem + L.b + (uint32_t)s * L.stage_b + (uint32_t)dw * 1024u + (uint32_t)r8 * 128u;
+          *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this CTA's stores -> visible to the tensor cores
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_b(s));
+        if (lane == 0) {
+#pragma unroll
+          for (int u = 0; u < CH; u++) mbar_arrive(full_b((kb * 4 + c0 + u) % SB));
+        }
       }
     }
     // ---------------- epilogue: this CTA's 128 rows of both passes ----------------
     const bool accum_ready = ok && mbar_wait_bounded(accum_bar, 0u, abort_flag);
     if (__all_sync(0xffffffffu, accum_ready)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int quad = warp & 3, third = dw >> 2;
-      constexpr int GROUPS = BN / 32;
+      const int quad = warp & 3, set = dw >> 2;  // DQ_WARPS / 4 sets of four warps share the 16-column groups
+      const int groups = bn / 16;
 #pragma unroll 1
       for (int ps = 0; ps < 2; ps++) {
         const int row = m0 + ps * 256 + (int)rank * 128 + quad * 32 + lane;
 #pragma unroll 1
-        for (int cg = third; cg < GROUPS; cg += DQ_WARPS / 4) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BN + cg * 32), r);
+        for (int cg = set; cg < groups; cg += DQ_WARPS / 4) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BNMAX + cg * 16), r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (row < M) {
-            OutT *dst = C + (size_t)row * N + n0 + cg * 32;
+            OutT *dst = C + (size_t)row * N + n0 + cg * 16;
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4)
+              for (int i = 0; i < 16; i += 4)
                 *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
                                                                    __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
             } else {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
+              for (int i = 0; i < 16; i += 8) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
@@ -662,15 +703,16 @@ dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W,
 }
 
 // two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
-template <typename OutT, int BN, int SA, int SB>
-dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
-  const size_t smem = tc_layout(BN / 2, SA, SB, 2).total + 1024;
-  static_assert(2 * 128 * 128 * SA + (BN / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  auto kernel = gemm_q4k_tc2_kernel<BN, OutT, SA, SB>;
+template <typename OutT, int BNMAX, int SA, int SB, int CH = 2>
+dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha,
+                        int tiles, int wide_tiles, int bn_wide, int bn_narrow) {
+  const size_t smem = tc_layout(BNMAX / 2, SA, SB, 2).total + 1024;
+  static_assert(2 * 128 * 128 * SA + (BNMAX / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * (N / BN), (M + 511) / 512);
-  cfg.blockDim = dim3((BN / 16 + 2) * 32);
+  cfg.gridDim = dim3(2 * tiles, (M + 511) / 512);
+  cfg.blockDim = dim3((BNMAX / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
@@ -680,11 +722,16 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status, wide_tiles, bn_wide, bn_narrow);
   ctx->launches++;
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc2_kernel failed: %s", cudaGetErrorString(e));
   return DP_OK;
+}
+// uniform tiles of BN columns
+template <typename OutT, int BN, int SA, int SB>
+dp_status launch_tc_2sm_uniform(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+  return launch_tc_2sm<OutT, BN, SA, SB>(ctx, tm, W, C, M, N, K, alpha, N / BN, N / BN, BN, BN);
 }
 
 // PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
@@ -732,16 +779,27 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
     const long clusters = ctx->sm_count / 2, sms = ctx->sm_count;
     const long waves2 = ((long)(N / 256) * ((M + 511) / 512) + clusters - 1) / clusters;
     const long waves1 = ((long)(N / bn) * ((M + BM - 1) / BM) + sms - 1) / sms;
-    if (waves2 * 677 < waves1 * 651) return launch_tc_2sm<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+    if (waves2 * 677 < waves1 * 651) return launch_tc_2sm_uniform<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
   }
-  if (two_sm >= 4 && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
-    if (two_sm == 5) return launch_tc_2sm<OutT, 256, 4, 5>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_2sm<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+  // One row of pair tiles (256 < M <= 512): spread N over all clusters in one even wave, with two tile widths
+  // 16 apart (N = 12288 on 74 clusters: 28 tiles of 176 columns and 46 of 160).  DP_GEMM_2SM=6 forces it.
+  if ((two_sm == -1 || two_sm == 6 || two_sm == 7) && M > 256 && M <= 512 && N % 16 == 0) {
+    const int clusters = ctx->sm_count / 2;
+    const int narrow = (N / 16 / clusters) * 16, wide = narrow + 16;
+    const int n_wide = (N - clusters * narrow) / 16;  // clusters * narrow + 16 * n_wide == N
+    if (narrow >= 96 && wide <= 192) {
+      if (two_sm == 7) return launch_tc_2sm<OutT, 192, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
+      return launch_tc_2sm<OutT, 192, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
+    }
+  }
+  if (two_sm >= 4 && two_sm <= 5 && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
+    if (two_sm == 5) return launch_tc_2sm_uniform<OutT, 256, 4, 5>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_2sm_uniform<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
   }
   if (two_sm >= 1 && two_sm <= 3 && M > 256 && N % 192 == 0) {
-    if (two_sm == 2) return launch_tc_2sm<OutT, 192, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
-    if (two_sm == 3) return launch_tc_2sm<OutT, 192, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_2sm<OutT, 192, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
+    if (two_sm == 2) return launch_tc_2sm_uniform<OutT, 192, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
+    if (two_sm == 3) return launch_tc_2sm_uniform<OutT, 192, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
+    return launch_tc_2sm_uniform<OutT, 192, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
   }
   // DP_GEMM_WIDE_M=1: 512 x 96 tiles when M > 256 (each weight dequantised once per 512 rows).  Off by
   // default: measured slower (512 x 12288 x 4096: 71.7 us against 65.9 us; M = 2048: 273.8 us against 243 us):
