@@ -431,24 +431,26 @@ __device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap 
 // The tile width is a run-time value (a multiple of 16 up to BNMAX): the first `wide_tiles` clusters of a
 // grid row take `bn_wide` columns, the others `bn_narrow`.  With 28 tiles of 176 and 46 of 160 columns the
 // 74 clusters of a B200 cover N = 12288 in one even wave, where uniform 256-wide tiles fill only 48.
-template <int BNMAX, typename OutT, int SA, int SB, int CH>
+// PS = passes: 256-row MMAs per pair tile (output tile 256*PS x bn).  One pass halves the activation bytes
+// per stage, which buys twice as many stages for the same shared memory.
+template <int BNMAX, typename OutT, int SA, int SB, int CH, int PS>
 __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
                                                                   OutT *__restrict__ C, int M, int N, int K, float alpha,
                                                                   int *__restrict__ err, int wide_tiles, int bn_wide, int bn_narrow) {
   constexpr int HBMAX = BNMAX / 2, DQ_WARPS = HBMAX / 8;  // warps 2 .. 2+DQ_WARPS-1: one 8-row group of weights each, then the epilogue
   static_assert(DQ_WARPS % 4 == 0, "the epilogue needs whole sets of four warps (one per 32 tensor-memory lanes)");
-  static_assert(2 * BNMAX <= 512, "two accumulators must fit tensor memory");
+  static_assert(PS * BNMAX <= 512, "the accumulators must fit tensor memory");
   static_assert((CH == 1 || CH == 2 || CH == 4) && SB >= 2 * CH, "the weight ring must hold two groups of CH stages");
   const int cluster_x = blockIdx.x >> 1;
   const int bn = cluster_x < wide_tiles ? bn_wide : bn_narrow;  // columns of this pair tile
   const int hb = bn / 2, dq = hb / 8;                            // this CTA's weight rows, its active dequant warps
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(HBMAX, SA, SB, 2);
+  const TcSmem L = tc_layout(HBMAX, SA, SB, PS);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();
   const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
-  const int m0 = blockIdx.y * 512;
+  const int m0 = blockIdx.y * (256 * PS);
   const int bpr = K / QK_K, num_k = K / BK;
   const int rot_b = cluster_x % bpr;  // K rotation of this pair (see the one-SM kernel)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
@@ -489,11 +491,11 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
         const int s = kt % SA;
         const uint32_t n = (uint32_t)(kt / SA);
         if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
-        if (rank == 0) mbar_expect_tx(full_a(s), 2u * L.stage_a);  // both CTAs' bytes are counted on CTA 0's barrier
+        if (rank == 0) mbar_expect_tx(full_a(s), 2u * L.stage_a);  // both CTAs' bytes (PS tiles each) are counted on CTA 0's barrier
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
         const uint32_t bar0 = mapa_shared(full_a(s), 0u);
 #pragma unroll
-        for (int ps = 0; ps < 2; ps++)
+        for (int ps = 0; ps < PS; ps++)
           tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, (((kt >> 2) + rot_b) % bpr * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
       }
     }
@@ -523,7 +525,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
           const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
           const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
 #pragma unroll
-          for (int ps = 0; ps < 2; ps++)
+          for (int ps = 0; ps < PS; ps++)
             umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
         umma_commit_2sm(empty_a(sa));
@@ -616,7 +618,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
       const int quad = warp & 3, set = dw >> 2;  // DQ_WARPS / 4 sets of four warps share the 16-column groups
       const int groups = bn / 16;
 #pragma unroll 1
-      for (int ps = 0; ps < 2; ps++) {
+      for (int ps = 0; ps < PS; ps++) {
         const int row = m0 + ps * 256 + (int)rank * 128 + quad * 32 + lane;
 #pragma unroll 1
         for (int cg = set; cg < groups; cg += DQ_WARPS / 4) {
@@ -703,15 +705,15 @@ dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W,
 }
 
 // two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
-template <typename OutT, int BNMAX, int SA, int SB, int CH = 2>
+template <typename OutT, int BNMAX, int SA, int SB, int CH = 2, int PS = 2>
 dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha,
                         int tiles, int wide_tiles, int bn_wide, int bn_narrow) {
-  const size_t smem = tc_layout(BNMAX / 2, SA, SB, 2).total + 1024;
-  static_assert(2 * 128 * 128 * SA + (BNMAX / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH>;
+  const size_t smem = tc_layout(BNMAX / 2, SA, SB, PS).total + 1024;
+  static_assert(PS * 128 * 128 * SA + (BNMAX / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * tiles, (M + 511) / 512);
+  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS));
   cfg.blockDim = dim3((BNMAX / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
@@ -783,12 +785,14 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   }
   // One row of pair tiles (256 < M <= 512): spread N over all clusters in one even wave, with two tile widths
   // 16 apart (N = 12288 on 74 clusters: 28 tiles of 176 columns and 46 of 160).  DP_GEMM_2SM=6 forces it.
-  if ((two_sm == -1 || two_sm == 6 || two_sm == 7) && M > 256 && M <= 512 && N % 16 == 0) {
+  if ((two_sm == -1 || (two_sm >= 6 && two_sm <= 9)) && M > 256 && M <= 512 && N % 16 == 0) {
     const int clusters = ctx->sm_count / 2;
     const int narrow = (N / 16 / clusters) * 16, wide = narrow + 16;
     const int n_wide = (N - clusters * narrow) / 16;  // clusters * narrow + 16 * n_wide == N
     if (narrow >= 96 && wide <= 192) {
       if (two_sm == 7) return launch_tc_2sm<OutT, 192, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
+      if (two_sm == 8) return launch_tc_2sm<OutT, 192, 6, 8, 2, 1>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
+      if (two_sm == 9) return launch_tc_2sm<OutT, 192, 8, 6, 2, 1>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
       return launch_tc_2sm<OutT, 192, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
     }
   }
