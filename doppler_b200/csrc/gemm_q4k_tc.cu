@@ -144,7 +144,7 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) 
   l.stage_b = (uint32_t)BN * 128u;
   l.a = 0;
   l.b = (uint32_t)SA * l.stage_a;
-  l.bars = l.b + (uint32_t)SB * l.stage_b;  // full_a[SA], empty_a[SA], full_b[SB], empty_b[SB], accum
+  l.bars = l.b + (uint32_t)SB * l.stage_b;  // full_a[SA], full_b[SB], done[max(SA, SB)], accum
   l.tmem_slot = l.bars + (2 * SA + 2 * SB + 1) * 8;
   l.abort_flag = l.tmem_slot + 8;
   l.total = l.abort_flag + 8;
@@ -175,20 +175,26 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
+  // One "K step done" barrier per step, in a ring of SD, frees both the activation stage and the weight
+  // stage of that step: the MMA thread commits once per step.  (tcgen05.commit is served at about one per
+  // 500-600 cycles; with one commit per ring and step, two per step, the commits and not the tensor pipe
+  // set the pace of every K step.)  The producer of stage ring X (depth SX) waits, before it refills the
+  // stage of step kt, for done(kt - SX); SD >= SX keeps that barrier from being committed again first.
+  constexpr int SD = SA > SB ? SA : SB;
   auto full_a = [&](int s) { return bars + 8u * (uint32_t)s; };
-  auto empty_a = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
-  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + s); };
-  auto empty_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + SB + s); };
-  const uint32_t accum_bar = bars + 8u * (uint32_t)(2 * SA + 2 * SB);
+  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
+  auto done = [&](int s) { return bars + 8u * (uint32_t)(SA + SB + s); };
+  const uint32_t accum_bar = bars + 8u * (uint32_t)(SA + SB + SD);
   constexpr uint32_t TMEM_COLS = 512;  // two accumulators of BN columns, rounded up to a power of two
 
   pdl_launch();
   pdl_wait();
   if (tid == 0) {
-    for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
-    // PAIR: a weight stage is full when the dequant warps of both CTAs have arrived, and free when
-    // the tensor cores of both CTAs have read it
-    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), PAIR ? 2 * DQ_WARPS : DQ_WARPS); mbar_init(empty_b(s), PAIR ? 2 : 1); }
+    for (int s = 0; s < SA; s++) mbar_init(full_a(s), 1);
+    // PAIR: a weight stage is full when the dequant warps of both CTAs have arrived, and a step is done
+    // when the tensor cores of both CTAs have read its stages
+    for (int s = 0; s < SB; s++) mbar_init(full_b(s), PAIR ? 2 * DQ_WARPS : DQ_WARPS);
+    for (int s = 0; s < SD; s++) mbar_init(done(s), PAIR ? 2 : 1);
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -212,8 +218,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     if (lane == 0) {
       for (int kt = 0; kt < num_k; kt++) {
         const int s = kt % SA;
-        const uint32_t n = (uint32_t)(kt / SA);
-        if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
+        if (kt >= SA && !mbar_wait_bounded(done((kt - SA) % SD), (uint32_t)((kt - SA) / SD) & 1u, abort_flag)) break;
         mbar_expect_tx(full_a(s), L.stage_a);
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
 #pragma unroll
@@ -242,8 +247,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           for (int mt = 0; mt < MT; mt++)
             umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
-        umma_commit(empty_a(sa));  // both stages are free once these MMAs have read them
-        if constexpr (PAIR) umma_commit_pair(empty_b(sb)); else umma_commit(empty_b(sb));
+        // both stages are free once these MMAs have read them
+        if constexpr (PAIR) umma_commit_pair(done(kt % SD)); else umma_commit(done(kt % SD));
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -303,9 +308,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       for (int chunk = 0; chunk < 4; chunk++) {
         const int kt = kb * 4 + chunk;
         const int s = kt % SB;
-        const uint32_t n = (uint32_t)(kt / SB);
         bool stage_free = true;
-        if (n > 0) stage_free = mbar_wait_bounded(empty_b(s), (n - 1) & 1u, abort_flag);
+        if (kt >= SB) stage_free = mbar_wait_bounded(done((kt - SB) % SD), (uint32_t)((kt - SB) / SD) & 1u, abort_flag);
         if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }  // leave together: the shuffles below name every lane
         uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
         const int src_lane = (chunk << 3) | r8;
@@ -456,20 +460,21 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
+  constexpr int SD = SA > SB ? SA : SB;  // ring of "K step done" barriers, one commit per step (see the one-SM kernel)
   auto full_a = [&](int s) { return bars + 8u * (uint32_t)s; };
-  auto empty_a = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
-  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + s); };
-  auto empty_b = [&](int s) { return bars + 8u * (uint32_t)(2 * SA + SB + s); };
-  const uint32_t accum_bar = bars + 8u * (uint32_t)(2 * SA + 2 * SB);
+  auto full_b = [&](int s) { return bars + 8u * (uint32_t)(SA + s); };
+  auto done = [&](int s) { return bars + 8u * (uint32_t)(SA + SB + s); };
+  const uint32_t accum_bar = bars + 8u * (uint32_t)(SA + SB + SD);
   constexpr uint32_t TMEM_COLS = 512;
 
   pdl_launch();
   pdl_wait();
   if (tid == 0) {
-    for (int s = 0; s < SA; s++) { mbar_init(full_a(s), 1); mbar_init(empty_a(s), 1); }
+    for (int s = 0; s < SA; s++) mbar_init(full_a(s), 1);
+    for (int s = 0; s < SD; s++) mbar_init(done(s), 1);
     // "weights full": CTA 0 waits for its own twelve dequant warps plus one arrival relayed from CTA 1,
     // whose twelve warps arrive on CTA 1's own barrier first (one cross-SM arrive per stage, not twelve)
-    for (int s = 0; s < SB; s++) { mbar_init(full_b(s), rank == 0 ? dq + 1 : dq); mbar_init(empty_b(s), 1); }
+    for (int s = 0; s < SB; s++) mbar_init(full_b(s), rank == 0 ? dq + 1 : dq);
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -489,8 +494,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
     if (lane == 0) {
       for (int kt = 0; kt < num_k; kt++) {
         const int s = kt % SA;
-        const uint32_t n = (uint32_t)(kt / SA);
-        if (n > 0 && !mbar_wait_bounded(empty_a(s), (n - 1) & 1u, abort_flag)) break;
+        if (kt >= SA && !mbar_wait_bounded(done((kt - SA) % SD), (uint32_t)((kt - SA) / SD) & 1u, abort_flag)) break;
         if (rank == 0) mbar_expect_tx(full_a(s), 2u * L.stage_a);  // both CTAs' bytes (PS tiles each) are counted on CTA 0's barrier
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
         const uint32_t bar0 = mapa_shared(full_a(s), 0u);
@@ -528,8 +532,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
           for (int ps = 0; ps < PS; ps++)
             umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
-        umma_commit_2sm(empty_a(sa));
-        umma_commit_2sm(empty_b(sb));
+        umma_commit_2sm(done(kt % SD));  // arrives on both CTAs' barrier: their stages of this step are free
       }
       if (ok) umma_commit_2sm(accum_bar);
     }
@@ -572,8 +575,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
 #pragma unroll
         for (int u = 0; u < CH; u++) {
           const int kt = kb * 4 + c0 + u;
-          const uint32_t n = (uint32_t)(kt / SB);
-          if (n > 0) stage_free = stage_free && mbar_wait_bounded(empty_b(kt % SB), (n - 1) & 1u, abort_flag);
+          if (kt >= SB) stage_free = stage_free && mbar_wait_bounded(done((kt - SB) % SD), (uint32_t)((kt - SB) / SD) & 1u, abort_flag);
         }
         if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }
 #pragma unroll
@@ -731,9 +733,9 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   return DP_OK;
 }
 // uniform tiles of BN columns
-template <typename OutT, int BN, int SA, int SB>
+template <typename OutT, int BN, int SA, int SB, int CH = 2>
 dp_status launch_tc_2sm_uniform(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
-  return launch_tc_2sm<OutT, BN, SA, SB>(ctx, tm, W, C, M, N, K, alpha, N / BN, N / BN, BN, BN);
+  return launch_tc_2sm<OutT, BN, SA, SB, CH>(ctx, tm, W, C, M, N, K, alpha, N / BN, N / BN, BN, BN);
 }
 
 // PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
@@ -770,33 +772,41 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
   // Two-SM kernel (tcgen05.mma.cta_group::2).  On 512 x 256 pair tiles its 256-wide MMAs fetch 8 KB of
   // operands per SM and 128 cycles instead of 10 KB per 96, and the tensor pipe runs about 1.3x faster per
-  // SM (M = 2048, N = 12288, K = 4096: 203.7 us = 1012 TFLOP/s against 243 us).  It needs whole waves of
-  // 74 clusters to win: at M = 512 its 48 tiles occupy 96 SMs (67.7 us against 65.1 us on 128 SMs), so
-  // the choice compares waves x measured time per tile.  DP_GEMM_2SM=0 never, 4 / 5 always (ring depths
-  // 3+4 / 4+5), 1 / 2 / 3 the 512 x 192 variant (as fast as the one-SM kernel: dequantisation, which it
-  // halves, is not what bounds this GEMM).
+  // SM.  It needs whole waves of 74 clusters to win (at M = 512, 48 tiles of 256 columns occupy 96 SMs), so
+  // the default below sizes the tiles to the waves.  DP_GEMM_2SM=0 never; 4 / 5 / 13 uniform 512 x 256
+  // tiles (ring depths 3+4 / 4+5 / 3+8); 1 / 2 / 3 uniform 512 x 192 tiles.
   static int two_sm = -2;
   if (two_sm == -2) { const char *e = getenv("DP_GEMM_2SM"); two_sm = e ? atoi(e) : -1; }
-  if (two_sm == -1 && M > 256 && N % 256 == 0) {
-    const long clusters = ctx->sm_count / 2, sms = ctx->sm_count;
-    const long waves2 = ((long)(N / 256) * ((M + 511) / 512) + clusters - 1) / clusters;
-    const long waves1 = ((long)(N / bn) * ((M + BM - 1) / BM) + sms - 1) / sms;
-    if (waves2 * 677 < waves1 * 651) return launch_tc_2sm_uniform<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
-  }
-  // One row of pair tiles (256 < M <= 512): spread N over all clusters in one even wave, with two tile widths
-  // 16 apart (N = 12288 on 74 clusters: 28 tiles of 176 columns and 46 of 160).  DP_GEMM_2SM=6 forces it.
-  if ((two_sm == -1 || (two_sm >= 6 && two_sm <= 9)) && M > 256 && M <= 512 && N % 16 == 0) {
-    const int clusters = ctx->sm_count / 2;
-    const int narrow = (N / 16 / clusters) * 16, wide = narrow + 16;
-    const int n_wide = (N - clusters * narrow) / 16;  // clusters * narrow + 16 * n_wide == N
-    if (narrow >= 96 && wide <= 192) {
-      if (two_sm == 7) return launch_tc_2sm<OutT, 192, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
-      if (two_sm == 8) return launch_tc_2sm<OutT, 192, 6, 8, 2, 1>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
-      if (two_sm == 9) return launch_tc_2sm<OutT, 192, 8, 6, 2, 1>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
-      return launch_tc_2sm<OutT, 192, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, clusters, n_wide, wide, narrow);
+  // Whole waves of even tiles (M > 256): with R = ceil(M / 512) rows of pair tiles, take the fewest waves of 74
+  // clusters that 256-wide tiles need, then as many column tiles per row as those waves hold, in two
+  // widths 16 apart.  N = 12288: M = 512 runs one wave of 28 x 176 + 46 x 160 columns instead of 48 tiles
+  // on 96 SMs; M = 2048 three waves of 55 tiles (53 x 224 + 2 x 208) instead of 48 x 256 in 2.6 waves.
+  // Tiles narrower than 128 columns are left to the one-SM kernel (N = 4096, M = 512 / 1024: 52 / 54 us there
+  // against 62 / 64 us here; every SM re-reads its activation rows once per tile column, so narrow tiles
+  // are bound by L2).  DP_GEMM_2SM=6 / 7 / 8 / 9 force other ring variants of the 192-wide instance.
+  if ((two_sm == -1 || (two_sm >= 6 && two_sm <= 10)) && M > 256 && N % 16 == 0) {
+    const int clusters = ctx->sm_count / 2, rows = (M + 511) / 512;
+    const int waves = (rows * ((N + 255) / 256) + clusters - 1) / clusters;
+    int cols = waves * clusters / rows;
+    if (cols > N / 96) cols = N / 96;
+    if (cols > 0) {
+      const int narrow = (N / 16 / cols) * 16;
+      const int n_wide = (N - cols * narrow) / 16;  // cols * narrow + 16 * n_wide == N, n_wide < cols
+      const int wide = narrow + 16, widest = n_wide ? wide : narrow;
+      const bool forced = two_sm != -1;
+      if ((narrow >= 128 || (forced && narrow >= 96)) && widest <= 192) {
+        if (two_sm == 6) return launch_tc_2sm<OutT, 192, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        if (two_sm == 7) return launch_tc_2sm<OutT, 192, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        if (two_sm == 8) return launch_tc_2sm<OutT, 192, 6, 8, 2, 1>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        if (two_sm == 9) return launch_tc_2sm<OutT, 192, 8, 6, 2, 1>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        // activation ring of four, weight ring of two whole super-blocks (four K steps per synchronisation)
+        return launch_tc_2sm<OutT, 192, 4, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      }
+      if (narrow >= 128 && widest <= 256 && !forced) return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
     }
   }
-  if (two_sm >= 4 && two_sm <= 5 && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
+  if (((two_sm >= 4 && two_sm <= 5) || two_sm == 13) && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
+    if (two_sm == 13) return launch_tc_2sm_uniform<OutT, 256, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha);
     if (two_sm == 5) return launch_tc_2sm_uniform<OutT, 256, 4, 5>(ctx, tm, W, C, M, N, K, alpha);
     return launch_tc_2sm_uniform<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
   }
