@@ -134,6 +134,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
+// Output scale: alpha, times an optional factor per output row (f32 activations are brought into f16 range
+// row by row with a power of two, which the epilogue multiplies back)
+struct TcAlpha {
+  float value;
+  const float *row_scale;
+  int weight_residue;  // 1: the B tile holds w - f16(w), the part of each weight that f16 rounding drops
+  int accumulate;      // 1: the epilogue adds to C instead of overwriting it (f32 output only)
+};
+
+// two dequantised weights as f16, or their f16 rounding residues
+__device__ __forceinline__ __half2 tc_pack_weights(float a, float b, int residue) {
+  __half2 h = __floats2half2_rn(a, b);
+  if (residue) {
+    const float2 f = __half22float2(h);
+    h = __floats2half2_rn(a - f.x, b - f.y);
+  }
+  return h;
+}
+
 struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
@@ -160,7 +179,7 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) 
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, bool PAIR, int MT = 2>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
-                                                                    int N, int K, float alpha, int *__restrict__ err) {
+                                                                    int N, int K, TcAlpha alpha, int *__restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const TcSmem L = tc_layout(BN, SA, SB, MT);
@@ -329,8 +348,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
             const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
             const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
-            const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
-            const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
+            const __half2 l2 = tc_pack_weights(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo), alpha.weight_residue);
+            const __half2 h2 = tc_pack_weights(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi), alpha.weight_residue);
             lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
             hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
           }
@@ -365,6 +384,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
 #pragma unroll 1
       for (int mt = 0; mt < MT; mt++) {
         const int row = m0 + mt * 128 + quad * 32 + lane;
+        const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
 #pragma unroll 1
         for (int cg = half; cg < GROUPS; cg += DQ_WARPS / 4) {
           uint32_t r[32];
@@ -375,15 +395,22 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
-                                                                   __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+              {
+                float4 o = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow, __uint_as_float(r[i + 2]) * arow,
+                                       __uint_as_float(r[i + 3]) * arow);
+                if (alpha.accumulate) {
+                  const float4 c = *reinterpret_cast<const float4 *>(dst + i);
+                  o.x += c.x, o.y += c.y, o.z += c.z, o.w += c.w;
+                }
+                *reinterpret_cast<float4 *>(dst + i) = o;
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint32_t p[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * alpha, __uint_as_float(r[i + 2 * j + 1]) * alpha);
+                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * arow, __uint_as_float(r[i + 2 * j + 1]) * arow);
                   p[j] = *reinterpret_cast<const uint32_t *>(&h);
                 }
                 *reinterpret_cast<uint4 *>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
@@ -439,7 +466,7 @@ __device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap 
 // per stage, which buys twice as many stages for the same shared memory.
 template <int BNMAX, typename OutT, int SA, int SB, int CH, int PS>
 __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
-                                                                  OutT *__restrict__ C, int M, int N, int K, float alpha,
+                                                                  OutT *__restrict__ C, int M, int N, int K, TcAlpha alpha,
                                                                   int *__restrict__ err, int wide_tiles, int bn_wide, int bn_narrow) {
   constexpr int HBMAX = BNMAX / 2, DQ_WARPS = HBMAX / 8;  // warps 2 .. 2+DQ_WARPS-1: one 8-row group of weights each, then the epilogue
   static_assert(DQ_WARPS % 4 == 0, "the epilogue needs whole sets of four warps (one per 32 tensor-memory lanes)");
@@ -596,8 +623,8 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
             const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
             const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
-            const __half2 l2 = __floats2half2_rn(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo));
-            const __half2 h2 = __floats2half2_rn(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi));
+            const __half2 l2 = tc_pack_weights(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo), alpha.weight_residue);
+            const __half2 h2 = tc_pack_weights(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi), alpha.weight_residue);
             lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
             hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
           }
@@ -622,6 +649,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
 #pragma unroll 1
       for (int ps = 0; ps < PS; ps++) {
         const int row = m0 + ps * 256 + (int)rank * 128 + quad * 32 + lane;
+        const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
 #pragma unroll 1
         for (int cg = set; cg < groups; cg += DQ_WARPS / 4) {
           uint32_t r[16];
@@ -632,15 +660,22 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 16; i += 4)
-                *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
-                                                                   __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+              {
+                float4 o = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow, __uint_as_float(r[i + 2]) * arow,
+                                       __uint_as_float(r[i + 3]) * arow);
+                if (alpha.accumulate) {
+                  const float4 c = *reinterpret_cast<const float4 *>(dst + i);
+                  o.x += c.x, o.y += c.y, o.z += c.z, o.w += c.w;
+                }
+                *reinterpret_cast<float4 *>(dst + i) = o;
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 16; i += 8) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * alpha, __uint_as_float(r[i + 2 * j + 1]) * alpha);
+                  const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * arow, __uint_as_float(r[i + 2 * j + 1]) * arow);
                   pk[j] = *reinterpret_cast<const uint32_t *>(&h);
                 }
                 *reinterpret_cast<uint4 *>(dst + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -666,6 +701,40 @@ __global__ void cast_f32_f16_kernel(const float *__restrict__ in, __half *__rest
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = __float2half_rn(in[i]);
 }
 
+// f32 row -> f16 row times a power of two, chosen per row so that the largest magnitude lands in [2^13, 2^14):
+// activations of any range (FFN intermediates reach 1e7) fit f16 with its full 11-bit significand, and the
+// scaling itself is exact.  row_scale[r] receives the inverse factor for the GEMM's epilogue.
+// With out_lo, the f16 rounding residue of every scaled element goes there (x * 2^-e = hi + lo to about 22 bits).
+__global__ void __launch_bounds__(256) scale_cast_rows_kernel(const float *__restrict__ in, __half *__restrict__ out, __half *__restrict__ out_lo,
+                                                              float *__restrict__ row_scale, int K) {
+  pdl_launch();
+  pdl_wait();
+  const float *x = in + (size_t)blockIdx.x * K;
+  __half *y = out + (size_t)blockIdx.x * K;
+  float mx = 0.0f;
+  for (int i = threadIdx.x; i < K; i += 256) mx = fmaxf(mx, fabsf(__ldg(x + i)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  __shared__ float wmax[8];
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = wmax[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) mx = fmaxf(mx, wmax[w]);
+  // exponent of the row maximum (0 for an all-zero or non-finite row: no scaling)
+  int e = 0;
+  if (mx > 0.0f && mx < __int_as_float(0x7f800000)) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 13;
+  e = max(-100, min(100, e));
+  const float down = __int_as_float((uint32_t)(127 - e) << 23), up = __int_as_float((uint32_t)(127 + e) << 23);
+  for (int i = threadIdx.x; i < K; i += 256) {
+    const float v = __ldg(x + i) * down;
+    const __half h = __float2half_rn(v);
+    y[i] = h;
+    if (out_lo) out_lo[(size_t)blockIdx.x * K + i] = __float2half_rn(v - __half2float(h));
+  }
+  if (threadIdx.x == 0) row_scale[blockIdx.x] = up;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -684,7 +753,7 @@ EncodeTiledFn get_encode() {
 }
 
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
-dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   const size_t smem = tc_layout(BN, SA, SB).total + 1024;
   static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
   DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -695,7 +764,7 @@ dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *
 
 // 512 x 96 tiles (four accumulators): one CTA covers 512 rows, so at M <= 512 each weight is dequantised once
 template <typename OutT>
-dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   constexpr int BN = 96, DQ = 12, SA = 2, SB = 4, MT = 4;
   const size_t smem = tc_layout(BN, SA, SB, MT).total + 1024;
   static_assert(MT * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
@@ -708,7 +777,7 @@ dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W,
 
 // two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
 template <typename OutT, int BNMAX, int SA, int SB, int CH = 2, int PS = 2>
-dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha,
+dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha,
                         int tiles, int wide_tiles, int bn_wide, int bn_narrow) {
   const size_t smem = tc_layout(BNMAX / 2, SA, SB, PS).total + 1024;
   static_assert(PS * 128 * 128 * SA + (BNMAX / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
@@ -734,13 +803,13 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
 }
 // uniform tiles of BN columns
 template <typename OutT, int BN, int SA, int SB, int CH = 2>
-dp_status launch_tc_2sm_uniform(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+dp_status launch_tc_2sm_uniform(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   return launch_tc_2sm<OutT, BN, SA, SB, CH>(ctx, tm, W, C, M, N, K, alpha, N / BN, N / BN, BN, BN);
 }
 
 // PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
-dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   const size_t smem = tc_layout(BN, SA, SB).total + 1024;
   auto kernel = gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, true>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -764,7 +833,7 @@ dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, O
 }
 
 template <typename OutT>
-dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, float alpha) {
+dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   // Equal depths (3 + 3) measured fastest on the 512 x 12288 x 4096 case: 65.1 us against 69.7 us with a
   // five-deep weight ring, whose extra 50 KB of shared memory come out of the L1 the weight loads use.
   // DP_GEMM_RINGS=1 selects the deeper weight ring.
@@ -839,8 +908,12 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
 
 }  // namespace
 
-dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
-                          int N, int K, float alpha, bool *handled) {
+static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
+                                  int N, int K, float alpha, int mode, bool *handled) {
+  // mode 0: A as given (f32 is cast to f16).  1: f32 rows scaled into f16 range, one pass.  2: as 1, in three
+  // passes A_hi.W_hi + A_lo.W_hi + A_hi.W_lo with the f16 rounding residues of A and W, which restores the
+  // f32-exact product to about 2^-21 of each term (f32 output only).
+  const bool row_scaled = mode >= 1;
   *handled = false;
   static int enabled = -1;
   if (enabled < 0) { const char *e = getenv("DP_GEMM_TC"); enabled = e ? atoi(e) : 1; }
@@ -854,8 +927,16 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
   if (!encode) return DP_OK;
 
   const __half *a16 = (const __half *)A;
-  dp_buf tmp = nullptr;
-  if (a_dtype == DP_F32) {
+  dp_buf tmp = nullptr, scales = nullptr, tmp_lo = nullptr;
+  if (a_dtype == DP_F32 && row_scaled) {
+    if (mode == 2 && c_dtype != DP_F32) return DP_OK;
+    DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_scaled", &tmp));
+    DP_TRY(dp_buf_acquire(ctx, (size_t)M * 4, "matmul_a_row_scale", &scales));
+    if (mode == 2) DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_residue", &tmp_lo));
+    DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, (const float *)A, (__half *)tmp->dptr,
+              tmp_lo ? (__half *)tmp_lo->dptr : (__half *)nullptr, (float *)scales->dptr, K);
+    a16 = (const __half *)tmp->dptr;
+  } else if (a_dtype == DP_F32) {
     DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_cast", &tmp));
     size_t n = (size_t)M * K, grid = (n + 255) / 256;
     if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
@@ -872,16 +953,42 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
   CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   dp_status st = DP_OK;
+  TcAlpha ta = {alpha, scales ? (const float *)scales->dptr : nullptr, 0, 0};
+  CUtensorMap tm_lo;
+  if (r == CUDA_SUCCESS && tmp_lo)
+    r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, tmp_lo->dptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
   } else if (c_dtype == DP_F32) {
-    st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, alpha);
+    st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, ta);
+    if (st == DP_OK && tmp_lo) {
+      ta.accumulate = 1;
+      st = dispatch_tc<float>(ctx, bn, tm_lo, W, (float *)C, M, N, K, ta);  // + A_lo . W_hi
+      ta.weight_residue = 1;
+      if (st == DP_OK) st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, ta);  // + A_hi . W_lo
+    }
   } else if (c_dtype == DP_F16) {
-    st = dispatch_tc<__half>(ctx, bn, tm, W, (__half *)C, M, N, K, alpha);
+    st = dispatch_tc<__half>(ctx, bn, tm, W, (__half *)C, M, N, K, ta);
   } else {
     st = dp_fail(ctx, DP_ERR_INVALID, "matmul: unsupported output dtype");
   }
   if (tmp) dp_buf_release(ctx, tmp);  // stream ordered: reused only by later work
+  if (scales) dp_buf_release(ctx, scales);
+  if (tmp_lo) dp_buf_release(ctx, tmp_lo);
   if (st == DP_OK) *handled = true;
   return st;
+}
+
+dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
+                          int N, int K, float alpha, bool *handled) {
+  return gemm_q4k_tc_impl(ctx, W, A, a_dtype, C, c_dtype, M, N, K, alpha, 0, handled);
+}
+
+// f32 activations of any range on the tensor-core kernel: every row is scaled into f16 range by a power
+// of two and scaled back in the epilogue.  passes == 1: activations and weights rounded to f16 (11-bit
+// significands, what the reference's tiled f16 prefill kernel computes).  passes == 3: the rounding
+// residues of both are multiplied in as well, which gives the f32-exact product to f32 accuracy.
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, int passes, bool *handled) {
+  return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, 1.0f, passes == 3 ? 2 : 1, handled);
 }

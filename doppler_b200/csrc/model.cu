@@ -25,6 +25,7 @@
 #include <cstring>
 #include <vector>
 
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, int passes, bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
                           int M, int N, int K, float alpha, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
@@ -641,10 +642,20 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   }
   // the GEMM may not alias its output with the residual: go through the partial buffer
   float *dst = (residual && residual == y) ? m->partial : y;
-  // f32 activations keep the f32-exact weight path (the reference's rule: f32 A selects the f32
-  // batched kernel, matmul.rules.json:15-22); the tensor-core kernel takes f16 activations, which
-  // the residual stream of a random-init model would overflow
-  DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
+  // Prefill chunks of 32 rows or more run on the tensor-core kernel: each activation row is scaled into f16
+  // range by a power of two (FFN intermediates of a random-init model reach 1e7, far outside f16) and
+  // scaled back in the epilogue.  Default: three passes, A_hi.W_hi + A_lo.W_hi + A_hi.W_lo with the f16
+  // rounding residues of activations and weights, which reproduces the f32-exact product (the reference's
+  // rule for f32 activations, matmul.rules.json:15-22) to f32 accuracy at about a tenth of the CUDA-core
+  // kernel's time.  DP_PREFILL_TC=1: one pass, activations and weights rounded to f16 as in the reference's
+  // tiled f16 prefill kernel (fused_matmul_q4_prefill_tiled_f16.wgsl), about 1e-3 of the output's rms away
+  // from the exact product; DP_PREFILL_TC=0, small chunks and shapes the tensor-core kernel does not tile:
+  // the f32-exact CUDA-core kernel.
+  static int prefill_tc = -1;
+  if (prefill_tc < 0) { const char *e = getenv("DP_PREFILL_TC"); prefill_tc = e ? atoi(e) : 3; }
+  bool handled = false;
+  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, prefill_tc == 1 ? 1 : 3, &handled));
+  if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
 }
