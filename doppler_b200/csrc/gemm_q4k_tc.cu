@@ -989,6 +989,7 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
 // of two and scaled back in the epilogue.  passes == 1: activations and weights rounded to f16 (11-bit
 // significands, what the reference's tiled f16 prefill kernel computes).  passes == 3: the rounding
 // residues of both are multiplied in as well, which gives the f32-exact product to f32 accuracy.
-dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, int passes, bool *handled) {
-  return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, 1.0f, passes == 3 ? 2 : 1, handled);
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
+                                    bool *handled) {
+  return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, alpha, passes == 3 ? 2 : 1, handled);
 }

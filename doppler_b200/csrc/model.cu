@@ -25,7 +25,7 @@
 #include <cstring>
 #include <vector>
 
-dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, int passes, bool *handled);
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes, bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
                           int M, int N, int K, float alpha, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
@@ -654,7 +654,7 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   static int prefill_tc = -1;
   if (prefill_tc < 0) { const char *e = getenv("DP_PREFILL_TC"); prefill_tc = e ? atoi(e) : 3; }
   bool handled = false;
-  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, prefill_tc == 1 ? 1 : 3, &handled));
+  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;

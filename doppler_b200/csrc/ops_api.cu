@@ -7,6 +7,8 @@
 #include <cstdlib>
 #include <cstring>
 
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
+                                    bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
                           int M, int N, int K, float alpha, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
@@ -106,6 +108,10 @@ extern "C" dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A
       bool handled = false;
       if (!o.exact_weights && M > 1 && A->dtype == DP_F16)  // f16 activations: tensor cores (matmul.rules.json:17)
         st = dpk_gemm_q4k_tc(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha, &handled);
+      // f32 activations select the f32-exact product (matmul.rules.json:15-22): from 32 rows on the tensor
+      // cores compute it in three passes (f16 halves and rounding residues of activations and weights)
+      else if (!o.exact_weights && M >= 32 && A->dtype == DP_F32 && o.out_dtype == DP_F32)
+        st = dpk_gemm_q4k_tc_rowscaled(ctx, (const uint8_t *)bptr, (const float *)aptr, (float *)cptr, M, N, K, o.alpha, 3, &handled);
       if (st == DP_OK && !handled)
         st = dpk_gemm_q4k_simt(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha);
     }
@@ -460,6 +466,9 @@ static dp_status fused_matvec(dp_ctx *ctx, dp_dtype wdtype, const char *w, const
       if (!handled) DP_TRY(dpk_gemv_q4k(ctx, (const uint8_t *)w, x, y, DP_F32, N, K, alpha, residual));
       return DP_OK;
     }
+    bool handled = false;
+    if (M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, (const uint8_t *)w, x, y, M, N, K, alpha, 3, &handled));
+    if (handled) return DP_OK;
     return dpk_gemm_q4k_simt(ctx, (const uint8_t *)w, x, DP_F32, y, DP_F32, M, N, K, alpha);
   }
   DP_TRY(dpk_gemv_f16w(ctx, (const __half *)w, x, DP_F32, y, DP_F32, M, N, K, alpha));

@@ -175,3 +175,30 @@ def test_large_m_gemm_takes_the_two_sm_kernel(dev):
         exp = A.astype(np.float64).reshape(M, K) @ w16.T
         got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
         assert_close(got, exp, f"two-SM gemm [{M},{K}]x[{N},{K}] vs f16-weight product")
+
+
+def test_f32_activation_gemm_runs_on_the_tensor_cores(dev):
+    """f32 activations select the f32-exact product (matmul.rules.json:15-22).  From 32 rows on it is computed
+    on the tensor cores: every row is scaled into f16 range by a power of two, and three passes multiply the
+    f16 halves and the f16 rounding residues of activations and weights (A_hi.W_hi + A_lo.W_hi + A_hi.W_lo).
+    Rows here span ten decades (FFN intermediates of the synthetic models reach 1e7) and one row is zero, so
+    the gate is per row: |a - b| <= 2e-5 * (|b| + rms(row of b)), fifty times tighter than the f16-rounded
+    kernel could meet."""
+    M, N, K = 200, 384, 1024
+    W = synthetic.q4k_matrix(synthetic.key(93, 0), N, K)
+    A = synthetic.normal_f32(synthetic.key(93, 1), M * K).reshape(M, K)
+    decades = np.linspace(-3.0, 7.0, M).astype(np.float32)
+    A = (A * (10.0 ** decades)[:, None]).astype(np.float32)
+    A[17] = 0.0
+    exp = np.asarray(O.q4k_gemm(W, N, K, A.ravel(), M), np.float64).reshape(M, N)
+    l0 = dev.launch_count
+    got = np.asarray(_matmul(dev, W, N, K, A, M), np.float64).reshape(M, N)
+    assert dev.launch_count - l0 == 4, "expected the scaling cast and three tensor-core passes"
+    assert np.all(np.isfinite(got))
+    rms = np.sqrt(np.mean(exp * exp, axis=1, keepdims=True))
+    ratio = np.abs(got - exp) / (2e-5 * (np.abs(exp) + rms) + 1e-300)
+    print(f"[parity] f32-activation tensor-core gemm: worst per-row gate ratio {ratio.max():.3f}")
+    assert ratio.max() <= 1.0
+    assert np.all(got[17] == 0.0)
+    exact = np.asarray(_matmul(dev, W, N, K, A, M, exact_weights=True), np.float64).reshape(M, N)
+    assert (np.abs(exact - exp) / (2e-5 * (np.abs(exp) + rms) + 1e-300)).max() <= 1.0
