@@ -220,6 +220,27 @@ def kernel_case(args):
         out_lines.append({"case": "q4k_gemm_tcgen05", "shape": [M, N, K], "us_per_call": dt * 1e6, "TFLOPs": fl / dt / 1e12,
                           "frac_of_measured_burst": fl / dt / 1e12 / tf_burst, "frac_of_measured_sustained": fl / dt / 1e12 / tf_sus,
                           "frac_of_nominal_2250": fl / dt / 1e12 / 2250.0, "dtype": "f16 x q4k->f16, f32 accumulate"})
+    elif args.case == "prefill":
+        # whole-model prefill of the 9B-shaped decoder (f32 activations, f32-exact product on the tensor cores in
+        # three passes; DP_PREFILL_TC=1 one f16 pass, 0 the CUDA-core kernel).  Times model.prefill(), prompt upload
+        # and first-token read-back included.
+        from doppler_b200.model import DecoderModel
+        n = int(args.shape) if args.shape else 1024
+        cfg = dict(synthetic.MODEL_CONFIGS["9b"])
+        m = DecoderModel(dev, cfg, max_seq=n + 64)
+        m.load_synthetic()
+        prompt = synthetic.make_prompt(cfg, n)
+        m.prefill(prompt); dev.sync(); m.reset()
+        reps = 3
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            m.prefill(prompt); dev.sync(); m.reset()
+        dt = (time.perf_counter() - t0) / reps
+        layer_flops = 2.0 * n * cfg["hidden"] * ((cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * cfg["head_dim"] + cfg["n_heads"] * cfg["head_dim"] + 3 * cfg["inter"])
+        out_lines.append({"case": "prefill_9b", "prompt_tokens": n, "ms": dt * 1e3, "tokens_per_s": n / dt,
+                          "q4k_gemm_TFLOPs_useful": layer_flops * cfg["n_layers"] / dt / 1e12,
+                          "mode": "DP_PREFILL_TC=" + os.environ.get("DP_PREFILL_TC", "3 (default: three tensor-core passes, f32-exact)")})
+        m.destroy()
     else:
         B, kv = tuple(int(v) for v in args.shape.split(",")) if args.shape else (32, 8192)
         H, Hkv, D = 32, 8, 128
@@ -250,7 +271,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="9b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "attention"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "attention", "prefill"],
                     help="time ONE kernel of the path on a BASELINE configuration instead of the decoder "
                          "(gemv: configs 0 and 9B shapes, gemm: config 1, attention: config 2); also the small "
                          "command the profiler captures use")

@@ -430,7 +430,13 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   m->qdim = m->nh * c.head_dim; m->kvdim = m->nkv * c.head_dim;
   m->inter = c.inter / p; m->vocab_l = c.vocab / p; m->vocab0 = m->vocab_l * c.tp_rank;
   const int B = m->cfg.max_batch;
-  m->T = B > 512 ? B : 512;  // prefill chunk
+  // Prefill chunk: up to 2048 rows per GEMM (the tile grid of a 4096-column projection fills the GPU from
+  // about 1536 rows on), no more than the longest sequence needs
+  {
+    int t = c.max_seq < 2048 ? (c.max_seq + 255) / 256 * 256 : 2048;
+    if (t < 512) t = 512;
+    m->T = B > t ? B : t;
+  }
   m->layers.resize(c.n_layers);
   m->seq_len.assign(B, 0);
   dp_status st = DP_OK;
