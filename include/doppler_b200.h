@@ -127,14 +127,19 @@ uint32_t dp_recorder_op_count(dp_recorder *rec);
  * C[M,N] = alpha * A[M,K] . B[N,K]^T.  B.dtype DP_Q4K selects the fused
  * dequant kernels (M==1: decode GEMV, fused_matmul_q4.wgsl:279; M>1: prefill
  * GEMM, fused_matmul_q4_batched*.wgsl / _prefill_tiled_f16.wgsl); DP_F16 is the
- * f16-weight GEMV/GEMM used for the LM head (matmul_gemv_subgroup.wgsl). */
+ * f16-weight GEMV/GEMM used for the LM head (matmul_gemv_subgroup.wgsl).
+ * M>1 with Q4_K weights follows the reference's rule (matmul.rules.json:15-22):
+ * f16 activations give the product with weights rounded to f16 (one
+ * tensor-core pass); f32 activations give the f32-exact product, from 32 rows
+ * on in three tensor-core passes over the f16 halves and rounding residues of
+ * activations and weights (f32 output), otherwise on CUDA cores. */
 typedef struct {
   float alpha;        /* default 1 */
   dp_dtype out_dtype; /* DP_F32 or DP_F16 (reference: outputDtype, required) */
   size_t a_off, b_off, c_off; /* extra byte offsets, multiples of 256 */
   dp_buf out_buf;     /* optional caller-owned output */
   int transpose_b;    /* must be 1 (weights are [N,K]); 0 is DP_ERR_UNSUPPORTED */
-  int exact_weights;  /* M>1 only: 1 = keep f32-exact weights (2 tensor-core passes) */
+  int exact_weights;  /* M>1 only: 1 = always the CUDA-core kernel with f32-exact weights */
 } dp_matmul_opts;
 void dp_matmul_opts_default(dp_matmul_opts *o);
 dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A, const dp_weight *B, int M,
