@@ -39,6 +39,7 @@ struct dp_ctx {
   dp_buf attn_scratch = nullptr;
   dp_buf argmax_scratch = nullptr;
   dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
+  dp_buf gemm_scratch = nullptr;  // f16 activations (halves, residues, row scales) of the tensor-core GEMM (stream ordered)
   bool pdl = false;  // launch with programmatic dependent launch (set while the decode step is recorded)
   // Weight matrix of the NEXT Q4_K GEMV in program order (set by the decode schedule, consumed by the
   // next TMA GEMV launch): that launch's producer warps pull its first row tiles into L2 once their own

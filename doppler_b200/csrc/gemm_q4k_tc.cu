@@ -641,34 +641,40 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
       }
     }
     // ---------------- epilogue: this CTA's 128 rows of both passes ----------------
+    // Tensor memory hands a thread one output row, so storing from registers puts a warp's 32 lanes on 32
+    // different rows (16 bytes each, and as many scattered loads when C is accumulated).  The tile of a
+    // pass goes through shared memory instead (the operand rings are idle by now): rows padded by 16 bytes
+    // keep the 16-byte shared stores conflict free, and the copy to C runs along the rows, a warp on 512
+    // contiguous bytes.  Every warp takes part in the barriers, also one whose bounded wait gave up.
     const bool accum_ready = ok && mbar_wait_bounded(accum_bar, 0u, abort_flag);
-    if (__all_sync(0xffffffffu, accum_ready)) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool go = __all_sync(0xffffffffu, accum_ready);
+    if (go) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    {
+      constexpr int ET = DQ_WARPS * 32;  // epilogue threads
+      static_assert(128 * (BNMAX * (int)sizeof(OutT) + 16) <= PS * 128 * 128 * SA + HBMAX * 128 * SB, "the output tile of a pass must fit the idle operand rings");
       const int quad = warp & 3, set = dw >> 2;  // DQ_WARPS / 4 sets of four warps share the 16-column groups
       const int groups = bn / 16;
+      const uint32_t row_bytes = (uint32_t)bn * (uint32_t)sizeof(OutT), row_pitch = row_bytes + 16u;
+      uint8_t *stage = smem + L.a;
+      const int et = tid - 64;  // 0 .. ET-1
 #pragma unroll 1
       for (int ps = 0; ps < PS; ps++) {
-        const int row = m0 + ps * 256 + (int)rank * 128 + quad * 32 + lane;
-        const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
+        const int row0 = m0 + ps * 256 + (int)rank * 128;  // first row of this CTA's part of the pass
+        if (go) {
+          const int lrow = quad * 32 + lane;
+          const int row = row0 + lrow;
+          const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
 #pragma unroll 1
-        for (int cg = set; cg < groups; cg += DQ_WARPS / 4) {
-          uint32_t r[16];
-          tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BNMAX + cg * 16), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (row < M) {
-            OutT *dst = C + (size_t)row * N + n0 + cg * 16;
+          for (int cg = set; cg < groups; cg += DQ_WARPS / 4) {
+            uint32_t r[16];
+            tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BNMAX + cg * 16), r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint8_t *dst = stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 16u * (uint32_t)sizeof(OutT);
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 16; i += 4)
-              {
-                float4 o = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow, __uint_as_float(r[i + 2]) * arow,
-                                       __uint_as_float(r[i + 3]) * arow);
-                if (alpha.accumulate) {
-                  const float4 c = *reinterpret_cast<const float4 *>(dst + i);
-                  o.x += c.x, o.y += c.y, o.z += c.z, o.w += c.w;
-                }
-                *reinterpret_cast<float4 *>(dst + i) = o;
-              }
+                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow,
+                                                                       __uint_as_float(r[i + 2]) * arow, __uint_as_float(r[i + 3]) * arow);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; i += 8) {
@@ -678,11 +684,33 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
                   const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * arow, __uint_as_float(r[i + 2 * j + 1]) * arow);
                   pk[j] = *reinterpret_cast<const uint32_t *>(&h);
                 }
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4 *>(dst + 2 * i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
               }
             }
           }
         }
+        asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the pass's tile is staged
+        if (go) {
+          const int cpr = (int)(row_bytes >> 4);  // 16-byte chunks per row
+          const int total = 128 * cpr;
+          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * N + n0);
+#pragma unroll 2
+          for (int c = et; c < total; c += ET) {
+            const int lrow = c / cpr, ch = c - lrow * cpr;
+            if (row0 + lrow >= M) break;  // rows grow with c
+            uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
+            char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
+            if constexpr (sizeof(OutT) == 4) {
+              if (alpha.accumulate) {
+                const float4 old = *reinterpret_cast<const float4 *>(g);
+                v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
+                v.z = __float_as_uint(__uint_as_float(v.z) + old.z), v.w = __float_as_uint(__uint_as_float(v.w) + old.w);
+              }
+            }
+            *reinterpret_cast<uint4 *>(g) = v;
+          }
+        }
+        if (ps + 1 < PS) asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the stage is free for the next pass
       }
     }
   }
@@ -927,21 +955,26 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   if (!encode) return DP_OK;
 
   const __half *a16 = (const __half *)A;
-  dp_buf tmp = nullptr, scales = nullptr, tmp_lo = nullptr;
-  if (a_dtype == DP_F32 && row_scaled) {
+  // The f16 copies of f32 activations live in one scratch allocation of the context, reused in stream order
+  // (a buffer handed back to the pool here could be given to somebody else before a recorded graph replays).
+  const __half *a_lo = nullptr;
+  const float *scales = nullptr;
+  if (a_dtype == DP_F32) {
     if (mode == 2 && c_dtype != DP_F32) return DP_OK;
-    DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_scaled", &tmp));
-    DP_TRY(dp_buf_acquire(ctx, (size_t)M * 4, "matmul_a_row_scale", &scales));
-    if (mode == 2) DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_residue", &tmp_lo));
-    DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, (const float *)A, (__half *)tmp->dptr,
-              tmp_lo ? (__half *)tmp_lo->dptr : (__half *)nullptr, (float *)scales->dptr, K);
-    a16 = (const __half *)tmp->dptr;
-  } else if (a_dtype == DP_F32) {
-    DP_TRY(dp_buf_acquire(ctx, (size_t)M * K * 2, "matmul_a_f16_cast", &tmp));
-    size_t n = (size_t)M * K, grid = (n + 255) / 256;
-    if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
-    DP_LAUNCH(ctx, cast_f32_f16_kernel, (unsigned)grid, 256, 0, (const float *)A, (__half *)tmp->dptr, n);
-    a16 = (const __half *)tmp->dptr;
+    const size_t a_bytes = ((size_t)M * K * 2 + 255) / 256 * 256;
+    DP_TRY(dp_scratch(ctx, &ctx->gemm_scratch, 2 * a_bytes + (size_t)M * 4, "matmul_a_f16"));
+    char *base = (char *)ctx->gemm_scratch->dptr;
+    a16 = (const __half *)base;
+    if (row_scaled) {
+      if (mode == 2) a_lo = (const __half *)(base + a_bytes);
+      scales = (const float *)(base + 2 * a_bytes);
+      DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, (const float *)A, (__half *)base, mode == 2 ? (__half *)(base + a_bytes) : (__half *)nullptr,
+                (float *)(base + 2 * a_bytes), K);
+    } else {
+      size_t n = (size_t)M * K, grid = (n + 255) / 256;
+      if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
+      DP_LAUNCH(ctx, cast_f32_f16_kernel, (unsigned)grid, 256, 0, (const float *)A, (__half *)base, n);
+    }
   } else if (a_dtype != DP_F16) {
     return DP_OK;
   }
@@ -953,16 +986,16 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   dp_status st = DP_OK;
-  TcAlpha ta = {alpha, scales ? (const float *)scales->dptr : nullptr, 0, 0};
+  TcAlpha ta = {alpha, scales, 0, 0};
   CUtensorMap tm_lo;
-  if (r == CUDA_SUCCESS && tmp_lo)
-    r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, tmp_lo->dptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (r == CUDA_SUCCESS && a_lo)
+    r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a_lo, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
   } else if (c_dtype == DP_F32) {
     st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, ta);
-    if (st == DP_OK && tmp_lo) {
+    if (st == DP_OK && a_lo) {
       ta.accumulate = 1;
       st = dispatch_tc<float>(ctx, bn, tm_lo, W, (float *)C, M, N, K, ta);  // + A_lo . W_hi
       ta.weight_residue = 1;
@@ -973,9 +1006,6 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   } else {
     st = dp_fail(ctx, DP_ERR_INVALID, "matmul: unsupported output dtype");
   }
-  if (tmp) dp_buf_release(ctx, tmp);  // stream ordered: reused only by later work
-  if (scales) dp_buf_release(ctx, scales);
-  if (tmp_lo) dp_buf_release(ctx, tmp_lo);
   if (st == DP_OK) *handled = true;
   return st;
 }
