@@ -374,36 +374,38 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         }
       }
     }
-    // ---------------- epilogue: tensor memory -> registers -> C ----------------
+    // ---------------- epilogue: tensor memory -> registers -> shared memory -> C ----------------
+    // Staged through the idle operand rings and copied out along the rows, like the two-SM kernel's.
     const bool accum_ready = ok && mbar_wait_bounded(accum_bar, 0u, abort_flag);
-    if (__all_sync(0xffffffffu, accum_ready)) {  // tcgen05.ld is warp-wide: enter together or not at all
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool go = __all_sync(0xffffffffu, accum_ready);  // tcgen05.ld is warp-wide: enter together or not at all
+    if (go) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    {
+      constexpr int ET = DQ_WARPS * 32;  // epilogue threads
+      static_assert(128 * (BN * (int)sizeof(OutT) + 16) <= MT * 128 * 128 * SA + BN * 128 * SB, "the output tile of a pass must fit the idle operand rings");
       const int quad = warp & 3;         // the 32 TMEM lanes this warp may read
       const int half = dw >> 2;          // DQ_WARPS/4 warps share a quarter and split the column groups
       constexpr int GROUPS = BN / 32;
+      constexpr uint32_t row_bytes = (uint32_t)BN * (uint32_t)sizeof(OutT), row_pitch = row_bytes + 16u;
+      uint8_t *stage = smem + L.a;
+      const int et = tid - 64;
 #pragma unroll 1
       for (int mt = 0; mt < MT; mt++) {
-        const int row = m0 + mt * 128 + quad * 32 + lane;
-        const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
+        const int row0 = m0 + mt * 128;
+        if (go) {
+          const int lrow = quad * 32 + lane;
+          const int row = row0 + lrow;
+          const float arow = (alpha.row_scale && row < M) ? alpha.value * __ldg(alpha.row_scale + row) : alpha.value;
 #pragma unroll 1
-        for (int cg = half; cg < GROUPS; cg += DQ_WARPS / 4) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * BN + cg * 32), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (row < M) {
-            OutT *dst = C + (size_t)row * N + n0 + cg * 32;
+          for (int cg = half; cg < GROUPS; cg += DQ_WARPS / 4) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * BN + cg * 32), r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint8_t *dst = stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 32u * (uint32_t)sizeof(OutT);
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-              {
-                float4 o = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow, __uint_as_float(r[i + 2]) * arow,
-                                       __uint_as_float(r[i + 3]) * arow);
-                if (alpha.accumulate) {
-                  const float4 c = *reinterpret_cast<const float4 *>(dst + i);
-                  o.x += c.x, o.y += c.y, o.z += c.z, o.w += c.w;
-                }
-                *reinterpret_cast<float4 *>(dst + i) = o;
-              }
+                *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow,
+                                                                       __uint_as_float(r[i + 2]) * arow, __uint_as_float(r[i + 3]) * arow);
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -413,11 +415,33 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
                   const __half2 h = __floats2half2_rn(__uint_as_float(r[i + 2 * j]) * arow, __uint_as_float(r[i + 2 * j + 1]) * arow);
                   p[j] = *reinterpret_cast<const uint32_t *>(&h);
                 }
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
+                *reinterpret_cast<uint4 *>(dst + 2 * i) = make_uint4(p[0], p[1], p[2], p[3]);
               }
             }
           }
         }
+        asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the tile of these 128 rows is staged
+        if (go) {
+          constexpr int cpr = (int)(row_bytes >> 4);  // 16-byte chunks per row
+          constexpr int total = 128 * cpr;
+          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * N + n0);
+#pragma unroll 2
+          for (int c = et; c < total; c += ET) {
+            const int lrow = c / cpr, ch = c - lrow * cpr;
+            if (row0 + lrow >= M) break;  // rows grow with c
+            uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
+            char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
+            if constexpr (sizeof(OutT) == 4) {
+              if (alpha.accumulate) {
+                const float4 old = *reinterpret_cast<const float4 *>(g);
+                v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
+                v.z = __float_as_uint(__uint_as_float(v.z) + old.z), v.w = __float_as_uint(__uint_as_float(v.w) + old.w);
+              }
+            }
+            *reinterpret_cast<uint4 *>(g) = v;
+          }
+        }
+        if (mt + 1 < MT) asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the stage is free for the next 128 rows
       }
     }
   }
