@@ -323,13 +323,28 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           for (int c = 0; c < 4; c++) qn[j][c] = __ldg(reinterpret_cast<const uint2 *>(blk + 4 + 8 * c) + oct);
         }
       }
+      // A weight ring of eight stages is filled a whole super-block at a time: the four stage waits, the
+      // proxy fence and the arrives are paid once per four K steps, and the four dequantisations are
+      // independent instruction streams (shallower rings synchronise every K step).
+      constexpr bool BLOCK_SYNC = SB >= 8 && SB % 4 == 0;
+      if constexpr (BLOCK_SYNC) {
+        bool stages_free = true;
+#pragma unroll
+        for (int chunk = 0; chunk < 4; chunk++) {
+          const int kt = kb * 4 + chunk;
+          if (kt >= SB) stages_free = stages_free && mbar_wait_bounded(done((kt - SB) % SD), (uint32_t)((kt - SB) / SD) & 1u, abort_flag);
+        }
+        if (!__all_sync(0xffffffffu, stages_free)) { ok = false; break; }
+      }
 #pragma unroll
       for (int chunk = 0; chunk < 4; chunk++) {
         const int kt = kb * 4 + chunk;
         const int s = kt % SB;
-        bool stage_free = true;
-        if (kt >= SB) stage_free = mbar_wait_bounded(done((kt - SB) % SD), (uint32_t)((kt - SB) / SD) & 1u, abort_flag);
-        if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }  // leave together: the shuffles below name every lane
+        if constexpr (!BLOCK_SYNC) {
+          bool stage_free = true;
+          if (kt >= SB) stage_free = mbar_wait_bounded(done((kt - SB) % SD), (uint32_t)((kt - SB) / SD) & 1u, abort_flag);
+          if (!__all_sync(0xffffffffu, stage_free)) { ok = false; break; }  // leave together: the shuffles below name every lane
+        }
         uint8_t *bt = smem + L.b + (uint32_t)s * L.stage_b;
         const int src_lane = (chunk << 3) | r8;
 #pragma unroll
@@ -364,13 +379,27 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             st_cluster_v4(rline + off_hi, hi[0], hi[1], hi[2], hi[3]);
           }
         }
-        // generic-proxy stores -> visible to the tensor core (of both CTAs in the PAIR variant)
+        if constexpr (!BLOCK_SYNC) {
+          // generic-proxy stores -> visible to the tensor core (of both CTAs in the PAIR variant)
+          if constexpr (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
+          else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(full_b(s));
+            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b(s), pair_rank ^ 1u));
+          }
+        }
+      }
+      if constexpr (BLOCK_SYNC) {
         if constexpr (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
         else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(full_b(s));
-          if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b(s), pair_rank ^ 1u));
+#pragma unroll
+          for (int chunk = 0; chunk < 4; chunk++) {
+            mbar_arrive(full_b((kb * 4 + chunk) % SB));
+            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b((kb * 4 + chunk) % SB), pair_rank ^ 1u));
+          }
         }
       }
     }
@@ -888,7 +917,9 @@ template <typename OutT>
 dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   // Equal depths (3 + 3) measured fastest on the 512 x 12288 x 4096 case: 65.1 us against 69.7 us with a
   // five-deep weight ring, whose extra 50 KB of shared memory come out of the L1 the weight loads use.
-  // DP_GEMM_RINGS=1 selects the deeper weight ring.
+  // DP_GEMM_RINGS=1 selects the deeper weight ring, 2 (128-wide tiles) a weight ring of eight stages filled a
+  // super-block at a time; neither is faster (N = 4096, K = 12288, M = 1024: 141 / 147 / 143 us), nor are sixteen
+  // dequant warps instead of eight (148 us).
   static int rings = -1;
   if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
   // Two-SM kernel (tcgen05.mma.cta_group::2).  On 512 x 256 pair tiles its 256-wide MMAs fetch 8 KB of
@@ -955,6 +986,7 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
     return launch_tc_pair<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
   }
   if (bn == 192) return rings ? launch_tc<192, 12, OutT, 3, 5>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  if (rings == 2) return launch_tc<128, 8, OutT, 3, 8>(ctx, tm, W, C, M, N, K, alpha);
   return rings ? launch_tc<128, 8, OutT, 4, 6>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
 }
 
