@@ -141,6 +141,7 @@ struct TcAlpha {
   const float *row_scale;
   int weight_residue;  // 1: the B tile holds w - f16(w), the part of each weight that f16 rounding drops
   int accumulate;      // 1: the epilogue adds to C instead of overwriting it (f32 output only)
+  int k_splits;        // one-SM kernel: parts of K per tile (grid.z), added into C by atomics (f32 output only)
 };
 
 // two dequantised weights as f16, or their f16 rounding residues
@@ -186,7 +187,12 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   static_assert(MT * BN <= 512, "accumulators exceed tensor memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
-  const int bpr = K / QK_K, num_k = K / BK;
+  // Split over K (grid.z parts, whole super-blocks each): a problem of few tiles (N = 4096 at M <= 512 is 64)
+  // fills the GPU with several CTAs per tile, whose epilogues add into a zeroed (or accumulated) f32 C.
+  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
+  const int bpr_row = K / QK_K;                       // super-blocks per weight row
+  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;  // this CTA's share
+  const int num_k = bpr * (QK_K / BK);
   // Every CTA walks K in its own rotation (by whole super-blocks).  All CTAs of a grid row need the same
   // activation tiles; in lockstep they would all ask the same few L2 lines for them at the same time, and
   // the L2 slices holding those lines, not the tensor pipe, would set the pace of every K step.
@@ -242,7 +248,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
-          tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, (((kt >> 2) + rot_b) % bpr * 4 + (kt & 3)) * BK, m0 + 128 * mt, full_a(s));
+          tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + 128 * mt, full_a(s));
       }
     }
   } else if (warp == 1) {
@@ -288,7 +294,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     const uint32_t *rowp[RG];
 #pragma unroll
     for (int j = 0; j < RG; j++) {
-      rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (grp0 + dw + j * DQ_WARPS) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+      rowp[j] = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (grp0 + dw + j * DQ_WARPS) * 8 + r8) * bpr_row * Q4K_BLOCK_BYTES) + (size_t)kb0 * Q4K_BLOCK_WORDS;
       const uint32_t *blk0 = rowp[j] + (size_t)rot_b * Q4K_BLOCK_WORDS;
       hdr[j] = __ldg(reinterpret_cast<const uint4 *>(blk0));
 #pragma unroll
@@ -461,6 +467,12 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
             if constexpr (sizeof(OutT) == 4) {
+              if (k_splits > 1) {  // several CTAs add their share of K into the same tile
+                float *gf = reinterpret_cast<float *>(g);
+                atomicAdd(gf, __uint_as_float(v.x)), atomicAdd(gf + 1, __uint_as_float(v.y));
+                atomicAdd(gf + 2, __uint_as_float(v.z)), atomicAdd(gf + 3, __uint_as_float(v.w));
+                continue;
+              }
               if (alpha.accumulate) {
                 const float4 old = *reinterpret_cast<const float4 *>(g);
                 v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
@@ -835,10 +847,21 @@ EncodeTiledFn get_encode() {
 
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
+  // few tiles and f32 output: split K over 2 .. 4 CTAs per tile (whole super-blocks, at least four each)
+  int splits = 1;
+  static int split_k = -1;
+  if (split_k < 0) { const char *e = getenv("DP_GEMM_SPLIT_K"); split_k = e ? atoi(e) : 1; }
+  if constexpr (sizeof(OutT) == 4) {
+    const int tiles = (N / BN) * ((M + BM - 1) / BM), bpr = K / QK_K;
+    for (int sp = 4; sp >= 2 && split_k; sp--)
+      if (tiles * sp <= ctx->sm_count && bpr % sp == 0 && bpr / sp >= 4) { splits = sp; break; }
+    if (splits > 1 && !alpha.accumulate) DP_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
+  }
+  alpha.k_splits = splits;
   const size_t smem = tc_layout(BN, SA, SB).total + 1024;
   static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
   DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(N / BN, (M + BM - 1) / BM);
+  dim3 grid(N / BN, (M + BM - 1) / BM, splits);
   DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
   return DP_OK;
 }
@@ -1042,7 +1065,7 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   dp_status st = DP_OK;
-  TcAlpha ta = {alpha, scales, 0, 0};
+  TcAlpha ta = {alpha, scales, 0, 0, 1};
   CUtensorMap tm_lo;
   if (r == CUDA_SUCCESS && a_lo)
     r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a_lo, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -202,3 +202,22 @@ def test_f32_activation_gemm_runs_on_the_tensor_cores(dev):
     assert np.all(got[17] == 0.0)
     exact = np.asarray(_matmul(dev, W, N, K, A, M, exact_weights=True), np.float64).reshape(M, N)
     assert (np.abs(exact - exp) / (2e-5 * (np.abs(exp) + rms) + 1e-300)).max() <= 1.0
+
+
+def test_few_tiles_split_k(dev):
+    """A problem of few output tiles (here two) is split over K: up to four CTAs per tile take whole
+    super-blocks each and add their share into the zeroed f32 output with atomics.  Oracle as in the two-SM
+    test (float64 product with f16-rounded weights, 1e-3 gate); f32 activations go through the three-pass
+    path, whose second and third pass add onto the first, against the exact-weight oracle per row."""
+    M, N, K = 96, 256, 4096
+    W = synthetic.q4k_matrix(synthetic.key(94, 0), N, K)
+    w16 = O.q4k_dequant_flat(W, N * K).reshape(N, K).astype(np.float16).astype(np.float64)
+    A = synthetic.normal_f16(synthetic.key(94, 1), M * K)
+    exp = A.astype(np.float64).reshape(M, K) @ w16.T
+    got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
+    assert_close(got, exp, f"split-K gemm [{M},{K}]x[{N},{K}] vs f16-weight product")
+    A32 = synthetic.normal_f32(synthetic.key(94, 2), M * K)
+    exp32 = np.asarray(O.q4k_gemm(W, N, K, A32, M), np.float64).reshape(M, N)
+    got32 = np.asarray(_matmul(dev, W, N, K, A32, M), np.float64).reshape(M, N)
+    rms = np.sqrt(np.mean(exp32 * exp32, axis=1, keepdims=True))
+    assert (np.abs(got32 - exp32) / (2e-5 * (np.abs(exp32) + rms) + 1e-300)).max() <= 1.0

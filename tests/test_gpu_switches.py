@@ -50,7 +50,7 @@ print("ok")
     {"DP_GEMV_BREG": "1"}, {"DP_GEMV_VARIANT": "0"}, {"DP_GEMV_VARIANT": "1"}, {"DP_GEMV_PREFETCH": "1"},
     {"DP_ATTN_TC": "0"}, {"DP_ATTN_FUSE_QK": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_PAIR": "1"}, {"DP_GEMM_RINGS": "1"},
     {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"}, {"DP_GEMM_2SM": "1"}, {"DP_GEMM_2SM": "4"}, {"DP_GEMM_2SM": "0"},
-    {"DP_GEMM_2SM": "6"}, {"DP_GEMM_2SM": "7"}, {"DP_PREFILL_TC": "0"},
+    {"DP_GEMM_2SM": "6"}, {"DP_GEMM_2SM": "7"}, {"DP_PREFILL_TC": "0"}, {"DP_GEMM_SPLIT_K": "0"}, {"DP_GEMM_RINGS": "2"},
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_alternative_kernels_stay_correct(tmp_path, env):
     script = tmp_path / "child.py"
