@@ -547,7 +547,11 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
   const uint32_t rank = cluster_ctarank();
   const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
   const int m0 = blockIdx.y * (256 * PS);
-  const int bpr = K / QK_K, num_k = K / BK;
+  // split over K as in the one-SM kernel: grid.z pairs per tile, whole super-blocks each, f32 adds into C
+  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
+  const int bpr_row = K / QK_K;
+  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;
+  const int num_k = bpr * (QK_K / BK);
   const int rot_b = cluster_x % bpr;  // K rotation of this pair (see the one-SM kernel)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
@@ -592,7 +596,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
         const uint32_t bar0 = mapa_shared(full_a(s), 0u);
 #pragma unroll
         for (int ps = 0; ps < PS; ps++)
-          tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, (((kt >> 2) + rot_b) % bpr * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
+          tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
       }
     }
   } else if (warp == 1) {
@@ -634,7 +638,7 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
     const int r8 = lane & 7, oct = lane >> 3;
     bool ok = true;
     const bool active = dw < dq;  // narrower tiles leave the last dequant warps without rows (they still do the epilogue)
-    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (int)rank * hb + (active ? dw : 0) * 8 + r8) * bpr * Q4K_BLOCK_BYTES);
+    const uint32_t *rowp = reinterpret_cast<const uint32_t *>(W + (size_t)(n0 + (int)rank * hb + (active ? dw : 0) * 8 + r8) * bpr_row * Q4K_BLOCK_BYTES) + (size_t)kb0 * Q4K_BLOCK_WORDS;
     const uint32_t *blk0 = rowp + (size_t)rot_b * Q4K_BLOCK_WORDS;
     uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk0));
     uint2 qn[4];
@@ -766,6 +770,12 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
             if constexpr (sizeof(OutT) == 4) {
+              if (k_splits > 1) {  // several pairs add their share of K into the same tile
+                float *gf = reinterpret_cast<float *>(g);
+                atomicAdd(gf, __uint_as_float(v.x)), atomicAdd(gf + 1, __uint_as_float(v.y));
+                atomicAdd(gf + 2, __uint_as_float(v.z)), atomicAdd(gf + 3, __uint_as_float(v.w));
+                continue;
+              }
               if (alpha.accumulate) {
                 const float4 old = *reinterpret_cast<const float4 *>(g);
                 v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
@@ -888,7 +898,11 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS));
+  const int splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
+  if constexpr (sizeof(OutT) == 4) {
+    if (splits > 1 && !alpha.accumulate) DP_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
+  }
+  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), splits);
   cfg.blockDim = dim3((BNMAX / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
@@ -959,6 +973,23 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
   // Tiles narrower than 128 columns are left to the one-SM kernel (N = 4096, M = 512 / 1024: 52 / 54 us there
   // against 62 / 64 us here; every SM re-reads its activation rows once per tile column, so narrow tiles
   // are bound by L2).  DP_GEMM_2SM=6 / 7 / 8 / 9 force other ring variants of the 192-wide instance.
+  // Few 512 x 256 pair tiles (N = 4096 at M <= 1024: 16 or 32), a long K and f32 output: 2 - 4 pairs per tile
+  // split K between them (whole super-blocks, at least twelve each) and add into C.  N = 4096, K = 12288:
+  // M = 512 74.6 us, M = 1024 115.6 us against 87.0 / 141.2 us on the one-SM kernel; at K = 4096 the zeroing
+  // and the adds cost more than the split saves (47.4 / 61.9 us against 41.7 / 53.3 us), hence the twelve.
+  static int split_k = -1;
+  if (split_k < 0) { const char *e = getenv("DP_GEMM_SPLIT_K"); split_k = e ? atoi(e) : 1; }
+  if constexpr (sizeof(OutT) == 4) {
+    if (two_sm == -1 && split_k && M > 256 && N % 256 == 0) {
+      const int clusters = ctx->sm_count / 2, tiles = (N / 256) * ((M + 511) / 512), bpr = K / QK_K;
+      for (int sp = 4; sp >= 2; sp--)
+        if (tiles * sp <= clusters && bpr % sp == 0 && bpr / sp >= 12) {
+          TcAlpha a2 = alpha;
+          a2.k_splits = sp;
+          return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, a2, N / 256, N / 256, 256, 256);
+        }
+    }
+  }
   if ((two_sm == -1 || (two_sm >= 6 && two_sm <= 10)) && M > 256 && N % 16 == 0) {
     const int clusters = ctx->sm_count / 2, rows = (M + 511) / 512;
     const int waves = (rows * ((N + 255) / 256) + clusters - 1) / clusters;
