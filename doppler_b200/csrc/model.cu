@@ -75,6 +75,7 @@ struct dp_model {
   // 9B-shaped step it costs more than it saves (2.113 ms with, 2.082 ms without; the prefetch traffic
   // lands on the current kernel's tail).
   bool prefetch_next = false;
+  bool recording_decode = false;  // set while a decode step is recorded into its CUDA graph
   bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel (DP_ATTN_FUSE_QK=0: separate kernel)
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
@@ -660,7 +661,8 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   static int prefill_tc = -1;
   if (prefill_tc < 0) { const char *e = getenv("DP_PREFILL_TC"); prefill_tc = e ? atoi(e) : 3; }
   bool handled = false;
-  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
+  // (batched decode steps, recorded into a CUDA graph, keep the CUDA-core kernel)
+  if (prefill_tc && M >= 32 && !m->recording_decode) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
@@ -924,7 +926,9 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
     dp_recorder *rec = nullptr;
     DP_TRY(dp_recorder_begin(ctx, "decode_step", 1, &rec));
     ctx->pdl = getenv("DP_PDL") ? atoi(getenv("DP_PDL")) != 0 : true;  // kernels of the step overlap their launch with the predecessor's tail
+    m->recording_decode = true;
     dp_status s = record_decode_step(m, batch);
+    m->recording_decode = false;
     ctx->pdl = false;
     if (s != DP_OK) { std::string keep = ctx->err; dp_recorder_abort(rec); ctx->err = keep; return s; }
     DP_TRY(dp_recorder_finish_graph(rec, &m->graph[slot]));
