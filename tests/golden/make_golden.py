@@ -4,6 +4,17 @@
 
 Inputs come from the seeded generators of the library (doppler_b200.synthetic) and from the
 reference's own LCG test-data generator; outputs are what the oracle computes for them.
+
+    python tests/golden/make_golden.py --receipt <reference checkout>
+
+copies the reference-held fixture of its 9B gate_proj receipt
+(reports/qwen-3-5-9b-metal/2026-07-12/layer0-ffn-gate-oracle/: block-d.f32, block-dmin.f32,
+packed-scale-bits.u8, packed-min-bits.u8) into receipt_9b_gate_headers.npz, together with the
+sha256 digests the receipt JSON records for the decoded scales and minima the reference computed
+from them (artifactFiles.decodedScales / decodedMinima).  Those digests are reference-produced
+numbers: tests/test_oracle_pins.py and tests/test_gpu_dequant.py hash what the oracle and the
+CUDA dequant kernel decode from the same headers and compare.  The same call copies two manifests of
+the reference's model catalog (models/local/<id>/manifest.json) for tests/test_rdrr.py.
 """
 import json
 import os
@@ -58,5 +69,43 @@ def main():
     print("wrote fixtures; min top1-top2 margin", min(margins))
 
 
+def receipt(ref_root):
+    base = os.path.join(ref_root, "reports", "qwen-3-5-9b-metal", "2026-07-12")
+    folder = os.path.join(base, "layer0-ffn-gate-oracle")
+    meta = json.load(open(os.path.join(base, "layer0-ffn-gate-oracle.json")))
+    d = np.fromfile(os.path.join(folder, "block-d.f32"), np.float32)
+    dmin = np.fromfile(os.path.join(folder, "block-dmin.f32"), np.float32)
+    sc = np.fromfile(os.path.join(folder, "packed-scale-bits.u8"), np.uint8)
+    mn = np.fromfile(os.path.join(folder, "packed-min-bits.u8"), np.uint8)
+    d16, dmin16 = d.astype(np.float16), dmin.astype(np.float16)
+    # the receipt stores the f16 block scales widened to f32: the narrowing is exact
+    assert np.array_equal(d16.astype(np.float32), d) and np.array_equal(dmin16.astype(np.float32), dmin)
+    assert sc.size == mn.size == 8 * d.size and int(sc.max()) < 64 and int(mn.max()) < 64
+    files = meta["artifactFiles"]
+    np.savez_compressed(
+        os.path.join(HERE, "receipt_9b_gate_headers.npz"),
+        d_f16=d16.view(np.uint16), dmin_f16=dmin16.view(np.uint16), scale_codes=sc, min_codes=mn,
+        shape=np.array(meta["artifacts"]["q4"]["tensorDescriptor"]["shape"], np.int64),
+        decoded_scales_sha256=np.array(files["decodedScales"]["sha256"]),
+        decoded_minima_sha256=np.array(files["decodedMinima"]["sha256"]),
+    )
+    print("wrote receipt_9b_gate_headers.npz:", d.size, "blocks")
+
+
+def manifests(ref_root):
+    """Two manifests of the reference's model catalog (models/local/*/manifest.json), gzip'd as they are."""
+    import gzip
+
+    for name in ("qwen-3-embedding-0-6b-q4k-ehf16-af32", "qwen-3-5-0-8b-q4k-ehaf16"):
+        raw = open(os.path.join(ref_root, "models", "local", name, "manifest.json"), "rb").read()
+        with gzip.GzipFile(os.path.join(HERE, "manifest__" + name + ".json.gz"), "wb", mtime=0) as f:
+            f.write(raw)
+        print("wrote manifest__%s.json.gz (%d bytes of JSON)" % (name, len(raw)))
+
+
 if __name__ == "__main__":
-    main()
+    if "--receipt" in sys.argv:
+        receipt(sys.argv[sys.argv.index("--receipt") + 1])
+        manifests(sys.argv[sys.argv.index("--receipt") + 1])
+    else:
+        main()

@@ -95,3 +95,20 @@ def test_full_size_round_trip_property(dev):
     assert np.abs(d1.ravel() - w).max() < 0.2 / 15 + 1e-3
     dev.release_buffer(t.buffer)
     dev.release_buffer(buf)
+
+
+def test_receipt_headers_decode_to_the_reference_digests(dev):
+    """The CUDA dequant kernel on the 196,608 real block headers of the reference's 9B gate_proj
+    receipt: decoded scales and minima hash to the digests the reference recorded for its own
+    dequantiser (layer0-ffn-gate-oracle.json, artifactFiles.decodedScales / decodedMinima)."""
+    from parity import receipt_headers, receipt_probe_blocks, sha256_f32
+
+    z = receipt_headers()
+    nb = z["d_f16"].size
+    for_minima, for_scales = receipt_probe_blocks()
+    w = _run_flat(dev, for_minima, nb).reshape(-1, 32)
+    assert np.all(w == w[:, :1])
+    assert sha256_f32(np.float32(0.0) - w[:, 0]) == str(z["decoded_minima_sha256"])
+    w = _run_flat(dev, for_scales, nb).reshape(-1, 32)
+    assert np.all(w == w[:, :1])
+    assert sha256_f32(w[:, 0]) == str(z["decoded_scales_sha256"])

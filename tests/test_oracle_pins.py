@@ -1,7 +1,11 @@
 """Pins the CPU oracle to the reference.
 
-The reference keeps no literal numeric vectors for this path and its JavaScript
-cannot run here, so the oracle is pinned three ways:
+Reference-produced numbers: the reference's retained 9B receipt
+(reports/qwen-3-5-9b-metal/2026-07-12/layer0-ffn-gate-oracle.json) records the sha256 of the
+decoded scales and minima its own dequantiser produced for the 196,608 block headers of a real
+[12288, 4096] Q4_K tensor; the headers are committed under tests/golden/ and the oracle must
+reproduce both digests (test_receipt_* below).  Beyond that the reference's JavaScript cannot
+run here, so the oracle is also pinned three ways:
  1. the reference's own procedural unit tests are re-run against it (same inputs,
     same assertions): tests/converter/quantizer.test.js, tests/gpu/dequant-numeric.test.js,
     tests/tooling/q4k-projection-reference.test.js, tests/kernels/browser/kernel-suite.js;
@@ -368,3 +372,36 @@ def test_small_ops_against_numpy():
     assert O.argmax(np.array([1, 5, 7, 2], np.float32), pad_id=2) == 1
     emb = rng.standard_normal((10, 4)).astype(np.float16)
     assert np.array_equal(O.gather_f16(emb, [3, 7], 4), emb[[3, 7]].astype(np.float32))
+
+
+# ---- reference-produced digests: the 9B gate_proj receipt ---------------------------------
+def test_receipt_header_fields_decode_back():
+    """The a1 packing rule round-trips through the oracle's header reader on real headers."""
+    from parity import pack_q4k_headers, receipt_headers
+
+    z = receipt_headers()
+    nb = 4096
+    blocks = pack_q4k_headers(z["d_f16"][:nb], z["dmin_f16"][:nb], z["scale_codes"][: 8 * nb], z["min_codes"][: 8 * nb], 0x5A)
+    for b in range(0, nb, 257):
+        sc, mn, d, dm = O.q4k_decode_header(blocks[b * BLOCK:(b + 1) * BLOCK])
+        assert np.array_equal(sc, z["scale_codes"][8 * b: 8 * b + 8]) and np.array_equal(mn, z["min_codes"][8 * b: 8 * b + 8])
+        assert d == float(z["d_f16"][b: b + 1].view(np.float16)[0]) and dm == float(z["dmin_f16"][b: b + 1].view(np.float16)[0])
+
+
+def test_receipt_decoded_scales_and_minima_match_the_reference_digests():
+    """quantizer.js:204-209 / q4k-projection-reference.js:26-37 on 1,572,864 real sub-blocks: the
+    oracle's dequantiser, fed the receipt's headers, yields exactly the bytes whose sha256 the
+    reference recorded (artifactFiles.decodedScales / decodedMinima)."""
+    from parity import receipt_headers, receipt_probe_blocks, sha256_f32
+
+    z = receipt_headers()
+    n_blocks = z["d_f16"].size
+    assert n_blocks == int(z["shape"][0]) * int(z["shape"][1]) // QK_K == 196608
+    for_minima, for_scales = receipt_probe_blocks()
+    w = O.q4k_dequant_flat(for_minima, n_blocks * QK_K).reshape(-1, 32)
+    assert np.all(w == w[:, :1])  # one value per sub-block
+    minima = np.float32(0.0) - w[:, 0]
+    assert sha256_f32(minima) == str(z["decoded_minima_sha256"])
+    w = O.q4k_dequant_flat(for_scales, n_blocks * QK_K).reshape(-1, 32)
+    assert np.all(w == w[:, :1])
+    assert sha256_f32(w[:, 0]) == str(z["decoded_scales_sha256"])

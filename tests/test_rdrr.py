@@ -197,3 +197,36 @@ def test_load_decoder_from_artifact(dev, tmp_path):
         model.destroy()
     with pytest.raises(rdrr.RdrrError, match="exceeds the model's maxSeqLen"):
         rdrr.load_decoder(dev, str(tmp_path), 10 ** 9)
+
+
+# ---- manifests the reference ships (models/local/<id>/manifest.json, committed gzip'd) ----------
+def _reference_manifest(name):
+    import gzip
+
+    return gzip.open(os.path.join(GOLDEN, "manifest__" + name + ".json.gz"), "rt", encoding="utf-8").read()
+
+
+def test_reference_manifest_of_the_0_6b_q4k_model_parses_to_the_baseline_shape():
+    m = rdrr.parse_manifest(_reference_manifest("qwen-3-embedding-0-6b-q4k-ehf16-af32"))
+    assert m["quantization"] == "Q4_K_M" and len(m["tensors"]) == 310
+    cfg = rdrr.decoder_config(m)
+    want = dict(n_layers=28, hidden=1024, n_heads=16, n_kv_heads=8, head_dim=128, inter=3072, eps=1e-6, rope_theta=1e6)
+    for k, v in want.items():
+        assert cfg[k] == v, k
+    assert cfg["tie_word_embeddings"] is True
+    tmap = rdrr.parse_tensor_map(m["tensors"])
+    H, I = cfg["hidden"], cfg["inter"]
+    # packed Q4_K sizes follow N * ceil(K/256) * 144 (matmul-selection.js:230-233), row layout
+    for name, (n, k) in {"q_proj": (2048, H), "k_proj": (1024, H), "o_proj": (H, 2048), "gate_proj": (I, H), "down_proj": (H, I)}.items():
+        hits = [t for key, t in tmap.items() if key.endswith("layers.0." + ("self_attn." if "_proj" in name and name[0] in "qkvo" else "mlp.") + name + ".weight")]
+        assert len(hits) == 1, name
+        t = hits[0]
+        assert t["dtype"] == "Q4_K_M" and t.get("layout", "row") == "row" and list(t["shape"]) == [n, k]
+        assert t["size"] == n * ((k + 255) // 256) * 144
+
+
+def test_reference_manifest_outside_the_path_is_refused_with_the_reason():
+    m = rdrr.parse_manifest(_reference_manifest("qwen-3-5-0-8b-q4k-ehaf16"))
+    assert len(m["tensors"]) == 489
+    with pytest.raises(rdrr.RdrrError, match="attentionOutputGate"):
+        rdrr.decoder_config(m)
