@@ -42,7 +42,7 @@ class WeightS(C.Structure):
 
 class MatmulOpts(C.Structure):
     _fields_ = [("alpha", C.c_float), ("out_dtype", C.c_int), ("a_off", C.c_size_t), ("b_off", C.c_size_t),
-                ("c_off", C.c_size_t), ("out_buf", C.c_void_p), ("transpose_b", C.c_int), ("exact_weights", C.c_int)]
+                ("c_off", C.c_size_t), ("out_buf", C.c_void_p), ("transpose_b", C.c_int), ("exact_weights", C.c_int), ("f16_weights", C.c_int)]
 
 
 class AttnOpts(C.Structure):
@@ -109,6 +109,7 @@ SIGNATURES = {
     "dp_recorder_abort": (_i, [_vp]),
     "dp_recorder_finish_graph": (_i, [_vp, C.POINTER(_vp)]),
     "dp_graph_launch": (_i, [_vp]),
+    "dp_graph_launch_timed": (_i, [_vp, _i, C.POINTER(_dbl)]),
     "dp_graph_destroy": (None, [_vp]),
     "dp_recorder_op_count": (_u32, [_vp]),
     "dp_matmul_opts_default": (None, [C.POINTER(MatmulOpts)]),

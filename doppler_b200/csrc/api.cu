@@ -222,7 +222,12 @@ dp_status dp_out_buffer(dp_ctx *ctx, dp_buf out_buf, size_t offset, size_t bytes
 
 dp_status dp_scratch(dp_ctx *ctx, dp_buf *slot, size_t bytes, const char *label) {
   if (*slot && (*slot)->capacity >= bytes) return DP_OK;
-  if (*slot) { DP_TRY(dp_buf_release(ctx, *slot)); *slot = nullptr; }
+  if (*slot) {
+    const bool capturing = ctx->active_recorder && ctx->active_recorder->capture;
+    if (capturing || ctx->live_graphs > 0) ctx->retired_scratch.push_back(*slot);  // a graph may still point at it
+    else DP_TRY(dp_buf_release(ctx, *slot));
+    *slot = nullptr;
+  }
   return dp_buf_acquire(ctx, bytes, label, slot);
 }
 
@@ -298,6 +303,9 @@ static dp_status end_capture(dp_recorder *rec, dp_graph **out) {
   }
   // kernels recorded during capture did not run yet; they are counted per launch
   ctx->launches = rec->launches_at_begin;
+  // the graph's kernels keep pointing at the recording's temporaries: they live as long as the graph
+  gr->owned.swap(rec->temporaries);
+  ctx->live_graphs++;
   *out = gr;
   return DP_OK;
 }
@@ -363,9 +371,40 @@ extern "C" dp_status dp_graph_launch(dp_graph *g) {
   return DP_OK;
 }
 
+// `reps` replays between two CUDA events on the context's stream; *ms receives the device time of all of them
+extern "C" dp_status dp_graph_launch_timed(dp_graph *g, int reps, double *ms) {
+  if (!g || !ms || reps < 1) return DP_ERR_INVALID;
+  dp_ctx *ctx = g->ctx;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  DP_CUDA(ctx, cudaEventCreate(&e0));
+  cudaError_t e = cudaEventCreate(&e1);
+  if (e == cudaSuccess) e = cudaEventRecord(e0, ctx->stream);
+  for (int i = 0; i < reps && e == cudaSuccess; i++) {
+    e = cudaGraphLaunch(g->exec, ctx->stream);
+    ctx->launches += g->kernels;
+  }
+  if (e == cudaSuccess) e = cudaEventRecord(e1, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  float t = 0.0f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&t, e0, e1);
+  cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "timed graph launch: %s", cudaGetErrorString(e));
+  *ms = t;
+  return DP_OK;
+}
+
 extern "C" void dp_graph_destroy(dp_graph *g) {
   if (!g) return;
+  dp_ctx *ctx = g->ctx;
   if (g->exec) cudaGraphExecDestroy(g->exec);
   if (g->graph) cudaGraphDestroy(g->graph);
+  // launches of the graph are ordered on the context's stream, so are later users of these buffers
+  for (dp_buf b : g->owned) dp_buf_release(ctx, b);
+  if (ctx && --ctx->live_graphs <= 0) {
+    ctx->live_graphs = 0;
+    for (dp_buf b : ctx->retired_scratch) dp_buf_release(ctx, b);
+    ctx->retired_scratch.clear();
+  }
   delete g;
 }

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(ATT_THREADS, LPK == 16 ? 2 : 1) attn_split_ker
   const int G = p.num_heads / p.num_kv_heads;
   const int h0 = kvh * G + ht * GT;  // first query head of this CTA
 
-  int kv_len = p.kv_lens ? p.kv_lens[b] : p.kv_len;
+  int kv_len = p.kv_lens ? min(max(p.kv_lens[b], 0), p.kv_len) : p.kv_len;  // the host checked the cache for p.kv_len keys
   const AttnRange r = attn_range(kv_len, p.causal, p.start_pos, qi, p.sliding_window, p.kv_start);
   const int n_keys = r.hi - r.lo;
   const int per_split = (n_keys + splits - 1) / splits;
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(128) attn_split_generic_kernel(dpk_attn_params
   const int split = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
   const int b = z / p.seq_len, qi = z % p.seq_len;
   const int kvh = h / (p.num_heads / p.num_kv_heads);
-  int kv_len = p.kv_lens ? p.kv_lens[b] : p.kv_len;
+  int kv_len = p.kv_lens ? min(max(p.kv_lens[b], 0), p.kv_len) : p.kv_len;  // the host checked the cache for p.kv_len keys
   const AttnRange r = attn_range(kv_len, p.causal, p.start_pos, qi, p.sliding_window, p.kv_start);
   const int n_keys = r.hi - r.lo;
   const int per_split = (n_keys + splits - 1) / splits;

@@ -55,7 +55,9 @@ extern "C" dp_status dp_attention_decode_static(void *stream, const float *q, co
   if (e != cudaSuccess || device < 0 || device >= 64)
     return static_fail(DP_ERR_CUDA, std::string("attention (static scratch): no current CUDA device: ") + cudaGetErrorString(e));
   if (!g_scratch_addr[device]) {
-    // once per device, with that device current: the symbol's address on THIS device
+    // once per device, with that device current: the symbol's address on THIS device.  The table is
+    // filled without a lock: two host threads that race here both look the address up and both
+    // store the same pointer, which is harmless (an aligned pointer store is not torn).
     float *p = nullptr;
     e = cudaGetSymbolAddress((void **)&p, g_static_attn_scratch);
     if (e != cudaSuccess || !p)

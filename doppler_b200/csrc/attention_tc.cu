@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
   const int G = p.num_heads / p.num_kv_heads;
   const int h0 = kvh * G + ht * gt;
 
-  int kv_len = p.kv_lens ? p.kv_lens[b] : p.kv_len;
+  int kv_len = p.kv_lens ? min(max(p.kv_lens[b], 0), p.kv_len) : p.kv_len;  // the host checked the cache for p.kv_len keys
   int lo = 0, hi = kv_len;
   {
     const int abs_q = p.start_pos + qi;

@@ -41,14 +41,14 @@ struct dp_ctx {
   dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
   dp_buf gemm_scratch = nullptr;  // f16 activations (halves, residues, row scales) of the tensor-core GEMM (stream ordered)
   bool pdl = false;  // launch with programmatic dependent launch (set while the decode step is recorded)
-  // Weight matrix of the NEXT Q4_K GEMV in program order (set by the decode schedule, consumed by the
-  // next TMA GEMV launch): that launch's producer warps pull its first row tiles into L2 once their own
-  // copies are issued, so the next kernel's pipeline fills from L2 instead of HBM.
-  const void *gemv_next_w = nullptr;
-  int gemv_next_rows = 0, gemv_next_k = 0;
   int *dev_status = nullptr;  // device word raised by a kernel whose bounded wait gave up
   dp_recorder *active_recorder = nullptr;
   dp_tp_state *tp = nullptr;
+  // Captured graphs keep device pointers.  While a capture is open or a graph of this context is alive,
+  // a context scratch that has to grow is not handed back to the pool (a later acquire could give it to
+  // somebody else while a graph replay still writes it): it waits here until the last graph is destroyed.
+  int live_graphs = 0;
+  std::vector<dp_buf> retired_scratch;
 };
 
 struct dp_recorder {
@@ -66,6 +66,7 @@ struct dp_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   uint64_t kernels = 0;
+  std::vector<dp_buf> owned;  // the recording's temporaries: the graph's kernels point at them until it is destroyed
 };
 
 dp_status dp_fail(dp_ctx *ctx, dp_status st, const char *fmt, ...);

@@ -81,7 +81,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
-// ---- two-CTA cluster helpers (PAIR variant) ----
+// ---- two-CTA cluster helpers (two-SM kernel) ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -91,9 +91,6 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) { 
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
-}
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
@@ -118,12 +115,6 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
   *abort_flag = 1;
   return false;
 }
-// commit that arrives on the same barrier offset in both CTAs of the pair
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-               "h"((uint16_t)3)
-               : "memory");
-}
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -141,7 +132,6 @@ struct TcAlpha {
   const float *row_scale;
   int weight_residue;  // 1: the B tile holds w - f16(w), the part of each weight that f16 rounding drops
   int accumulate;      // 1: the epilogue adds to C instead of overwriting it (f32 output only)
-  int k_splits;        // one-SM kernel: parts of K per tile (grid.z), added into C by atomics (f32 output only)
 };
 
 // two dequantised weights as f16, or their f16 rounding residues
@@ -171,13 +161,8 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) 
   return l;
 }
 
-// PAIR: two CTAs of a cluster own the two 256-row halves of a 512 x BN output tile.  They need the same
-// weight tile, so each dequantises half of its rows and stores them into BOTH CTAs' shared memory
-// (distributed shared memory); every weight is then dequantised once per 512 rows instead of once per
-// 256.  The tensor-core side is unchanged: each CTA issues its own cta_group::1 MMAs on its own copy.
-// MT = number of 128-row accumulators per CTA (output tile 128*MT x BN).  MT = 4 with BN = 96 covers 512
-// rows per CTA, so that at M = 512 every weight is dequantised by one CTA only.
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, bool PAIR, int MT = 2>
+// MT = number of 128-row accumulators per CTA (output tile 128*MT x BN).
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, int MT = 2>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, TcAlpha alpha, int *__restrict__ err) {
@@ -187,11 +172,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   static_assert(MT * BN <= 512, "accumulators exceed tensor memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
-  // Split over K (grid.z parts, whole super-blocks each): a problem of few tiles (N = 4096 at M <= 512 is 64)
-  // fills the GPU with several CTAs per tile, whose epilogues add into a zeroed (or accumulated) f32 C.
-  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
   const int bpr_row = K / QK_K;                       // super-blocks per weight row
-  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;  // this CTA's share
+  const int bpr = bpr_row, kb0 = 0;
   const int num_k = bpr * (QK_K / BK);
   // Every CTA walks K in its own rotation (by whole super-blocks).  All CTAs of a grid row need the same
   // activation tiles; in lockstep they would all ask the same few L2 lines for them at the same time, and
@@ -216,10 +198,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   pdl_wait();
   if (tid == 0) {
     for (int s = 0; s < SA; s++) mbar_init(full_a(s), 1);
-    // PAIR: a weight stage is full when the dequant warps of both CTAs have arrived, and a step is done
-    // when the tensor cores of both CTAs have read its stages
-    for (int s = 0; s < SB; s++) mbar_init(full_b(s), PAIR ? 2 * DQ_WARPS : DQ_WARPS);
-    for (int s = 0; s < SD; s++) mbar_init(done(s), PAIR ? 2 : 1);
+    for (int s = 0; s < SB; s++) mbar_init(full_b(s), DQ_WARPS);
+    for (int s = 0; s < SD; s++) mbar_init(done(s), 1);
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -232,11 +212,6 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  uint32_t pair_rank = 0;
-  if constexpr (PAIR) {
-    pair_rank = cluster_ctarank();
-    cluster_sync_all();  // the peer's barriers exist before anyone arrives on them remotely
-  }
 
   if (warp == 0) {
     // ---------------- activation tiles: TMA ----------------
@@ -259,8 +234,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
       for (int kt = 0; kt < num_k && ok; kt++) {
         const int sa = kt % SA, sb = kt % SB;
         if (!mbar_wait_bounded(full_a(sa), (uint32_t)(kt / SA) & 1u, abort_flag)) { ok = false; break; }
-        if (PAIR ? !mbar_wait_bounded_cluster(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)
-                 : !mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_bounded(full_b(sb), (uint32_t)(kt / SB) & 1u, abort_flag)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(smem + L.a + (uint32_t)sa * L.stage_a);
         const uint32_t b_addr = smem_u32(smem + L.b + (uint32_t)sb * L.stage_b);
@@ -273,7 +247,7 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
         }
         // both stages are free once these MMAs have read them
-        if constexpr (PAIR) umma_commit_pair(done(kt % SD)); else umma_commit(done(kt % SD));
+        umma_commit(done(kt % SD));
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -282,11 +256,9 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     const int dw = warp - 2;            // 0..7
     const int r8 = lane & 7, oct = lane >> 3;  // row within the 8-row group, byte octet of the 32-byte chunk
     bool ok = true;
-    constexpr int RG = BN / 8 / DQ_WARPS / (PAIR ? 2 : 1);  // 8-row groups per warp (PAIR: this CTA's half of the tile)
-    static_assert(RG >= 1 && RG * DQ_WARPS * 8 * (PAIR ? 2 : 1) == BN, "dequant warps must tile the weight rows");
-    const int grp0 = PAIR ? (int)pair_rank * (BN / 16) : 0;  // first 8-row group this CTA dequantises
-    const uint32_t b_local = smem_u32(smem + L.b);
-    const uint32_t b_peer = PAIR ? mapa_shared(b_local, pair_rank ^ 1u) : 0u;
+    constexpr int RG = BN / 8 / DQ_WARPS;  // 8-row groups per warp
+    static_assert(RG >= 1 && RG * DQ_WARPS * 8 == BN, "dequant warps must tile the weight rows");
+    constexpr int grp0 = 0;
     // software pipeline at super-block granularity: while the four K steps of block b are dequantised,
     // the header and the four quant pieces of block b+1 are already in flight
     uint4 hdr[RG];
@@ -379,33 +351,20 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           const uint32_t off_lo = ((uint32_t)oct ^ (uint32_t)r8) << 4, off_hi = ((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4;
           *reinterpret_cast<uint4 *>(line + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
           *reinterpret_cast<uint4 *>(line + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-          if constexpr (PAIR) {  // the same two chunks into the peer CTA's copy of the stage
-            const uint32_t rline = b_peer + (smem_u32(line) - b_local);
-            st_cluster_v4(rline + off_lo, lo[0], lo[1], lo[2], lo[3]);
-            st_cluster_v4(rline + off_hi, hi[0], hi[1], hi[2], hi[3]);
-          }
         }
         if constexpr (!BLOCK_SYNC) {
-          // generic-proxy stores -> visible to the tensor core (of both CTAs in the PAIR variant)
-          if constexpr (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
-          else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          // generic-proxy stores -> visible to the tensor core
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(full_b(s));
-            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b(s), pair_rank ^ 1u));
-          }
+          if (lane == 0) mbar_arrive(full_b(s));
         }
       }
       if constexpr (BLOCK_SYNC) {
-        if constexpr (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
-        else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
 #pragma unroll
-          for (int chunk = 0; chunk < 4; chunk++) {
-            mbar_arrive(full_b((kb * 4 + chunk) % SB));
-            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(full_b((kb * 4 + chunk) % SB), pair_rank ^ 1u));
-          }
+          for (int chunk = 0; chunk < 4; chunk++) mbar_arrive(full_b((kb * 4 + chunk) % SB));
         }
       }
     }
@@ -467,12 +426,6 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
             if constexpr (sizeof(OutT) == 4) {
-              if (k_splits > 1) {  // several CTAs add their share of K into the same tile
-                float *gf = reinterpret_cast<float *>(g);
-                atomicAdd(gf, __uint_as_float(v.x)), atomicAdd(gf + 1, __uint_as_float(v.y));
-                atomicAdd(gf + 2, __uint_as_float(v.z)), atomicAdd(gf + 3, __uint_as_float(v.w));
-                continue;
-              }
               if (alpha.accumulate) {
                 const float4 old = *reinterpret_cast<const float4 *>(g);
                 v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
@@ -488,7 +441,6 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if constexpr (PAIR) cluster_sync_all();  // no CTA leaves while its peer may still store into it or arrive on its barriers
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -547,10 +499,8 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
   const uint32_t rank = cluster_ctarank();
   const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
   const int m0 = blockIdx.y * (256 * PS);
-  // split over K as in the one-SM kernel: grid.z pairs per tile, whole super-blocks each, f32 adds into C
-  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
   const int bpr_row = K / QK_K;
-  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;
+  const int bpr = bpr_row, kb0 = 0;
   const int num_k = bpr * (QK_K / BK);
   const int rot_b = cluster_x % bpr;  // K rotation of this pair (see the one-SM kernel)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
@@ -770,12 +720,6 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
             if constexpr (sizeof(OutT) == 4) {
-              if (k_splits > 1) {  // several pairs add their share of K into the same tile
-                float *gf = reinterpret_cast<float *>(g);
-                atomicAdd(gf, __uint_as_float(v.x)), atomicAdd(gf + 1, __uint_as_float(v.y));
-                atomicAdd(gf + 2, __uint_as_float(v.z)), atomicAdd(gf + 3, __uint_as_float(v.w));
-                continue;
-              }
               if (alpha.accumulate) {
                 const float4 old = *reinterpret_cast<const float4 *>(g);
                 v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
@@ -857,35 +801,11 @@ EncodeTiledFn get_encode() {
 
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  // few tiles and f32 output: split K over 2 .. 4 CTAs per tile (whole super-blocks, at least four each)
-  int splits = 1;
-  static int split_k = -1;
-  if (split_k < 0) { const char *e = getenv("DP_GEMM_SPLIT_K"); split_k = e ? atoi(e) : 1; }
-  if constexpr (sizeof(OutT) == 4) {
-    const int tiles = (N / BN) * ((M + BM - 1) / BM), bpr = K / QK_K;
-    for (int sp = 4; sp >= 2 && split_k; sp--)
-      if (tiles * sp <= ctx->sm_count && bpr % sp == 0 && bpr / sp >= 4) { splits = sp; break; }
-    if (splits > 1 && !alpha.accumulate) DP_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
-  }
-  alpha.k_splits = splits;
   const size_t smem = tc_layout(BN, SA, SB).total + 1024;
   static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(N / BN, (M + BM - 1) / BM, splits);
-  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, false>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
-  return DP_OK;
-}
-
-// 512 x 96 tiles (four accumulators): one CTA covers 512 rows, so at M <= 512 each weight is dequantised once
-template <typename OutT>
-dp_status launch_tc_wide_m(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  constexpr int BN = 96, DQ = 12, SA = 2, SB = 4, MT = 4;
-  const size_t smem = tc_layout(BN, SA, SB, MT).total + 1024;
-  static_assert(MT * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  auto kernel = gemm_q4k_tc_kernel<BN, DQ, OutT, SA, SB, false, MT>;
-  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(N / BN, (M + 128 * MT - 1) / (128 * MT));
-  DP_LAUNCH(ctx, kernel, grid, (DQ + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(N / BN, (M + BM - 1) / BM, 1);
+  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
   return DP_OK;
 }
 
@@ -898,11 +818,7 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  const int splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
-  if constexpr (sizeof(OutT) == 4) {
-    if (splits > 1 && !alpha.accumulate) DP_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
-  }
-  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), splits);
+  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), 1);
   cfg.blockDim = dim3((BNMAX / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
@@ -919,78 +835,18 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc2_kernel failed: %s", cudaGetErrorString(e));
   return DP_OK;
 }
-// uniform tiles of BN columns
-template <typename OutT, int BN, int SA, int SB, int CH = 2>
-dp_status launch_tc_2sm_uniform(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  return launch_tc_2sm<OutT, BN, SA, SB, CH>(ctx, tm, W, C, M, N, K, alpha, N / BN, N / BN, BN, BN);
-}
-
-// PAIR variant: clusters of two CTAs along the M tiles (an even number of 256-row tiles)
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
-dp_status launch_tc_pair(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  const size_t smem = tc_layout(BN, SA, SB).total + 1024;
-  auto kernel = gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, true>;
-  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(N / BN, (M + BM - 1) / BM);
-  cfg.blockDim = dim3((DQ_WARPS + 2) * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 2;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status);
-  ctx->launches++;
-  if (e == cudaSuccess) e = cudaGetLastError();
-  if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc_kernel (paired) failed: %s", cudaGetErrorString(e));
-  return DP_OK;
-}
-
 template <typename OutT>
 dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  // Equal depths (3 + 3) measured fastest on the 512 x 12288 x 4096 case: 65.1 us against 69.7 us with a
-  // five-deep weight ring, whose extra 50 KB of shared memory come out of the L1 the weight loads use.
-  // DP_GEMM_RINGS=1 selects the deeper weight ring, 2 (128-wide tiles) a weight ring of eight stages filled a
-  // super-block at a time; neither is faster (N = 4096, K = 12288, M = 1024: 141 / 147 / 143 us), nor are sixteen
-  // dequant warps instead of eight (148 us).
-  static int rings = -1;
-  if (rings < 0) { const char *e = getenv("DP_GEMM_RINGS"); rings = e ? atoi(e) : 0; }
-  // Two-SM kernel (tcgen05.mma.cta_group::2).  On 512 x 256 pair tiles its 256-wide MMAs fetch 8 KB of
-  // operands per SM and 128 cycles instead of 10 KB per 96, and the tensor pipe runs about 1.3x faster per
-  // SM.  It needs whole waves of 74 clusters to win (at M = 512, 48 tiles of 256 columns occupy 96 SMs), so
-  // the default below sizes the tiles to the waves.  DP_GEMM_2SM=0 never; 4 / 5 / 13 uniform 512 x 256
-  // tiles (ring depths 3+4 / 4+5 / 3+8); 1 / 2 / 3 uniform 512 x 192 tiles.
-  static int two_sm = -2;
-  if (two_sm == -2) { const char *e = getenv("DP_GEMM_2SM"); two_sm = e ? atoi(e) : -1; }
-  // Whole waves of even tiles (M > 256): with R = ceil(M / 512) rows of pair tiles, take the fewest waves of 74
-  // clusters that 256-wide tiles need, then as many column tiles per row as those waves hold, in two
-  // widths 16 apart.  N = 12288: M = 512 runs one wave of 28 x 176 + 46 x 160 columns instead of 48 tiles
-  // on 96 SMs; M = 2048 three waves of 55 tiles (53 x 224 + 2 x 208) instead of 48 x 256 in 2.6 waves.
-  // Tiles narrower than 128 columns are left to the one-SM kernel (N = 4096, M = 512 / 1024: 52 / 54 us there
-  // against 62 / 64 us here; every SM re-reads its activation rows once per tile column, so narrow tiles
-  // are bound by L2).  DP_GEMM_2SM=6 / 7 / 8 / 9 force other ring variants of the 192-wide instance.
-  // Few 512 x 256 pair tiles (N = 4096 at M <= 1024: 16 or 32), a long K and f32 output: 2 - 4 pairs per tile
-  // split K between them (whole super-blocks, at least twelve each) and add into C.  N = 4096, K = 12288:
-  // M = 512 74.6 us, M = 1024 115.6 us against 87.0 / 141.2 us on the one-SM kernel; at K = 4096 the zeroing
-  // and the adds cost more than the split saves (47.4 / 61.9 us against 41.7 / 53.3 us), hence the twelve.
-  static int split_k = -1;
-  if (split_k < 0) { const char *e = getenv("DP_GEMM_SPLIT_K"); split_k = e ? atoi(e) : 1; }
-  if constexpr (sizeof(OutT) == 4) {
-    if (two_sm == -1 && split_k && M > 256 && N % 256 == 0) {
-      const int clusters = ctx->sm_count / 2, tiles = (N / 256) * ((M + 511) / 512), bpr = K / QK_K;
-      for (int sp = 4; sp >= 2; sp--)
-        if (tiles * sp <= clusters && bpr % sp == 0 && bpr / sp >= 12) {
-          TcAlpha a2 = alpha;
-          a2.k_splits = sp;
-          return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, a2, N / 256, N / 256, 256, 256);
-        }
-    }
-  }
-  if ((two_sm == -1 || (two_sm >= 6 && two_sm <= 10)) && M > 256 && N % 16 == 0) {
+  // Two-SM kernel (tcgen05.mma.cta_group::2) for M > 256.  On 512 x 256 pair tiles its 256-wide MMAs fetch
+  // 8 KB of operands per SM and 128 cycles instead of 10 KB per 96, and the tensor pipe runs about 1.3x
+  // faster per SM.  It needs whole waves of 74 clusters to win (at M = 512, 48 uniform tiles of 256 columns
+  // occupy 96 SMs), so the tiles are sized to the waves: with R = ceil(M / 512) rows of pair tiles, take the
+  // fewest waves of 74 clusters that 256-wide tiles need, then as many column tiles per row as those waves
+  // hold, in two widths 16 apart.  N = 12288: M = 512 runs one wave of 28 x 176 + 46 x 160 columns; M = 2048
+  // three waves of 55 tiles (53 x 224 + 2 x 208).  Tiles narrower than 128 columns are left to the one-SM
+  // kernel (every SM re-reads its activation rows once per tile column, so narrow tiles are bound by L2).
+  // Measurements of the alternatives that were tried and dropped: profiles/gemm_q4k_tc__config1.md.
+  if (M > 256 && N % 16 == 0) {
     const int clusters = ctx->sm_count / 2, rows = (M + 511) / 512;
     const int waves = (rows * ((N + 255) / 256) + clusters - 1) / clusters;
     int cols = waves * clusters / rows;
@@ -999,59 +855,44 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
       const int narrow = (N / 16 / cols) * 16;
       const int n_wide = (N - cols * narrow) / 16;  // cols * narrow + 16 * n_wide == N, n_wide < cols
       const int wide = narrow + 16, widest = n_wide ? wide : narrow;
-      const bool forced = two_sm != -1;
-      if ((narrow >= 128 || (forced && narrow >= 96)) && widest <= 192) {
-        if (two_sm == 6) return launch_tc_2sm<OutT, 192, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-        if (two_sm == 7) return launch_tc_2sm<OutT, 192, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-        if (two_sm == 8) return launch_tc_2sm<OutT, 192, 6, 8, 2, 1>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-        if (two_sm == 9) return launch_tc_2sm<OutT, 192, 8, 6, 2, 1>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-        // activation ring of four, weight ring of two whole super-blocks (four K steps per synchronisation)
-        return launch_tc_2sm<OutT, 192, 4, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-      }
-      if (narrow >= 128 && widest <= 256 && !forced) return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      // activation ring of four, weight ring of two whole super-blocks (four K steps per synchronisation)
+      if (narrow >= 128 && widest <= 192) return launch_tc_2sm<OutT, 192, 4, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      if (narrow >= 128 && widest <= 256) return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
     }
   }
-  if (((two_sm >= 4 && two_sm <= 5) || two_sm == 13) && M > 256 && N % 256 == 0) {  // 512 x 256 pair tiles: 256-wide MMAs
-    if (two_sm == 13) return launch_tc_2sm_uniform<OutT, 256, 3, 8, 4>(ctx, tm, W, C, M, N, K, alpha);
-    if (two_sm == 5) return launch_tc_2sm_uniform<OutT, 256, 4, 5>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_2sm_uniform<OutT, 256, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
-  }
-  if (two_sm >= 1 && two_sm <= 3 && M > 256 && N % 192 == 0) {
-    if (two_sm == 2) return launch_tc_2sm_uniform<OutT, 192, 3, 4>(ctx, tm, W, C, M, N, K, alpha);
-    if (two_sm == 3) return launch_tc_2sm_uniform<OutT, 192, 5, 4>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_2sm_uniform<OutT, 192, 4, 7>(ctx, tm, W, C, M, N, K, alpha);
-  }
-  // DP_GEMM_WIDE_M=1: 512 x 96 tiles when M > 256 (each weight dequantised once per 512 rows).  Off by
-  // default: measured slower (512 x 12288 x 4096: 71.7 us against 65.9 us; M = 2048: 273.8 us against 243 us):
-  // halving the dequantisation does not pay for N = 96 MMAs, which read more shared memory per flop, and
-  // for twice the activation traffic from L2.
-  static int wide_m = -1;
-  if (wide_m < 0) { const char *e = getenv("DP_GEMM_WIDE_M"); wide_m = e ? atoi(e) : 0; }
-  if (wide_m && M > 256 && N % 96 == 0) return launch_tc_wide_m<OutT>(ctx, tm, W, C, M, N, K, alpha);
-  // DP_GEMM_PAIR=1: with an even number of 256-row tiles, pairs of CTAs share the dequantisation through
-  // distributed shared memory.  Correct (same parity tests), but measured slower on 512 x 12288 x 4096:
-  // 101.6 us against 66.5 us, because the proxy fence in front of each stage's arrive has to wait for the
-  // remote stores to land, once per K step and warp.  Off by default.
-  static int pair = -1;
-  if (pair < 0) { const char *e = getenv("DP_GEMM_PAIR"); pair = e ? atoi(e) : 0; }
-  const int m_tiles = (M + BM - 1) / BM;
-  if (pair && m_tiles % 2 == 0) {
-    if (bn == 192) return launch_tc_pair<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
-    return launch_tc_pair<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
-  }
-  if (bn == 192) return rings ? launch_tc<192, 12, OutT, 3, 5>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
-  if (rings == 2) return launch_tc<128, 8, OutT, 3, 8>(ctx, tm, W, C, M, N, K, alpha);
-  return rings ? launch_tc<128, 8, OutT, 4, 6>(ctx, tm, W, C, M, N, K, alpha) : launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  // one-SM kernel, equal ring depths (3 + 3 measured fastest on 512 x 12288 x 4096)
+  if (bn == 192) return launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  return launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
 }
 
 }  // namespace
 
+// C (f16) = f16(alpha-scaled f32 sums), the rounding the reference's f16-output kernels apply at the store
+// (fused_matmul_q4_batched_f16a.wgsl:151)
+__global__ void cast_f32_f16_out_kernel(const float *__restrict__ in, __half *__restrict__ out, size_t n) {
+  pdl_launch();
+  pdl_wait();
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      const float4 v = *reinterpret_cast<const float4 *>(in + i);
+      const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+      *reinterpret_cast<uint2 *>(out + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+    } else {
+      for (size_t j = i; j < n; j++) out[j] = __float2half_rn(in[j]);
+    }
+  }
+}
+
 static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
                                   int N, int K, float alpha, int mode, bool *handled) {
-  // mode 0: A as given (f32 is cast to f16).  1: f32 rows scaled into f16 range, one pass.  2: as 1, in three
-  // passes A_hi.W_hi + A_lo.W_hi + A_hi.W_lo with the f16 rounding residues of A and W, which restores the
-  // f32-exact product to about 2^-21 of each term (f32 output only).
-  const bool row_scaled = mode >= 1;
+  // mode 0: A as given (f32 is cast to f16), weights rounded to f16: one product.
+  //      1: f32 rows scaled into f16 range, one product.
+  //      2: as 1, three products A_hi.W_hi + A_lo.W_hi + A_hi.W_lo with the f16 rounding residues of A and W,
+  //         which restores the f32-exact product to about 2^-21 of each term (f32 output only).
+  //      3: f16 A, two products A.W_hi + A.W_lo: the product with weights kept to f32 accuracy (what the
+  //         reference's rule-selected kernel for f16 activations computes, fused_matmul_q4_batched_f16a.wgsl:107);
+  //         an f16 output is rounded once, from the f32 sum.
+  const bool row_scaled = mode == 1 || mode == 2;
   *handled = false;
   static int enabled = -1;
   if (enabled < 0) { const char *e = getenv("DP_GEMM_TC"); enabled = e ? atoi(e) : 1; }
@@ -1063,12 +904,14 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   if (!bn) return DP_OK;
   EncodeTiledFn encode = get_encode();
   if (!encode) return DP_OK;
+  if (mode == 3 && a_dtype != DP_F16) return DP_OK;
 
   const __half *a16 = (const __half *)A;
-  // The f16 copies of f32 activations live in one scratch allocation of the context, reused in stream order
-  // (a buffer handed back to the pool here could be given to somebody else before a recorded graph replays).
+  // The f16 copies of f32 activations (and the f32 sums of a two-product f16 output) live in one scratch
+  // allocation of the context, reused in stream order.
   const __half *a_lo = nullptr;
   const float *scales = nullptr;
+  float *c32 = nullptr;  // mode 3 with f16 output: the two products are summed here first
   if (a_dtype == DP_F32) {
     if (mode == 2 && c_dtype != DP_F32) return DP_OK;
     const size_t a_bytes = ((size_t)M * K * 2 + 255) / 256 * 256;
@@ -1087,6 +930,9 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
     }
   } else if (a_dtype != DP_F16) {
     return DP_OK;
+  } else if (mode == 3 && c_dtype == DP_F16) {
+    DP_TRY(dp_scratch(ctx, &ctx->gemm_scratch, (size_t)M * N * 4, "matmul_c_f32"));
+    c32 = (float *)ctx->gemm_scratch->dptr;
   }
   CUtensorMap tm;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -1096,20 +942,31 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   dp_status st = DP_OK;
-  TcAlpha ta = {alpha, scales, 0, 0, 1};
+  TcAlpha ta = {alpha, scales, 0, 0};
   CUtensorMap tm_lo;
   if (r == CUDA_SUCCESS && a_lo)
     r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a_lo, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
-  } else if (c_dtype == DP_F32) {
-    st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, ta);
+  } else if (c_dtype == DP_F32 || c32) {
+    float *cf = c32 ? c32 : (float *)C;
+    st = dispatch_tc<float>(ctx, bn, tm, W, cf, M, N, K, ta);
     if (st == DP_OK && a_lo) {
       ta.accumulate = 1;
-      st = dispatch_tc<float>(ctx, bn, tm_lo, W, (float *)C, M, N, K, ta);  // + A_lo . W_hi
+      st = dispatch_tc<float>(ctx, bn, tm_lo, W, cf, M, N, K, ta);  // + A_lo . W_hi
+    }
+    if (st == DP_OK && (a_lo || mode == 3)) {
+      ta.accumulate = 1;
       ta.weight_residue = 1;
-      if (st == DP_OK) st = dispatch_tc<float>(ctx, bn, tm, W, (float *)C, M, N, K, ta);  // + A_hi . W_lo
+      st = dispatch_tc<float>(ctx, bn, tm, W, cf, M, N, K, ta);  // + A_hi . W_lo
+    }
+    if (st == DP_OK && c32) {
+      const size_t n = (size_t)M * N;
+      size_t grid = (n / 4 + 255) / 256;
+      if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
+      if (grid < 1) grid = 1;
+      DP_LAUNCH(ctx, cast_f32_f16_out_kernel, (unsigned)grid, 256, 0, (const float *)c32, (__half *)C, n);
     }
   } else if (c_dtype == DP_F16) {
     st = dispatch_tc<__half>(ctx, bn, tm, W, (__half *)C, M, N, K, ta);
@@ -1120,9 +977,12 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   return st;
 }
 
+// f16 (or f32, cast to f16) activations.  f16_weights: one product with the dequantised weights rounded to f16,
+// the numerics of the reference's opt-in tiled kernel (fused_matmul_q4_prefill_tiled_f16.wgsl:201).  Otherwise,
+// for f16 activations, two products that keep the weights to f32 accuracy (the rule-selected kernel's numerics).
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
-                          int N, int K, float alpha, bool *handled) {
-  return gemm_q4k_tc_impl(ctx, W, A, a_dtype, C, c_dtype, M, N, K, alpha, 0, handled);
+                          int N, int K, float alpha, bool f16_weights, bool *handled) {
+  return gemm_q4k_tc_impl(ctx, W, A, a_dtype, C, c_dtype, M, N, K, alpha, (!f16_weights && a_dtype == DP_F16) ? 3 : 0, handled);
 }
 
 // f32 activations of any range on the tensor-core kernel: every row is scaled into f16 range by a power

@@ -248,19 +248,12 @@ struct GemvSource {
   const float *w;   // norm weights
   float eps;
   int D, splits;    // SRC_COMBINE: head_dim and number of splits
-  // the next GEMV's matrix (may be null): rows, bytes per row, CTAs of that launch, row tiles to pull into L2 per CTA
-  const uint8_t *next_w;
-  int next_rows, next_row_bytes, next_grid, next_tiles;
 };
 
 // GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
 // while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
-// BREG (rows that fit one ring stage, i.e. one chunk per tile): a consumer warp then meets the same
-// super-block columns in every tile, so it keeps their B fragments (activation digits), block scales
-// and sub-block sums in registers for the whole launch instead of re-reading them from shared memory
-// for every tile.
-template <typename OutT, int GROUPS, int SRC, bool BREG>
-__global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 ? 2 : 1) gemv_q4k_tma_kernel(
+template <typename OutT, int GROUPS, int SRC>
+__global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
     const float *__restrict__ residual, int *__restrict__ err, const GemvSource gs) {
@@ -402,16 +395,6 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
         }
       }
     }
-    if (ok && gs.next_w && (int)blockIdx.x < gs.next_grid && lane < 16) {
-      // all copies of this launch are issued; warm L2 with the row tiles this CTA index streams first next time
-      const int tiles_n = gs.next_rows / 16;
-      for (int j = 0; j < gs.next_tiles; j++) {
-        const int rt = (int)blockIdx.x + j * gs.next_grid;
-        if (rt >= tiles_n) break;
-        const uint8_t *row = gs.next_w + (size_t)(rt * 16 + lane) * (size_t)gs.next_row_bytes;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"((uint32_t)gs.next_row_bytes) : "memory");
-      }
-    }
     if (!ok && lane == 0) {  // gave up: let the copies already issued land before the CTA exits
       const uint32_t first = u > (uint32_t)stages ? u - (uint32_t)stages : 0u;
       for (uint32_t v = first; v < u; v++) {
@@ -430,27 +413,6 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
     uint32_t tile_no = (uint32_t)group;
     bool ok = true;
     float *red = reinterpret_cast<float *>(smem + L.red);
-    uint2 bfr[TG_MAX_BW][4];
-    float xsr[TG_MAX_BW], s0r[TG_MAX_BW], s1r[TG_MAX_BW];
-    if constexpr (BREG) {
-#pragma unroll
-      for (int i = 0; i < TG_MAX_BW; i++) {
-        const int b = warp + i * TG_CONSUMERS;  // chunks == 1: block column of the row
-        xsr[i] = s0r[i] = s1r[i] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < 4; c++) bfr[i][c] = make_uint2(0u, 0u);
-        if (b < cb) {
-          const uint2 *lb = reinterpret_cast<const uint2 *>(smem + (size_t)b * 1024) + g * 4 + t;
-          if (limb_lane) {
-#pragma unroll
-            for (int c = 0; c < 4; c++) bfr[i][c] = lb[c * 32];
-          }
-          xsr[i] = sm_xscale[b];
-          s0r[i] = sm_ssum[b * 8 + 2 * t];
-          s1r[i] = sm_ssum[b * 8 + 2 * t + 1];
-        }
-      }
-    }
     for (int rt = blockIdx.x + group * gridDim.x; rt < tiles && ok; rt += GROUPS * gridDim.x, tile_no += GROUPS) {
       float resA = 0.0f, resB = 0.0f;
       uint32_t u = tile_no * (uint32_t)chunks;
@@ -497,8 +459,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
 #pragma unroll
           for (int c = 0; c < 4; c++) {
             uint2 bf = make_uint2(0u, 0u);
-            if constexpr (BREG) bf = bfr[i][c];
-            else if (limb_lane) bf = lb[c * 32];
+            if (limb_lane) bf = lb[c * 32];
             int c0, c1, c2, c3;
             mma_u8s8(c0, c1, c2, c3, qa[i][c].x & M4, qb[i][c].x & M4, qa[i][c].y & M4, qb[i][c].y & M4, bf.x, bf.y);
             (void)c1; (void)c3;
@@ -511,11 +472,11 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, GROUPS == 1 
             accAh += (int)__byte_perm(wsa, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h1;
             accBh += (int)__byte_perm(wsb, 0u, 0x4440u + (uint32_t)((2 * c + 1) & 3)) * h3;
           }
-          const float xs = BREG ? xsr[i] : sm_xscale[b];
+          const float xs = sm_xscale[b];
           const float2 dA = q4k_d_dmin(ha[i].x), dB = q4k_d_dmin(hb[i].x);
           const float fa = (float)(accA + (accAh >> 4)) * wt;
           const float fb = (float)(accB + (accBh >> 4)) * wt;
-          const float s0 = BREG ? s0r[i] : sm_ssum[b * 8 + 2 * t], s1 = BREG ? s1r[i] : sm_ssum[b * 8 + 2 * t + 1];
+          const float s0 = sm_ssum[b * 8 + 2 * t], s1 = sm_ssum[b * 8 + 2 * t + 1];
           const uint32_t mwA = t < 2 ? sa.mn03 : sa.mn47, mwB = t < 2 ? sb_.mn03 : sb_.mn47;
           const int sh = (t & 1) * 16;
           const float mA = fmaf((float)((mwA >> (sh + 8)) & 0xffu), s1, (float)((mwA >> sh) & 0xffu) * s0);
@@ -558,16 +519,13 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   if (!dpk_gemv_q4k_fast_ok(N, K)) return false;
   const int bpr = K / QK_K;
   // chunk = the largest divisor of the row's block count whose stage (16 padded row pieces) stays
-  // under the limit: long per-row copies keep the number of bulk-copy requests per byte low
-  static int limit = -1;
-  if (limit < 0) { const char *e = getenv("DP_GEMV_STAGE_KB"); limit = (e ? atoi(e) : 56) * 1024; }
+  // under 56 KB: long per-row copies keep the number of bulk-copy requests per byte low
+  const int limit = 56 * 1024;
   int cb = 0;
   for (int c = bpr; c >= 1; c--)
     if (bpr % c == 0 && c <= TG_MAX_BW * TG_CONSUMERS && 16 * (c * Q4K_BLOCK_BYTES + TG_ROW_PAD) <= limit) { cb = c; break; }
   if (cb == 0) return false;
-  static int budget_kb = -1;
-  if (budget_kb < 0) { const char *e = getenv("DP_GEMV_SMEM_KB"); budget_kb = e ? atoi(e) : 227; }
-  size_t budget = (size_t)budget_kb * 1024;
+  size_t budget = (size_t)227 * 1024;
   if (budget > ctx->smem_optin) budget = ctx->smem_optin;
   int stages = 8;
   while (stages >= 2 && tg_layout(K, cb, stages).total > budget) stages--;
@@ -576,50 +534,28 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   return true;
 }
 
-template <typename OutT, int GROUPS, int SRC, bool BREG>
-static dp_status launch_tma_impl(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
+template <typename OutT, int GROUPS, int SRC>
+static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
                             uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
   const float *ssum = limbs ? xscale + K / QK_K : nullptr;
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
-  GemvSource src = gs;
-  src.next_w = nullptr;
-  if (ctx->gemv_next_w && ctx->gemv_next_rows >= 16 && ctx->gemv_next_k % QK_K == 0) {
-    src.next_w = (const uint8_t *)ctx->gemv_next_w;
-    src.next_rows = ctx->gemv_next_rows;
-    src.next_row_bytes = ctx->gemv_next_k / QK_K * Q4K_BLOCK_BYTES;
-    src.next_grid = ctx->gemv_next_rows / 16 < ctx->sm_count ? ctx->gemv_next_rows / 16 : ctx->sm_count;
-    const int tile_bytes = 16 * src.next_row_bytes;
-    src.next_tiles = (192 * 1024 + tile_bytes - 1) / tile_bytes;  // about one ring's worth per SM
-  }
-  ctx->gemv_next_w = nullptr;  // a hint serves one launch
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, BREG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, BREG>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
-            N, K, cb, stages, alpha, residual, ctx->dev_status, src);
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+            N, K, cb, stages, alpha, residual, ctx->dev_status, gs);
   return DP_OK;
 }
 
-template <typename OutT, int GROUPS, int SRC>
-static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
-                            uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
-  // Off by default: measured slower (9B-shaped step 2.007 ms against 1.931 ms; 227 MB matrix 55.0 us against
-  // 52.2 us) because the extra 22 registers per thread push the kernel into spills at its 120-register cap.
-  static const bool breg = [] { const char *e = getenv("DP_GEMV_BREG"); return e ? atoi(e) != 0 : false; }();
-  if (breg && cb == K / QK_K) return launch_tma_impl<OutT, GROUPS, SRC, true>(ctx, W, limbs, y, N, K, cb, stages, smem, alpha, residual, gs);
-  return launch_tma_impl<OutT, GROUPS, SRC, false>(ctx, W, limbs, y, N, K, cb, stages, smem, alpha, residual, gs);
-}
-
-// 0 = plain MMA kernel, 1 / 2 = TMA kernel with one / two consumer groups
+// DP_GEMV_VARIANT=0: the plain-load MMA kernel instead of the TMA-fed one (fallback switch)
 static int gemv_variant() {
   static int v = -1;
   if (v < 0) {
     const char *e = getenv("DP_GEMV_VARIANT");
-    v = e ? atoi(e) : 2;
-    if (v < 0 || v > 2) v = 2;
+    v = (e && atoi(e) == 0) ? 0 : 2;
   }
   return v;
 }
@@ -633,13 +569,8 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
   if (variant == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
   const int8_t *limbs = (const int8_t *)actq;
   GemvSource gs{};
-  if (y_dtype == DP_F32) {
-    if (variant == 1) DP_TRY((launch_tma<float, 1, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
-    else DP_TRY((launch_tma<float, 2, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
-  } else {
-    if (variant == 1) DP_TRY((launch_tma<__half, 1, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
-    else DP_TRY((launch_tma<__half, 2, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
-  }
+  if (y_dtype == DP_F32) DP_TRY((launch_tma<float, 2, SRC_DIGITS>(ctx, W, limbs, (float *)y, N, K, cb, stages, smem, alpha, residual, gs)));
+  else DP_TRY((launch_tma<__half, 2, SRC_DIGITS>(ctx, W, limbs, (__half *)y, N, K, cb, stages, smem, alpha, residual, gs)));
   *handled = true;
   return DP_OK;
 }
@@ -655,18 +586,10 @@ dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const 
   if (K > 16 * 2 * QK_K && mode == SRC_RMSNORM) return DP_OK;  // the norm keeps two blocks per warp in registers
   GemvSource gs{};
   gs.x = x; gs.w = w; gs.eps = eps; gs.D = D; gs.splits = splits;
-  if (gemv_variant() == 1) {
-    if (K > 8 * 2 * QK_K && mode == SRC_RMSNORM) return DP_OK;
-    if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 1, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 1, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 1, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else return DP_OK;
-  } else {
-    if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
-    else return DP_OK;
-  }
+  if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  else return DP_OK;
   *handled = true;
   return DP_OK;
 }

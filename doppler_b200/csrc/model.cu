@@ -27,7 +27,7 @@
 
 dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes, bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
-                          int M, int N, int K, float alpha, bool *handled);
+                          int M, int N, int K, float alpha, bool f16_weights, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
                             float alpha, const float *residual, bool *handled);
 dp_status dpk_q4k_prep_act(dp_ctx *ctx, const float *x, void *actq, int K);
@@ -71,12 +71,8 @@ struct dp_model {
   dp_buf attn_scratch = nullptr;
   dp_buf actq = nullptr;  // fixed-point activation digits of the decode GEMV (sized for the largest K)
   int attn_splits_decode = 1;
-  // GEMV launches can warm L2 with the next matrix (DP_GEMV_PREFETCH=1).  Off by default: measured on the
-  // 9B-shaped step it costs more than it saves (2.113 ms with, 2.082 ms without; the prefetch traffic
-  // lands on the current kernel's tail).
-  bool prefetch_next = false;
   bool recording_decode = false;  // set while a decode step is recorded into its CUDA graph
-  bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel (DP_ATTN_FUSE_QK=0: separate kernel)
+  bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
   int graph_batch[2] = {0, 0};
@@ -415,6 +411,8 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   DP_CHECK(ctx, c.head_dim % 64 == 0 && c.head_dim <= 256, "model: head_dim %d must be 64, 128, 192 or 256", c.head_dim);
   DP_CHECK(ctx, c.n_heads % c.n_kv_heads == 0, "model: n_heads %d not a multiple of n_kv_heads %d", c.n_heads, c.n_kv_heads);
   DP_CHECK(ctx, c.tp_rank >= 0 && c.tp_rank < p, "model: tp_rank %d outside [0,%d)", c.tp_rank, p);
+  DP_CHECK(ctx, p <= DP_TP_MAX_RANKS, "model: tp_size %d exceeds the %d ranks a group holds", p, DP_TP_MAX_RANKS);
+  DP_CHECK(ctx, c.max_batch <= 256, "model: max_batch %d > 256", c.max_batch);
   DP_CHECK(ctx, c.n_kv_heads % p == 0 && c.n_heads % p == 0, "model: heads (%d/%d) do not divide over %d ranks", c.n_heads, c.n_kv_heads, p);
   DP_CHECK(ctx, c.inter % (p * DP_QK_K) == 0 && (c.n_heads * c.head_dim) % (p * DP_QK_K) == 0,
            "model: row-parallel matrices must split on 256-element super-blocks over %d ranks", p);
@@ -423,10 +421,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   DP_CHECK(ctx, p == 1 || dp_tp_ready(ctx), "model: tp_size %d needs dp_tp_init on this context first", p);
   dp_model *m = new dp_model();
   m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
-  if (const char *e = getenv("DP_GEMV_PREFETCH")) m->prefetch_next = atoi(e) != 0;
-  if (const char *e = getenv("DP_ATTN_FUSE_QK")) m->fuse_qk = atoi(e) != 0;
   if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
-  DP_CHECK(ctx, m->cfg.max_batch <= 256, "model: max_batch %d > 256", m->cfg.max_batch);
   m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
   m->qdim = m->nh * c.head_dim; m->kvdim = m->nkv * c.head_dim;
   m->inter = c.inter / p; m->vocab_l = c.vocab / p; m->vocab0 = m->vocab_l * c.tp_rank;
@@ -661,8 +656,9 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   static int prefill_tc = -1;
   if (prefill_tc < 0) { const char *e = getenv("DP_PREFILL_TC"); prefill_tc = e ? atoi(e) : 3; }
   bool handled = false;
-  // (batched decode steps, recorded into a CUDA graph, keep the CUDA-core kernel)
-  if (prefill_tc && M >= 32 && !m->recording_decode) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
+  // (batched decode steps recorded into a CUDA graph take the same path: the f16 scratch belongs to the
+  // context and is never recycled while a graph is alive)
+  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
@@ -678,13 +674,6 @@ enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
 // (RMSNorm, SiLU*up or the split-K merge) while its weight ring fills, so a layer is six kernels:
 //   GEMV qkv [rmsnorm]  ->  qk-norm + rope + KV append  ->  attention split
 //   -> GEMV o [split merge] + residual  ->  GEMV gate|up [rmsnorm]  ->  GEMV down [silu*up] + residual
-// tell the next Q4_K GEMV launch which matrix follows it (see dp_ctx::gemv_next_w)
-static inline void hint_next(dp_model *m, const dp_buf w, int rows, int k) {
-  m->ctx->gemv_next_w = (m->prefetch_next && w) ? w->dptr : nullptr;
-  m->ctx->gemv_next_rows = rows;
-  m->ctx->gemv_next_k = k;
-}
-
 static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
   dp_ctx *ctx = m->ctx;
   const dp_model_cfg &c = m->cfg;
@@ -701,7 +690,6 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     const int nqkv = m->qdim + 2 * m->kvdim;
     // ---- q, k, v ----
     bool done = false;
-    if (single) hint_next(m, L.o, H, m->qdim);
     if (n_ready) {  // written by the exchange kernel of the previous layer
       n_ready = false;
       DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, true));
@@ -754,7 +742,6 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     float *o_dst = p == 1 ? m->h : m->partial;
     const float *o_res = p == 1 ? m->h : nullptr;
     done = false;
-    if (single) hint_next(m, L.gateup, 2 * m->inter, H);
     const bool split_merge_ok = single && splits > 1 && D % 8 == 0 && m->qdim % QK_K == 0;
     if (split_merge_ok) {
       DP_TRY(dpk_attention_split_only(ctx, ap, (float *)m->attn_scratch->dptr, splits));
@@ -789,7 +776,6 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     }
     // ---- gate | up ----
     done = false;
-    if (single) hint_next(m, L.down, H, m->inter);
     if (gu_digits) {
       DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, true));
       done = true;
@@ -810,7 +796,6 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     float *d_dst = p == 1 ? m->h : m->partial;
     const float *d_res = p == 1 ? m->h : nullptr;
     done = false;
-    if (single) hint_next(m, l + 1 < c.n_layers ? m->layers[l + 1].qkv : nullptr, nqkv, H);
     if (single && m->inter % QK_K == 0)
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
     if (!done) {
@@ -983,10 +968,7 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
                              (const uint8_t *)L.down->dptr};
       const float *X[4] = {m->n, m->att, m->n, m->actv};
       float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
-      const dp_buf next_qkv = l + 1 < c.n_layers ? m->layers[l + 1].qkv : (r + 1 < reps ? m->layers[0].qkv : nullptr);
-      const dp_buf NW[4] = {L.o, L.gateup, L.down, next_qkv};
       for (int i = 0; i < 4; i++) {
-        hint_next(m, NW[i], sh[(i + 1) & 3].N, sh[(i + 1) & 3].K);  // as the decode schedule does
         // digits_ready: in the decode step the producer kernel has already written them
         DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K)));
         n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;

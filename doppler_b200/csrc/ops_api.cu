@@ -10,7 +10,7 @@
 dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
                                     bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
-                          int M, int N, int K, float alpha, bool *handled);
+                          int M, int N, int K, float alpha, bool f16_weights, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
                             float alpha, const float *residual, bool *handled);
 
@@ -106,8 +106,12 @@ extern "C" dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A
         st = dpk_gemv_q4k(ctx, (const uint8_t *)bptr, (const float *)aptr, cptr, o.out_dtype, N, K, o.alpha, nullptr);
     } else {
       bool handled = false;
-      if (!o.exact_weights && M > 1 && A->dtype == DP_F16)  // f16 activations: tensor cores (matmul.rules.json:17)
-        st = dpk_gemm_q4k_tc(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha, &handled);
+      // f16 activations on the tensor cores.  Default: the rule-selected kernel's numerics (matmul.rules.json:17,
+      // fused_matmul_q4_batched_f16a.wgsl:107,151: f32 weights, f32 accumulate, one rounding of an f16 output).
+      // f16_weights: the opt-in tiled kernel's numerics (matmul-selection.js:550-620,
+      // fused_matmul_q4_prefill_tiled_f16.wgsl:201: weights rounded to f16 first), one tensor-core product.
+      if (!o.exact_weights && M > 1 && A->dtype == DP_F16)
+        st = dpk_gemm_q4k_tc(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha, o.f16_weights != 0, &handled);
       // f32 activations select the f32-exact product (matmul.rules.json:15-22): from 32 rows on the tensor
       // cores compute it in three passes (f16 halves and rounding residues of activations and weights)
       else if (!o.exact_weights && M >= 32 && A->dtype == DP_F32 && o.out_dtype == DP_F32)

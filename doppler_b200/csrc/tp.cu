@@ -81,6 +81,7 @@ extern "C" dp_status dp_tp_unique_id(void *out128) {
 extern "C" dp_status dp_tp_init(dp_ctx *ctx, int rank, int size, const void *id128) {
   if (!ctx || !id128) return DP_ERR_INVALID;
   DP_CHECK(ctx, size >= 1 && rank >= 0 && rank < size, "tp_init: rank %d outside [0,%d)", rank, size);
+  DP_CHECK(ctx, size <= DP_TP_MAX_RANKS, "tp_init: %d ranks requested, groups hold up to %d (one NVSwitch domain)", size, DP_TP_MAX_RANKS);
   if (ctx->tp) return dp_fail(ctx, DP_ERR_STATE, "tp_init: the context already has a group");
   std::string why;
   if (!load_nccl(&why)) return dp_fail(ctx, DP_ERR_COMM, "tp_init: %s", why.c_str());
@@ -142,6 +143,7 @@ extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *out64) {
   if (!ctx || !out64) return DP_ERR_INVALID;
   if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_export: call dp_tp_init first");
   dp_tp_state *tp = ctx->tp;
+  DP_CHECK(ctx, tp->size <= DP_TP_MAX_RANKS, "tp_ipc_export: the exchange area holds %d ranks", DP_TP_MAX_RANKS);
   DP_CUDA(ctx, cudaSetDevice(ctx->device));
   if (!tp->xbuf) {
     DP_CUDA(ctx, cudaMalloc(&tp->xbuf, dp_tp_area_bytes()));
@@ -160,6 +162,7 @@ extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *handles64_by_rank
   if (!dp_tp_ready(ctx) || !ctx->tp->xbuf) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_attach: export this rank's area first");
   dp_tp_state *tp = ctx->tp;
   if (tp->attached) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_attach: already attached");
+  DP_CHECK(ctx, tp->size <= DP_TP_MAX_RANKS, "tp_ipc_attach: the exchange area holds %d ranks", DP_TP_MAX_RANKS);
   DP_CUDA(ctx, cudaSetDevice(ctx->device));
   for (int r = 0; r < tp->size; r++) {
     if (r == tp->rank) { tp->peer[r] = tp->xbuf; continue; }

@@ -120,7 +120,7 @@ class DecoderModel:
 
     def set_allreduce_mode(self, mode: int):
         """0: NCCL allreduce + residual add; 1: one-shot peer-memory exchange fused with the residual
-        add and the next RMSNorm (single-token decode; needs tp.setup_exchange)."""
+        add and the next RMSNorm (single-token decode; needs tp.export_exchange + tp.attach_exchange)."""
         self.device.check(self.device.lib.dp_model_set_allreduce_mode(self.h, mode))
 
     def bench_gemv(self, reps: int = 1) -> dict:

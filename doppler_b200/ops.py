@@ -239,6 +239,12 @@ class Graph:
     def launch(self):
         self.device.check(self.device.lib.dp_graph_launch(self.h))
 
+    def launch_timed(self, reps: int = 1) -> float:
+        """Device time in ms of `reps` replays (CUDA events on the context's stream; synchronises)."""
+        ms = C.c_double()
+        self.device.check(self.device.lib.dp_graph_launch_timed(self.h, reps, C.byref(ms)))
+        return float(ms.value)
+
     def destroy(self):
         if self.h:
             self.device.lib.dp_graph_destroy(self.h)
@@ -254,7 +260,8 @@ def _rec(recorder: Optional[CommandRecorder]):
 # ------------------------------------------------------------------------------
 def record_matmul(recorder, A: Tensor, B: WeightBuffer, M: int, N: int, K: int, *, alpha: float = 1.0,
                   output_buffer: Optional[Buffer] = None, transpose_b=True, a_offset: int = 0, b_offset: int = 0,
-                  c_offset: int = 0, output_dtype: Optional[str] = None, exact_weights: bool = False, **_ignored) -> Tensor:
+                  c_offset: int = 0, output_dtype: Optional[str] = None, exact_weights: bool = False, f16_weights: bool = False,
+                  **_ignored) -> Tensor:
     """reference: recordMatmul, src/gpu/kernels/matmul.js:664 (options matmul.d.ts:20-87)"""
     dev = A.buffer.device
     if output_dtype is None:
@@ -269,6 +276,7 @@ def record_matmul(recorder, A: Tensor, B: WeightBuffer, M: int, N: int, K: int, 
     o.out_buf = output_buffer.h if output_buffer is not None else None
     o.transpose_b = 1 if transpose_b in (True, "auto") else 0
     o.exact_weights = 1 if exact_weights else 0
+    o.f16_weights = 1 if f16_weights else 0  # opt-in: the reference's tiled f16 prefill kernel's numerics
     a, b, out = A.c(), B.c(), L.TensorS()
     dev.check(dev.lib.dp_matmul(dev.h, _rec(recorder), C.byref(a), C.byref(b), M, N, K, C.byref(o), C.byref(out)))
     return _wrap(dev, out, output_buffer, "matmul_output")

@@ -7,11 +7,14 @@ vocabulary rows.  After o_proj and down_proj the partial [hidden] vectors are su
 
 `shard_plan` and the two slicing helpers restate on the host what the C++ loader does
 (dp_model_load_q4k), so the split can be checked without a GPU.
+
+Rendezvous is the caller's: the library only makes and consumes the bytes (a 128-byte NCCL
+unique id, one 64-byte CUDA IPC handle per rank); how they travel between the processes is up
+to the launcher (the tests and the benchmark use a torch.distributed gloo group).
 """
 from __future__ import annotations
 
 import ctypes as C
-import os
 
 import numpy as np
 
@@ -66,34 +69,35 @@ def merge_argmax(pairs):
     return best_i
 
 
-def init_group(dev, rank: int, world: int):
-    """Create the NCCL group of the context: rank 0 makes the unique id, torch.distributed (any
-    backend, e.g. gloo) carries it to the other ranks."""
-    import torch
-    import torch.distributed as dist
-
-    uid = torch.zeros(128, dtype=torch.uint8)
-    if rank == 0:
-        buf = (C.c_uint8 * 128)()
-        if dev.lib.dp_tp_unique_id(buf) != L.OK:
-            raise RuntimeError("cannot create the NCCL unique id (libnccl not loadable?)")
-        uid = torch.tensor(list(buf), dtype=torch.uint8)
-    dist.broadcast(uid, 0)
-    ub = (C.c_uint8 * 128)(*uid.tolist())
-    dev.check(dev.lib.dp_tp_init(dev.h, rank, world, ub))
+def make_unique_id(dev) -> bytes:
+    """128-byte NCCL unique id, made by ONE rank; the caller carries it to the others by whatever
+    channel it has (a launcher's store, MPI, a file) and every rank passes it to init_group."""
+    buf = (C.c_uint8 * 128)()
+    if dev.lib.dp_tp_unique_id(buf) != L.OK:
+        raise RuntimeError("cannot create the NCCL unique id (libnccl not loadable?)")
+    return bytes(buf)
 
 
-def setup_exchange(dev, rank: int, world: int):
-    """Map every rank's peer-memory exchange area into this process (CUDA IPC handles travel over
-    torch.distributed).  Needed for the one-shot allreduce (DecoderModel.set_allreduce_mode(1))."""
-    import torch
-    import torch.distributed as dist
+def init_group(dev, rank: int, world: int, unique_id: bytes):
+    """Create the NCCL group of the context from the id rank 0 made (make_unique_id)."""
+    if len(unique_id) != 128:
+        raise ValueError("the NCCL unique id is 128 bytes")
+    dev.check(dev.lib.dp_tp_init(dev.h, rank, world, (C.c_uint8 * 128).from_buffer_copy(unique_id)))
 
+
+def export_exchange(dev) -> bytes:
+    """64-byte CUDA IPC handle of this rank's peer-memory exchange area (allocated on first use)."""
     mine = (C.c_uint8 * 64)()
     dev.check(dev.lib.dp_tp_ipc_export(dev.h, mine))
-    t = torch.tensor(list(mine), dtype=torch.uint8)
-    allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
-    dist.all_gather(allh, t)
-    flat = (C.c_uint8 * (64 * world))(*[int(b) for h in allh for b in h.tolist()])
-    dev.check(dev.lib.dp_tp_ipc_attach(dev.h, flat))
-    dist.barrier()  # nobody pushes before every rank has mapped every area
+    return bytes(mine)
+
+
+def attach_exchange(dev, handles_by_rank):
+    """Map every rank's exchange area into this process.  `handles_by_rank[r]` is what rank r got
+    from export_exchange.  All ranks must have attached (a barrier of the caller's) before any of
+    them decodes: a rank pushes into its peers' areas.  Needed for the one-shot exchange
+    (DecoderModel.set_allreduce_mode(1))."""
+    flat = b"".join(bytes(h) for h in handles_by_rank)
+    if len(flat) % 64:
+        raise ValueError("IPC handles are 64 bytes each")
+    dev.check(dev.lib.dp_tp_ipc_attach(dev.h, (C.c_uint8 * len(flat)).from_buffer_copy(flat)))

@@ -114,9 +114,20 @@ dp_status dp_recorder_track_temporary(dp_recorder *rec, dp_buf buf);
 dp_status dp_recorder_submit(dp_recorder *rec);          /* launches; temporaries go back to the pool */
 dp_status dp_recorder_submit_and_wait(dp_recorder *rec); /* + stream synchronise */
 dp_status dp_recorder_abort(dp_recorder *rec);
-/* ends a capturing recorder without launching and hands out the graph */
+/* Ends a capturing recorder without launching and hands out the graph.
+ * Lifetimes: a graph's kernels hold device pointers.  The graph takes over the recording's tracked
+ * temporaries and returns them to the pool in dp_graph_destroy; the context's internal scratch
+ * areas that recorded ops used stay allocated while any graph of the context is alive (one that a
+ * later, larger call has to regrow is parked, not recycled).  Buffers the CALLER passed to recorded
+ * ops (inputs, weights, output buffers) are the caller's to keep alive until dp_graph_destroy;
+ * releasing one earlier lets the pool hand it to another owner that a replay then overwrites.
+ * Destroy a context's graphs before the context. */
 dp_status dp_recorder_finish_graph(dp_recorder *rec, dp_graph **out);
 dp_status dp_graph_launch(dp_graph *g);
+/* reference: recorder timestamp profiling  src/gpu/command-recorder.js:123-181,622 (resolveProfileTimings).
+ * `reps` replays bracketed by two CUDA events on the context's stream, then a synchronise;
+ * *ms = device time of all replays. */
+dp_status dp_graph_launch_timed(dp_graph *g, int reps, double *ms);
 void dp_graph_destroy(dp_graph *g);
 /* reference: recorder op-label statistics  src/gpu/command-recorder.js:123-181 */
 uint32_t dp_recorder_op_count(dp_recorder *rec);
@@ -129,10 +140,15 @@ uint32_t dp_recorder_op_count(dp_recorder *rec);
  * GEMM, fused_matmul_q4_batched*.wgsl / _prefill_tiled_f16.wgsl); DP_F16 is the
  * f16-weight GEMV/GEMM used for the LM head (matmul_gemv_subgroup.wgsl).
  * M>1 with Q4_K weights follows the reference's rule (matmul.rules.json:15-22):
- * f16 activations give the product with weights rounded to f16 (one
- * tensor-core pass); f32 activations give the f32-exact product, from 32 rows
- * on in three tensor-core passes over the f16 halves and rounding residues of
- * activations and weights (f32 output), otherwise on CUDA cores. */
+ * the dequantised weights enter the product with f32 accuracy and the sum is
+ * kept in f32 (f16 outputs are rounded once, at the store:
+ * fused_matmul_q4_batched_f16a.wgsl:107,151).  On the tensor cores that is the
+ * f16 halves AND the f16 rounding residues of the weights (and, for f32
+ * activations from 32 rows on, of the activations) multiplied into one f32
+ * accumulator; smaller or untiled f32 problems run on CUDA cores.
+ * opts.f16_weights = 1 selects the numerics of the reference's opt-in tiled
+ * prefill kernel instead (fused_matmul_q4_prefill_tiled_f16.wgsl:201: every
+ * dequantised weight rounded to f16 first), one tensor-core product. */
 typedef struct {
   float alpha;        /* default 1 */
   dp_dtype out_dtype; /* DP_F32 or DP_F16 (reference: outputDtype, required) */
@@ -140,6 +156,7 @@ typedef struct {
   dp_buf out_buf;     /* optional caller-owned output */
   int transpose_b;    /* must be 1 (weights are [N,K]); 0 is DP_ERR_UNSUPPORTED */
   int exact_weights;  /* M>1 only: 1 = always the CUDA-core kernel with f32-exact weights */
+  int f16_weights;    /* M>1, f16 activations: 1 = weights rounded to f16 before the product (opt-in, see above) */
 } dp_matmul_opts;
 void dp_matmul_opts_default(dp_matmul_opts *o);
 dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A, const dp_weight *B, int M,

@@ -37,6 +37,16 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; a timed baseline sets the
+ * team size itself. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------ */
 /* f16 <-> f32                                                               */
 /* ------------------------------------------------------------------------ */
@@ -331,8 +341,21 @@ void orc_q4k_gemv(const uint8_t *w, size_t rows, size_t cols, const float *x, fl
 /* tests/kernels/fused-matmul-q4-widetile-f16a-parity.test.js:59-74: each
  * C[m,n] is a double sum over k in order.  Sums for different m are
  * independent, so they are carried side by side (same result, vectorisable). */
+static void q4k_gemm_impl(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c, int f16_weights);
+
 void orc_q4k_gemm(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c) {
   if (m == 1) { orc_q4k_gemv(w, n, k, a, alpha, c); return; } /* same sum, same order */
+  q4k_gemm_impl(w, n, k, a, m, alpha, c, 0);
+}
+
+/* The reference's opt-in tiled prefill kernel, src/gpu/kernels/fused_matmul_q4_prefill_tiled_f16.wgsl:
+ * every dequantised weight is rounded to f16 when it is staged (:196-201, tileB[slot] = f16(w)) and widened
+ * again for the multiply (:226-229); sums as above. */
+void orc_q4k_gemm_f16_weights(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c) {
+  q4k_gemm_impl(w, n, k, a, m, alpha, c, 1);
+}
+
+static void q4k_gemm_impl(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c, int f16_weights) {
   size_t bpr = (k + ORC_QK_K - 1) / ORC_QK_K;
   size_t mp = (m + ORC_MB - 1) / ORC_MB * ORC_MB;
   /* A transposed to [k][mp] so that the m-lanes are contiguous */
@@ -346,6 +369,8 @@ void orc_q4k_gemm(const uint8_t *w, size_t n, size_t k, const float *a, size_t m
     for (long r = 0; r < (long)n; r++) {
       for (size_t b = 0; b < bpr; b++)
         orc_q4k_dequant_block(w + ((size_t)r * bpr + b) * ORC_Q4K_BLOCK_BYTES, row + b * ORC_QK_K);
+      if (f16_weights)
+        for (size_t kk = 0; kk < bpr * ORC_QK_K; kk++) row[kk] = orc_f16_to_f32(orc_f32_to_f16_rne(row[kk]));
       for (size_t m0 = 0; m0 < mp; m0 += ORC_MB) {
         double acc[ORC_MB];
         for (int j = 0; j < ORC_MB; j++) acc[j] = 0;
@@ -565,6 +590,65 @@ int orc_argmax(const float *logits, int n, int pad_id) {
   return best_i;
 }
 
+
+/* ------------------------------------------------------------------------ */
+/* seeded synthetic inputs                                                   */
+/* ------------------------------------------------------------------------ */
+/*
+ * Restatement of the library's host-side input generators (dp_synth_* in
+ * doppler_b200/csrc/synth.cu), so that the CPU baseline can build the benchmark's
+ * model without loading the CUDA library.  Counter based: element i of stream
+ * `key` is a function of (key, i) only.  tests/test_oracle_synth.py checks that
+ * both produce the same bytes.
+ */
+static inline uint64_t synth_mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ULL;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  return z ^ (z >> 31);
+}
+static inline uint64_t synth_word(uint64_t key, uint64_t i) { return synth_mix64(key + i * 0x9E3779B97F4A7C15ULL); }
+static inline float synth_normal(uint64_t h) { /* Box-Muller on two 24-bit uniforms, f32 arithmetic */
+  const float u1 = (float)((h >> 40) + 1u) * (1.0f / 16777216.0f);
+  const float u2 = (float)((h >> 16) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+  return sqrtf(-2.0f * logf(u1)) * cosf(6.2831853071795864f * u2);
+}
+
+uint64_t orc_synth_key(uint64_t seed, uint64_t tensor_id) { return synth_mix64(seed * 0x100000001B3ULL + tensor_id); }
+
+void orc_synth_normal_f32(uint64_t key, uint64_t first, size_t n, float sigma, float mean, float *out) {
+#pragma omp parallel for schedule(static)
+  for (size_t i = 0; i < n; i++) out[i] = mean + sigma * synth_normal(synth_word(key, first + i));
+}
+
+void orc_synth_normal_f16(uint64_t key, uint64_t first, size_t n, float sigma, uint16_t *out) {
+#pragma omp parallel for schedule(static)
+  for (size_t i = 0; i < n; i++) out[i] = orc_f32_to_f16_rne(sigma * synth_normal(synth_word(key, first + i)));
+}
+
+/* d, dmin = f16(|N(0, 0.02)|); scale bytes and quants = 140 uniformly random bytes */
+void orc_synth_q4k_blocks(uint64_t key, uint64_t first_block, size_t n_blocks, uint8_t *out) {
+#pragma omp parallel for schedule(static)
+  for (size_t b = 0; b < n_blocks; b++) {
+    const uint64_t base = (first_block + b) * 20u;
+    uint8_t *blk = out + b * 144u;
+    const uint16_t d = orc_f32_to_f16_rne(fabsf(0.02f * synth_normal(synth_word(key, base))));
+    const uint16_t dm = orc_f32_to_f16_rne(fabsf(0.02f * synth_normal(synth_word(key, base + 1))));
+    memcpy(blk, &d, 2);
+    memcpy(blk + 2, &dm, 2);
+    uint8_t bytes[144];
+    for (int j = 0; j < 18; j++) {
+      const uint64_t w = synth_word(key, base + 2 + (uint64_t)j);
+      memcpy(bytes + j * 8, &w, 8);
+    }
+    memcpy(blk + 4, bytes, 140);
+  }
+}
+
+void orc_synth_tokens(uint64_t key, size_t n, int vocab, int32_t *out) {
+  for (size_t i = 0; i < n; i++) out[i] = (int32_t)(synth_word(key, i) % (uint64_t)vocab);
+}
+
 /* ------------------------------------------------------------------------ */
 /* whole-model oracle                                                        */
 /* ------------------------------------------------------------------------ */
@@ -678,4 +762,18 @@ int orc_model_forward(orc_model *m, const int32_t *tokens, int n, float *margin,
   if (logits_out) memcpy(logits_out, logits, (size_t)c->vocab * 4);
   free(logits); free(h); free(nrm); free(q); free(k); free(v); free(att); free(proj); free(g); free(u); free(act);
   return tok;
+}
+
+/* Benchmark helper: put `n` positions of synthetic f16 K/V (values ~N(0,1)) into every layer's
+ * cache and move the sequence there, so that a timed decode step attends over a context of n
+ * tokens without an n-token prefill on the CPU. */
+int orc_model_fill_kv(orc_model *m, int n, uint64_t key) {
+  if (n < 0 || n > m->cfg.max_seq) return -1;
+  size_t per = (size_t)n * m->cfg.n_kv_heads * m->cfg.head_dim;
+  for (int l = 0; l < m->cfg.n_layers; l++) {
+    orc_synth_normal_f16(key + 2u * (uint64_t)l, 0, per, 1.0f, m->kc[l]);
+    orc_synth_normal_f16(key + 2u * (uint64_t)l + 1u, 0, per, 1.0f, m->vc[l]);
+  }
+  m->cur = n;
+  return 0;
 }

@@ -69,6 +69,9 @@ void orc_q4k_gemv(const uint8_t *w, size_t rows, size_t cols, const float *x, fl
 /* same math for M rows of A (f32, row-major [M,K]); C is f32 [M,N].
  * tests/kernels/fused-matmul-q4-widetile-f16a-parity.test.js:59-74 */
 void orc_q4k_gemm(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c);
+/* same with every dequantised weight rounded to f16 first: the reference's opt-in tiled prefill kernel,
+ * src/gpu/kernels/fused_matmul_q4_prefill_tiled_f16.wgsl:196-201,226-229 */
+void orc_q4k_gemm_f16_weights(const uint8_t *w, size_t n, size_t k, const float *a, size_t m, float alpha, float *c);
 /* f16-weight GEMV, tools/lib/q4k-projection-reference.js:183-209 */
 void orc_f16_gemv(const uint16_t *w, size_t rows, size_t cols, const float *x, float *y);
 
@@ -132,6 +135,16 @@ int orc_model_seq_len(const orc_model *m);
 const float *orc_model_last_hidden(const orc_model *m);
 
 int orc_num_threads(void);
+void orc_set_num_threads(int n);
+
+/* ---- seeded synthetic inputs (restatement of the library's dp_synth_* host generators) ---- */
+uint64_t orc_synth_key(uint64_t seed, uint64_t tensor_id);
+void orc_synth_normal_f32(uint64_t key, uint64_t first, size_t n, float sigma, float mean, float *out);
+void orc_synth_normal_f16(uint64_t key, uint64_t first, size_t n, float sigma, uint16_t *out);
+void orc_synth_q4k_blocks(uint64_t key, uint64_t first_block, size_t n_blocks, uint8_t *out);
+void orc_synth_tokens(uint64_t key, size_t n, int vocab, int32_t *out);
+/* benchmark helper: n positions of synthetic f16 K/V in every layer, sequence position = n */
+int orc_model_fill_kv(orc_model *m, int n, uint64_t key);
 
 #ifdef __cplusplus
 }

@@ -71,6 +71,7 @@ def _declare(L):
         "orc_q4k_decode_header": (None, [vp, vp, vp, vp, vp]),
         "orc_q4k_gemv": (None, [vp, sz, sz, vp, flt, vp]),
         "orc_q4k_gemm": (None, [vp, sz, sz, vp, sz, flt, vp]),
+        "orc_q4k_gemm_f16_weights": (None, [vp, sz, sz, vp, sz, flt, vp]),
         "orc_f16_gemv": (None, [vp, sz, sz, vp, vp]),
         "orc_attention": (None, [vp, vp, vp, i32, i32, i32, i32, i32, vp, dbl, vp]),
         "orc_attention_f16kv": (None, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, dbl, vp]),
@@ -89,6 +90,13 @@ def _declare(L):
         "orc_model_seq_len": (i32, [vp]),
         "orc_model_last_hidden": (vp, [vp]),
         "orc_num_threads": (i32, []),
+        "orc_set_num_threads": (None, [i32]),
+        "orc_synth_key": (u64, [u64, u64]),
+        "orc_synth_normal_f32": (None, [u64, u64, sz, flt, flt, vp]),
+        "orc_synth_normal_f16": (None, [u64, u64, sz, flt, vp]),
+        "orc_synth_q4k_blocks": (None, [u64, u64, sz, vp]),
+        "orc_synth_tokens": (None, [u64, sz, i32, vp]),
+        "orc_model_fill_kv": (i32, [vp, i32, u64]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -200,6 +208,14 @@ def q4k_gemm(w, n: int, k: int, a, m: int, alpha: float = 1.0) -> np.ndarray:
     return c
 
 
+def q4k_gemm_f16_weights(w, n: int, k: int, a, m: int, alpha: float = 1.0) -> np.ndarray:
+    """The opt-in tiled prefill kernel's product: dequantised weights rounded to f16 first."""
+    wb, av = np.ascontiguousarray(w, np.uint8), _f32(a)
+    c = np.empty((m, n), np.float32)
+    lib().orc_q4k_gemm_f16_weights(_p(wb), n, k, _p(av), m, alpha, _p(c))
+    return c
+
+
 def f16_gemv(w_f16, rows: int, cols: int, x) -> np.ndarray:
     wv, xv = np.ascontiguousarray(w_f16).view(np.uint16), _f32(x)
     y = np.empty(rows, np.float32)
@@ -275,6 +291,31 @@ def argmax(logits, pad_id=-1):
     return lib().orc_argmax(_p(lv), lv.size, pad_id)
 
 
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(int(n))
+
+
+class SynthBackend:
+    """The oracle's restatement of the library's seeded input generators, shaped like the handle
+    doppler_b200.synthetic.Generator wraps (same five primitives), so the CPU baseline can build
+    the benchmark model without loading the CUDA library."""
+
+    def dp_synth_key(self, seed, tensor_id):
+        return lib().orc_synth_key(seed, tensor_id)
+
+    def dp_synth_normal_f32(self, key, first, n, sigma, mean, out):
+        lib().orc_synth_normal_f32(key, first, n, sigma, mean, out)
+
+    def dp_synth_normal_f16(self, key, first, n, sigma, out):
+        lib().orc_synth_normal_f16(key, first, n, sigma, out)
+
+    def dp_synth_q4k_blocks(self, key, first_block, n_blocks, out):
+        lib().orc_synth_q4k_blocks(key, first_block, n_blocks, out)
+
+    def dp_synth_tokens(self, key, n, vocab, out):
+        lib().orc_synth_tokens(key, n, vocab, out)
+
+
 def num_threads() -> int:
     return lib().orc_num_threads()
 
@@ -311,6 +352,11 @@ class OracleModel:
 
     def reset(self):
         lib().orc_model_reset(self._h)
+
+    def fill_kv(self, n: int, key: int = 1):
+        """Benchmark helper: synthetic f16 K/V for positions [0, n), sequence position = n."""
+        if lib().orc_model_fill_kv(self._h, n, key) != 0:
+            raise RuntimeError("oracle model: context exceeds max_seq")
 
     def __del__(self):
         try:

@@ -1,4 +1,4 @@
-"""The measurement switches (environment variables read once per process) select alternative kernels.
+"""The fallback switches (environment variables read once per process, one per op) select the alternative kernels.
 Each alternative must stay correct, so a small parity check runs in a child process per setting."""
 import os
 import subprocess
@@ -28,7 +28,7 @@ M, N, K = 512, 768, 512
 W = synthetic.q4k_matrix(synthetic.key(83, 1), N, K)
 A = synthetic.normal_f16(synthetic.key(83, 2), M * K)
 c = dev.read_tensor(ops.run_matmul(dev.tensor_from(A.reshape(M, K)), dev.weight_from(W, "q4k", [N, K]), M, N, K, output_dtype="f32"))
-assert_close(c, O.q4k_gemm(W, N, K, A.astype(np.float32), M), "gemm", rtol=2e-3)
+assert_close(c, O.q4k_gemm(W, N, K, A.astype(np.float32), M), "gemm")
 cfg = dict(synthetic.MODEL_CONFIGS["small"])
 w = gaussian_model_weights(cfg, 1234)
 prompt = synthetic.make_prompt(cfg, 40, seed=1234)
@@ -47,10 +47,7 @@ print("ok")
 
 
 @pytest.mark.parametrize("env", [
-    {"DP_GEMV_BREG": "1"}, {"DP_GEMV_VARIANT": "0"}, {"DP_GEMV_VARIANT": "1"}, {"DP_GEMV_PREFETCH": "1"},
-    {"DP_ATTN_TC": "0"}, {"DP_ATTN_FUSE_QK": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_PAIR": "1"}, {"DP_GEMM_RINGS": "1"},
-    {"DP_GEMM_TC": "0"}, {"DP_GEMM_WIDE_M": "1"}, {"DP_GEMM_2SM": "1"}, {"DP_GEMM_2SM": "4"}, {"DP_GEMM_2SM": "0"},
-    {"DP_GEMM_2SM": "6"}, {"DP_GEMM_2SM": "7"}, {"DP_PREFILL_TC": "0"}, {"DP_GEMM_SPLIT_K": "0"}, {"DP_GEMM_RINGS": "2"},
+    {"DP_GEMV_VARIANT": "0"}, {"DP_ATTN_TC": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_TC": "0"}, {"DP_PREFILL_TC": "0"},
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_alternative_kernels_stay_correct(tmp_path, env):
     script = tmp_path / "child.py"

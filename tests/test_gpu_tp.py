@@ -14,7 +14,8 @@ WORKER = r'''
 import os, sys
 sys.path.insert(0, os.environ["DP_ROOT"]); sys.path.insert(0, os.path.join(os.environ["DP_ROOT"], "tests"))
 import numpy as np, torch.distributed as dist
-from doppler_b200 import synthetic, tp
+from doppler_b200 import synthetic
+import tp_rendezvous as tp
 from doppler_b200.model import DecoderModel
 from doppler_b200.ops import Device
 from model_util import gaussian_model_weights
