@@ -109,6 +109,8 @@ SIGNATURES = {
     "dp_recorder_abort": (_i, [_vp]),
     "dp_recorder_finish_graph": (_i, [_vp, C.POINTER(_vp)]),
     "dp_graph_launch": (_i, [_vp]),
+    "dp_ctx_set_wait_limit": (_i, [_vp, C.c_uint]),
+    "dp_tp_init_loopback": (_i, [_vp, _i, _i]),
     "dp_graph_launch_timed": (_i, [_vp, _i, C.POINTER(_dbl)]),
     "dp_graph_destroy": (None, [_vp]),
     "dp_recorder_op_count": (_u32, [_vp]),

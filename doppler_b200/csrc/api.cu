@@ -54,6 +54,7 @@ extern "C" void dp_ctx_destroy(dp_ctx *ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   dp_tp_destroy(ctx);
+  if (ctx->local_xd_area) cudaFree(ctx->local_xd_area);
   for (dp_buf_s *b : ctx->all) {
     if (b->dptr) cudaFree(b->dptr);
     delete b;
@@ -63,21 +64,38 @@ extern "C" void dp_ctx_destroy(dp_ctx *ctx) {
   delete ctx;
 }
 
+extern "C" dp_status dp_ctx_set_wait_limit(dp_ctx *ctx, unsigned polls) {
+  if (!ctx) return DP_ERR_INVALID;
+  DP_CHECK(ctx, polls >= 16, "set_wait_limit: %u polls is too few", polls);
+  ctx->wait_limit = polls;
+  return DP_OK;
+}
+
 extern "C" const char *dp_last_error(dp_ctx *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 extern "C" void *dp_ctx_stream(dp_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 extern "C" int dp_ctx_device(dp_ctx *ctx) { return ctx ? ctx->device : -1; }
 extern "C" uint64_t dp_ctx_launch_count(dp_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
-extern "C" dp_status dp_ctx_sync(dp_ctx *ctx) {
-  if (!ctx) return DP_ERR_INVALID;
-  DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+void dp_tp_reset_barrier(dp_ctx *ctx);
+
+// Reads (and clears) the status word kernels raise when a bounded device-side wait gave up.  The stream
+// must be idle.
+dp_status dp_take_dev_status(dp_ctx *ctx) {
   int flag = 0;
   DP_CUDA(ctx, cudaMemcpy(&flag, ctx->dev_status, 4, cudaMemcpyDeviceToHost));
   if (flag) {
     cudaMemset(ctx->dev_status, 0, 4);
+    dp_tp_reset_barrier(ctx);
+    cudaStreamSynchronize(ctx->stream);
     return dp_fail(ctx, DP_ERR_TIMEOUT, "a kernel gave up on a bounded device-side wait (status %d); its output is invalid", flag);
   }
   return DP_OK;
+}
+
+extern "C" dp_status dp_ctx_sync(dp_ctx *ctx) {
+  if (!ctx) return DP_ERR_INVALID;
+  DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return dp_take_dev_status(ctx);
 }
 
 // ---- pool ------------------------------------------------------------------

@@ -73,7 +73,7 @@ extern "C" dp_status dp_attention_decode_static(void *stream, const float *q, co
   ctx.device = device;
   ctx.stream = (cudaStream_t)stream;
   ctx.sm_count = sms;
-  dpk_attn_params p;
+  dpk_attn_params p{};
   p.q = q;
   p.k = (const __half *)k_f16;
   p.v = (const __half *)v_f16;

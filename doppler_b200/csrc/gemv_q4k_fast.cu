@@ -240,7 +240,7 @@ __host__ __device__ inline TgLayout tg_layout(int K, int cb, int stages) {
 // needs no kernel of its own (148 CTAs redo a few KB of work each; the latency hides under the
 // pipeline fill):
 //   SRC_RMSNORM  x = rmsnorm(h, w, eps)                 (rmsnorm.wgsl:119-187)
-//   SRC_SILU     x = silu(gate) * up, gate|up = gu[2K]   (silu.wgsl:98-104)
+//   SRC_SILU     x = silu(gate) * up, gu[2K] = eight gate values, their eight up values, ...   (silu.wgsl:98-104)
 //   SRC_COMBINE  x = merge of the split-K attention partials (layout of attention.cu)
 enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
 struct GemvSource {
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
       }
     } else if constexpr (SRC == SRC_SILU) {
       for (int b = cw; b < bpr; b += NW) {
-        const float *gp = gs.x + b * QK_K + lane * 8, *up = gs.x + K + b * QK_K + lane * 8;
+        const float *gp = gs.x + 2 * (b * QK_K + lane * 8), *up = gp + 8;  // gate|up interleaved in groups of eight
         const float4 g0 = *reinterpret_cast<const float4 *>(gp), g1 = *reinterpret_cast<const float4 *>(gp + 4);
         const float4 u0 = *reinterpret_cast<const float4 *>(up), u1 = *reinterpret_cast<const float4 *>(up + 4);
         const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};

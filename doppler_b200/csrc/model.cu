@@ -18,6 +18,7 @@
 #include "q4k.cuh"
 #include "actq.cuh"
 #include "tp_exchange.h"
+#include "decode_layer.h"
 
 #include <cfloat>
 #include <cmath>
@@ -44,6 +45,10 @@ dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
 dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 bool dp_tp_ready(dp_ctx *ctx);
 dp_tp_exchange *dp_tp_exchange_desc(dp_ctx *ctx);
+bool dp_tp_exchange_view(dp_ctx *ctx, int *rank, int *size, uint2 **areas);
+dp_status dp_tp_local_area(dp_ctx *ctx, uint2 **area);
+dp_status dp_take_dev_status(dp_ctx *ctx);
+dp_status dpk_decode_layer(dp_ctx *ctx, const DlParams &P);
 
 struct LayerW {
   dp_buf qkv = nullptr, o = nullptr, gateup = nullptr, down = nullptr;
@@ -63,6 +68,13 @@ struct dp_model {
   float *rope_cos = nullptr, *rope_sin = nullptr;
   dp_buf act = nullptr;  // one slab for all activations
   float *h, *n, *qkv, *q, *att, *gu, *actv, *partial, *logits;
+  float *hbuf[3];       // the residual stream of single-token decode rotates over three buffers (hbuf[0] == h): a launch of the
+                        // persistent kernel reads one and writes the next, so no CTA overwrites what another still has to read
+  float *h_last;        // where the last forward pass left the hidden state
+  int *attn_counters = nullptr;   // zeroed arrival counters of the decode attention's in-kernel split merge
+  uint2 *act_ll = nullptr;        // (value, ticket) words of the silu(gate) * up hand-off inside the persistent kernel
+  unsigned *d_ticket = nullptr;   // device counter of decode steps ever run on this CONTEXT (its exchange area outlives a model):
+                                  // hand-off tickets derive from it and never repeat
   dp_buf state = nullptr;  // device ints: pos[B], kvlen[B], tok[B], step, then argmax scratch
   int *d_pos, *d_kvlen, *d_tok, *d_step;
   float *am_vals; int *am_idx; float *am_best; int *am_pair_i; float *am_gather;
@@ -73,6 +85,12 @@ struct dp_model {
   int attn_splits_decode = 1;
   bool recording_decode = false;  // set while a decode step is recorded into its CUDA graph
   bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel
+  // Single-token decode on the per-layer persistent kernel: -1 = when the model is tensor parallel with the
+  // one-shot exchange (there it replaces the collectives), 1 = always, 0 = never (DP_DECODE_PERSISTENT).  On
+  // one GPU the schedule with one launch per projection is faster (measured: 1.93 ms against 2.35 ms per
+  // step of the 9B shape), because the consumer warps' arithmetic, not HBM, sets the pace of the persistent
+  // kernel and its hand-off prologues cannot overlap anything.
+  int persistent = -1;
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
   int graph_batch[2] = {0, 0};
@@ -139,28 +157,39 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_kernel(
   }
 }
 
-// out[t, :] = silu(gu[t, 0:I]) * gu[t, I:2I]   (silu.wgsl:30-37,98-104, sigmoid argument clamped to +-15)
+// The gate and up projections share one matrix whose rows are interleaved in groups of eight (eight gate rows,
+// then their eight up rows), so a 16-row tile of the decode GEMV holds matching pairs: gate c is output
+// (c / 8) * 16 + c % 8, up c is eight further.
+__device__ __forceinline__ size_t gu_gate_index(size_t c) { return (c >> 3) * 16 + (c & 7); }
+
+// out[t, c] = silu(gate[t, c]) * up[t, c]   (silu.wgsl:30-37,98-104, sigmoid argument clamped to +-15)
 __global__ void silu_gateup_kernel(const float *__restrict__ gu, float *__restrict__ out, int tokens, int inter) {
   pdl_launch();
   pdl_wait();
   const size_t total = (size_t)tokens * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / inter, c = i % inter;
-    const float g = gu[t * 2 * inter + c], u = gu[t * 2 * inter + inter + c];
+    const float g = gu[t * 2 * inter + gu_gate_index(c)], u = gu[t * 2 * inter + gu_gate_index(c) + 8];
     const float cl = fminf(fmaxf(g, -15.0f), 15.0f);
     out[i] = (g * (1.0f / (1.0f + expf(-cl)))) * u;
   }
 }
 
 // after a decode step: record the sampled tokens and move every sequence on by one
-__global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, int *out_tokens, int batch) {
+__global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, int *out_tokens, int batch, unsigned *ticket) {
   pdl_launch();
   pdl_wait();
   const int b = threadIdx.x;
   const int s = *step;
   if (b < batch) { out_tokens[s * batch + b] = tok[b]; pos[b] += 1; kvlen[b] += 1; }
   __syncthreads();
-  if (b == 0) *step = s + 1;
+  if (b == 0) { *step = s + 1; *ticket += 1u; }
+}
+
+__global__ void bump_ticket_kernel(unsigned *ticket) {
+  pdl_launch();
+  pdl_wait();
+  if (threadIdx.x == 0) *ticket += 1u;
 }
 
 // combine the per-rank (best value, index) pairs of a vocabulary-sharded argmax;
@@ -245,7 +274,7 @@ __global__ void __launch_bounds__(256) silu_actq_kernel(const float *__restrict_
   const int lane = threadIdx.x & 31, bpr = inter / QK_K;
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (b >= bpr) return;
-  const float *gp = gu + b * QK_K + lane * 8, *up = gu + inter + b * QK_K + lane * 8;
+  const float *gp = gu + 2 * (b * QK_K + lane * 8), *up = gp + 8;  // interleaved in groups of eight
   const float4 g0 = *reinterpret_cast<const float4 *>(gp), g1 = *reinterpret_cast<const float4 *>(gp + 4);
   const float4 u0 = *reinterpret_cast<const float4 *>(up), u1 = *reinterpret_cast<const float4 *>(up + 4);
   const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
@@ -293,108 +322,50 @@ __global__ void __launch_bounds__(256) attn_combine_actq_kernel(const float *__r
   actq_emit_block(o, lane, b, bpr, actq);
 }
 
-// ---- one-shot allreduce over peer memory, fused with the residual add and the next RMSNorm ----
-// (no counterpart in the reference, which has no collective backend).  One CTA per rank:
-//   1. push this rank's partial vector into its slot of EVERY rank's exchange area (plain stores
-//      over NVLink), fence, then raise this rank's epoch flag in every area;
-//   2. poll the flags of all ranks in this rank's OWN memory (bounded; on give-up a status word is
-//      raised and the kernel carries on so nothing hangs);
-//   3. h += sum of the slots in rank order (the same order on every rank, so all ranks hold the
-//      same bits), then RMSNorm with `norm_w` -> n_out and the GEMV activation digits.
-// Two parity sets of slots: a rank can be at most one exchange ahead of the slowest rank, because
-// finishing exchange e needs every rank's flag for e.
-__global__ void __launch_bounds__(256) tp_allreduce_rmsnorm_kernel(dp_tp_exchange *__restrict__ xd, const float *__restrict__ partial,
-                                                                   float *__restrict__ h, const float *__restrict__ norm_w,
-                                                                   float *__restrict__ n_out, void *__restrict__ actq, int size,
-                                                                   float eps, int *__restrict__ err) {
+// ---- vocabulary-sharded greedy pick over the peer-memory exchange area ----
+// (no counterpart in the reference, which has no collective backend).  One CTA per rank pushes this
+// rank's (best logit, global index) of every sequence, each as an 8-byte (value, ticket) word, into its
+// slot of EVERY rank's area (plain stores over NVLink), then re-reads all ranks' slots in its OWN memory
+// until they carry this exchange's ticket (bounded; on give-up a status word is raised and the kernel
+// carries on so nothing hangs), and merges in rank order: the largest value wins, ties go to the lower
+// global index (sample.wgsl:45-53), so every rank picks the same token.
+struct ArgmaxExchange {
+  int rank, nr;
+  uint2 *area[DP_TP_MAX_RANKS];
+};
+__global__ void __launch_bounds__(256) tp_argmax_exchange_kernel(const ArgmaxExchange xg, dp_tp_exchange *__restrict__ xd, const float *__restrict__ best,
+                                                                 int *__restrict__ tok, int batch, unsigned wait_limit, int *__restrict__ err) {
   pdl_launch();
   pdl_wait();
-  __shared__ float sh[32];
-  __shared__ unsigned s_epoch;
-  __shared__ int s_bad;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, bpr = size / QK_K;
-  const int rank = xd->rank, nr = xd->size;
-  if (tid == 0) { s_epoch = ++xd->epoch; s_bad = 0; }
+  __shared__ unsigned s_ticket;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_ticket = ++xd->am_ticket;
   __syncthreads();
-  const unsigned e = s_epoch;
-  const size_t par_off = (size_t)(e & 1u) * DP_TP_MAX_RANKS * DP_TP_SLOT_FLOATS;
-  // 1. push
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int b = warp + 8 * i;
-    if (b < bpr) {
-      const int off = b * QK_K + lane * 8;
-      const float4 a = *reinterpret_cast<const float4 *>(partial + off), c = *reinterpret_cast<const float4 *>(partial + off + 4);
-      for (int r = 0; r < nr; r++) {
-        float *dst = xd->area[r] + par_off + (size_t)rank * DP_TP_SLOT_FLOATS + off;
-        *reinterpret_cast<float4 *>(dst) = a;
-        *reinterpret_cast<float4 *>(dst + 4) = c;
+  const unsigned e = s_ticket;
+  if (tid < batch) {
+    const unsigned v = __float_as_uint(best[tid]), idx = (unsigned)tok[tid];
+    for (int r = 0; r < xg.nr; r++) {
+      uint2 *dst = xg.area[r] + dp_tp_am_slot_offset(e, xg.rank) + 2 * tid;
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v), "r"(e) : "memory");
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + 1), "r"(idx), "r"(e) : "memory");
+    }
+    float bv = -3.402823e+38f;
+    int bi = 0x7fffffff;
+    bool ok = true;
+    for (int r = 0; r < xg.nr && ok; r++) {
+      const uint2 *src = xg.area[xg.rank] + dp_tp_am_slot_offset(e, r) + 2 * tid;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      ok = false;
+      for (unsigned it = 0; it < wait_limit; it++) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+        if (w.y == e && w.w == e) { ok = true; break; }
       }
+      const float v2 = __uint_as_float(w.x);
+      const int i2 = (int)w.z;
+      if (ok && (v2 > bv || (v2 == bv && i2 < bi))) { bv = v2; bi = i2; }
     }
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < nr) {
-    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(xd->area[tid] + dp_tp_flags_offset_floats()) + (e & 1u) * DP_TP_MAX_RANKS + rank;
-    *flag = e;
-  }
-  // 2. wait for every rank's flag in local memory
-  if (tid < nr) {
-    volatile unsigned *flag = reinterpret_cast<volatile unsigned *>(xd->area[rank] + dp_tp_flags_offset_floats()) + (e & 1u) * DP_TP_MAX_RANKS + tid;
-    bool seen = false;
-    for (unsigned it = 0; it < (1u << 22); it++) {
-      if ((int)(*flag - e) >= 0) { seen = true; break; }
-    }
-    if (!seen) { s_bad = 1; atomicExch(err, 3); }
-  }
-  __syncthreads();
-  __threadfence_system();
-  // 3. reduce in rank order, residual add, RMSNorm, digits
-  const float *mine = xd->area[rank] + par_off;
-  float v[4][8];
-  float ss = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int b = warp + 8 * i;
-    if (b < bpr) {
-      const int off = b * QK_K + lane * 8;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int r = 0; r < nr; r++) {
-        const float *src = mine + (size_t)r * DP_TP_SLOT_FLOATS + off;
-        const float4 a = __ldcv(reinterpret_cast<const float4 *>(src)), c = __ldcv(reinterpret_cast<const float4 *>(src + 4));  // written by peers: never from a stale L1 line
-        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += c.x; acc[5] += c.y; acc[6] += c.z; acc[7] += c.w;
-      }
-      const float4 ha = *reinterpret_cast<const float4 *>(h + off), hc = *reinterpret_cast<const float4 *>(h + off + 4);
-      v[i][0] = ha.x + acc[0]; v[i][1] = ha.y + acc[1]; v[i][2] = ha.z + acc[2]; v[i][3] = ha.w + acc[3];
-      v[i][4] = hc.x + acc[4]; v[i][5] = hc.y + acc[5]; v[i][6] = hc.z + acc[6]; v[i][7] = hc.w + acc[7];
-      *reinterpret_cast<float4 *>(h + off) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-      *reinterpret_cast<float4 *>(h + off + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
-#pragma unroll
-      for (int j = 0; j < 8; j++) ss = fmaf(v[i][j], v[i][j], ss);
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (lane == 0) sh[warp] = ss;
-  __syncthreads();
-  float total = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; i++) total += sh[i];
-  const float inv_rms = 1.0f / sqrtf(total / (float)size + eps);
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int b = warp + 8 * i;
-    if (b < bpr) {
-      const int off = b * QK_K + lane * 8;
-      const float4 wa = *reinterpret_cast<const float4 *>(norm_w + off), wc = *reinterpret_cast<const float4 *>(norm_w + off + 4);
-      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
-      float o[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) o[j] = v[i][j] * inv_rms * wv[j];
-      *reinterpret_cast<float4 *>(n_out + off) = make_float4(o[0], o[1], o[2], o[3]);
-      *reinterpret_cast<float4 *>(n_out + off + 4) = make_float4(o[4], o[5], o[6], o[7]);
-      actq_emit_block(o, lane, b, bpr, actq);
-    }
+    if (!ok) atomicExch(err, 3);
+    tok[tid] = bi;
   }
 }
 
@@ -422,6 +393,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   dp_model *m = new dp_model();
   m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
   if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
+  if (const char *e = getenv("DP_DECODE_PERSISTENT")) m->persistent = atoi(e) != 0 ? 1 : 0;
   m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
   m->qdim = m->nh * c.head_dim; m->kvdim = m->nkv * c.head_dim;
   m->inter = c.inter / p; m->vocab_l = c.vocab / p; m->vocab0 = m->vocab_l * c.tp_rank;
@@ -457,8 +429,8 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   const size_t T = m->T;
   const size_t n_h = align_up(T * H, 64), n_qkv = align_up(T * (m->qdim + 2 * m->kvdim), 64), n_q = align_up(T * m->qdim, 64);
   const size_t n_gu = align_up(T * 2 * m->inter, 64), n_act = align_up(T * m->inter, 64), n_log = align_up((size_t)B * m->vocab_l, 64);
-  acquire((3 * n_h + n_qkv + 2 * n_q + n_gu + n_act + n_log) * 4, "activations", &m->act);
-  acquire(4096 + 1024 + 2048 + 16384 + (size_t)B * 256 * 8, "decode_state", &m->state);
+  acquire((3 * n_h + n_qkv + 2 * n_q + n_gu + n_act + n_log + 2 * align_up(H, 64) + 2 * align_up(m->inter, 64)) * 4, "activations", &m->act);
+  acquire(4096 + 1024 + 2048 + 16384 + (size_t)B * 256 * 8 + 4096, "decode_state", &m->state);
   // split-K scratch sized for the longest context
   dpk_attn_params ap{};
   ap.batch = B; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
@@ -480,7 +452,10 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   m->final_norm = nb;
   float *a = (float *)m->act->dptr;
   m->h = a; a += n_h; m->n = a; a += n_h; m->partial = a; a += n_h; m->qkv = a; a += n_qkv; m->q = a; a += n_q;
-  m->att = a; a += n_q; m->gu = a; a += n_gu; m->actv = a; a += n_act; m->logits = a;
+  m->att = a; a += n_q; m->gu = a; a += n_gu; m->actv = a; a += n_act; m->logits = a; a += n_log;
+  m->hbuf[0] = m->h; m->hbuf[1] = a; a += align_up(H, 64); m->hbuf[2] = a; a += align_up(H, 64);
+  m->act_ll = (uint2 *)a;  // 8-byte words: the slab is 256-byte aligned and every part before is a multiple of 64 floats
+  m->h_last = m->h;
   int *si = (int *)m->state->dptr;
   m->d_pos = si; m->d_kvlen = si + 256; m->d_tok = si + 512; m->d_step = si + 768;
   char *sp = (char *)m->state->dptr + 4096;
@@ -488,6 +463,8 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   m->am_pair_i = (int *)sp; sp += 2048;             // (value, index) per sequence, this rank
   m->am_gather = (float *)sp; sp += 16384;          // the pairs of up to 8 ranks
   m->am_vals = (float *)sp; m->am_idx = (int *)(m->am_vals + (size_t)B * 256);
+  m->attn_counters = (int *)((char *)m->state->dptr + m->state->bytes - 4096);  // zeroed below; the kernel leaves them at zero
+  m->d_ticket = (unsigned *)(ctx->dev_status + 16);  // zeroed with the context, then only ever incremented
   // rope tables (host build, init-rope.js semantics)
   {
     std::vector<float> cs((size_t)c.max_seq * D / 2), sn((size_t)c.max_seq * D / 2);
@@ -499,6 +476,7 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   if (st == DP_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
     st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaEventCreate failed");
   if (st == DP_OK) st = dp_buf_fill(ctx, m->state, 0, 0, m->state->bytes);
+  if (st == DP_OK && cudaMemsetAsync(m->act_ll, 0, (size_t)m->inter * 8, ctx->stream) != cudaSuccess) st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaMemsetAsync failed");
   if (st != DP_OK) { dp_model_destroy(m); return st; }
   *out = m;
   return DP_OK;
@@ -543,10 +521,15 @@ extern "C" dp_status dp_model_load_q4k(dp_model *m, int layer, dp_weight_id whic
       return dp_buf_upload(ctx, L.qkv, src + (size_t)r * rows * row_bytes, dst_row * row_bytes, (size_t)rows * row_bytes);
     }
     case DP_W_GATE: case DP_W_UP: {
+      // one matrix for both, rows interleaved in groups of eight: gate rows 8j..8j+7, then up rows 8j..8j+7
       DP_TRY(expect(c.inter, H, which == DP_W_GATE ? "gate_proj" : "up_proj"));
       const int rows = c.inter / p;
-      const size_t dst_row = which == DP_W_GATE ? 0 : (size_t)m->inter;
-      return dp_buf_upload(ctx, L.gateup, src + (size_t)r * rows * row_bytes, dst_row * row_bytes, (size_t)rows * row_bytes);
+      DP_CHECK(ctx, rows % 8 == 0, "loadQ4K: %d gate/up rows per rank are not a multiple of 8", rows);
+      const uint8_t *mine = src + (size_t)r * rows * row_bytes;
+      DP_CUDA(ctx, cudaMemcpy2DAsync((char *)L.gateup->dptr + (which == DP_W_GATE ? 0 : 8) * row_bytes, 16 * row_bytes, mine, 8 * row_bytes,
+                                     8 * row_bytes, (size_t)rows / 8, cudaMemcpyHostToDevice, ctx->stream));
+      DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      return DP_OK;
     }
     case DP_W_O: case DP_W_DOWN: {  // row parallel: this rank's super-block columns of every row
       const int kfull = which == DP_W_O ? c.n_heads * c.head_dim : c.inter;
@@ -619,6 +602,7 @@ extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
   if (mode == 1) {
     if (m->cfg.tp_size > 1 && !dp_tp_exchange_desc(m->ctx))
       return dp_fail(m->ctx, DP_ERR_STATE, "model: allreduce mode 1 needs the peer-memory exchange area (dp_tp_ipc_export / dp_tp_ipc_attach)");
+    if (m->persistent == 0) return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode 1 lives in the persistent decode kernel (DP_DECODE_PERSISTENT=0 disables it)");
     if (m->cfg.hidden % DP_QK_K || m->cfg.hidden > DP_TP_SLOT_FLOATS)
       return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode 1 carries hidden sizes that are multiples of 256 up to %d", DP_TP_SLOT_FLOATS);
   }
@@ -674,6 +658,121 @@ enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
 // (RMSNorm, SiLU*up or the split-K merge) while its weight ring fills, so a layer is six kernels:
 //   GEMV qkv [rmsnorm]  ->  qk-norm + rope + KV append  ->  attention split
 //   -> GEMV o [split merge] + residual  ->  GEMV gate|up [rmsnorm]  ->  GEMV down [silu*up] + residual
+// ---- single-token decode on the persistent per-layer kernel (decode_layer.cu) ----
+// Launches per step: gather, [q|k|v of layer 0], then per layer: attention (QK norm + RoPE + KV append +
+// split-K partials) and ONE kernel for o_proj -> gate|up -> down_proj -> q|k|v of the next layer (the last
+// layer ends with the final RMSNorm instead), LM head, argmax.
+struct DecodeGroup {  // the exchange group single-token decode runs on
+  int rank = 0, nr = 0;
+  uint2 *area[DP_TP_MAX_RANKS] = {};
+};
+
+// the group's areas (one-shot mode), a one-rank local area without tensor parallelism, or none (nr == 0:
+// NCCL mode, the per-projection schedule)
+static dp_status decode_group(dp_model *m, DecodeGroup *g) {
+  *g = DecodeGroup();
+  if (m->cfg.tp_size > 1) {
+    if (m->allreduce_mode == 1 && !dp_tp_exchange_view(m->ctx, &g->rank, &g->nr, g->area)) g->nr = 0;
+    return DP_OK;
+  }
+  DP_TRY(dp_tp_local_area(m->ctx, &g->area[0]));
+  g->rank = 0; g->nr = 1;
+  return DP_OK;
+}
+
+// Hand-off tickets of a step: layer l uses 3l (o_proj partials), 3l + 1 (silu(gate) * up) and 3l + 2 (down_proj
+// partials); a step's tickets start at its number (m->d_ticket, never reset) times the stride.
+static bool decode_phase_list(dp_model *m, int l, const DecodeGroup &g, DlParams *P) {
+  const dp_model_cfg &c = m->cfg;
+  const int H = c.hidden, nqkv = m->qdim + 2 * m->kvdim;
+  memset(P, 0, sizeof *P);
+  P->eps = c.eps; P->D = c.head_dim; P->splits = m->attn_splits_decode; P->hidden = H;
+  P->rank = g.rank; P->nr = g.nr;
+  for (int r = 0; r < g.nr; r++) P->area[r] = g.area[r];
+  P->act = m->act_ll;
+  P->ticket_step = m->d_ticket; P->ticket_stride = 3u * (unsigned)c.n_layers + 4u;
+  P->wait_limit = m->ctx->wait_limit; P->err = m->ctx->dev_status;
+  auto qkv_phase = [&](int layer, DlPhase *ph) {
+    ph->W = (const uint8_t *)m->layers[layer].qkv->dptr; ph->N = nqkv; ph->K = H;
+    ph->out = DL_OUT_STORE; ph->y = m->qkv;
+  };
+  if (l < 0) {  // the step's first kernel: q|k|v of layer 0 from the gathered embedding row
+    P->n_phases = 1;
+    P->h_in = m->hbuf[0];
+    qkv_phase(0, &P->ph[0]);
+    P->ph[0].src = DL_SRC_RMSNORM; P->ph[0].norm_w = m->layers[0].in_norm;
+    return dpk_decode_layer_plan(m->ctx, P);
+  }
+  LayerW &L = m->layers[l];
+  P->n_phases = 4;
+  P->h_in = m->hbuf[l % 3];  // the launch reads one buffer and leaves the updated stream in the next
+  DlPhase *o = &P->ph[0], *gu = &P->ph[1], *dn = &P->ph[2], *nx = &P->ph[3];
+  o->W = (const uint8_t *)L.o->dptr; o->N = H; o->K = m->qdim; o->src = DL_SRC_VECTOR; o->x = m->att;  // merged by the attention kernel's last CTAs
+  o->out = DL_OUT_PUSH; o->parity = 0; o->ticket_out = 3u * (unsigned)l;
+  gu->W = (const uint8_t *)L.gateup->dptr; gu->N = 2 * m->inter; gu->K = H; gu->src = DL_SRC_XCHG_RMSNORM; gu->parity = 0; gu->ticket_in = 3u * (unsigned)l;
+  gu->norm_w = L.post_norm; gu->out = DL_OUT_SILU; gu->ticket_out = 3u * (unsigned)l + 1u;
+  dn->W = (const uint8_t *)L.down->dptr; dn->N = H; dn->K = m->inter; dn->src = DL_SRC_ACT; dn->ticket_in = 3u * (unsigned)l + 1u;
+  dn->out = DL_OUT_PUSH; dn->parity = 1; dn->ticket_out = 3u * (unsigned)l + 2u;
+  nx->src = DL_SRC_XCHG_RMSNORM; nx->parity = 1; nx->ticket_in = 3u * (unsigned)l + 2u; nx->h_out = m->hbuf[(l + 1) % 3];
+  if (l + 1 < c.n_layers) {
+    qkv_phase(l + 1, nx);
+    nx->norm_w = m->layers[l + 1].in_norm;
+  } else {  // after the last layer: the final RMSNorm for the LM head, no projection
+    nx->W = nullptr; nx->N = 0; nx->K = H; nx->norm_w = m->final_norm; nx->n_out = m->n; nx->out = DL_OUT_STORE;
+  }
+  return dpk_decode_layer_plan(m->ctx, P);
+}
+
+static bool persistent_decode_ok(dp_model *m, const DecodeGroup &g) {
+  if (m->persistent == 0 || (m->persistent < 0 && g.nr < 2) || g.nr < 1 || !m->ctx->dev_status) return false;
+  const dp_model_cfg &c = m->cfg;
+  if (m->attn_splits_decode < 2 || c.head_dim % 8 || m->qdim % QK_K || c.hidden % QK_K || m->inter % QK_K) return false;
+  if (!m->fuse_qk) return false;
+  dpk_attn_params ap{};
+  ap.batch = 1; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = c.head_dim;
+  if (!dpk_attention_uses_tc(m->ctx, ap)) return false;
+  DlParams P;
+  for (int l = -1; l < c.n_layers; l++)
+    if (!decode_phase_list(m, l, g, &P)) return false;
+  return true;
+}
+
+// attention of one decode step and layer: QK norm + RoPE + KV append + split-K partials in one kernel
+static dp_status decode_attention(dp_model *m, int l, int tokens) {
+  const dp_model_cfg &c = m->cfg;
+  LayerW &L = m->layers[l];
+  dpk_attn_params ap{};
+  ap.q = m->q; ap.out = m->att;
+  ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = c.head_dim;
+  ap.scale = 1.0f / sqrtf((float)c.head_dim); ap.softcap = 0.0f; ap.sliding_window = 0; ap.kv_start = 0;
+  ap.k = (const __half *)m->kc[l]->dptr; ap.v = (const __half *)m->vc[l]->dptr;
+  ap.batch = tokens; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.causal = 0; ap.start_pos = 0;
+  ap.kv_batch_stride = (size_t)c.max_seq * m->kvdim; ap.kv_lens = m->d_kvlen;
+  ap.fuse.qkv = m->qkv;
+  ap.fuse.q_norm = L.q_norm; ap.fuse.k_norm = L.k_norm;
+  ap.fuse.cos_t = m->rope_cos; ap.fuse.sin_t = m->rope_sin;
+  ap.fuse.pos = m->d_pos;
+  ap.fuse.kc = (__half *)m->kc[l]->dptr; ap.fuse.vc = (__half *)m->vc[l]->dptr;
+  ap.fuse.eps = c.eps; ap.fuse.nh = m->nh; ap.fuse.nkv = m->nkv;
+  ap.merge_counters = m->attn_counters;  // the last CTA of every KV-head group merges the splits into m->att
+  return dpk_attention_split_only(m->ctx, ap, (float *)m->attn_scratch->dptr, m->attn_splits_decode);
+}
+
+static dp_status run_layers_persistent(dp_model *m, const DecodeGroup &xd, bool with_attention) {
+  dp_ctx *ctx = m->ctx;
+  DlParams P;
+  if (!decode_phase_list(m, -1, xd, &P)) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: no plan for the first projection");
+  DP_TRY(dpk_decode_layer(ctx, P));
+  for (int l = 0; l < m->cfg.n_layers; l++) {
+    if (with_attention) DP_TRY(decode_attention(m, l, 1));
+    if (!decode_phase_list(m, l, xd, &P)) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: no plan for layer %d", l);
+    DP_TRY(dpk_decode_layer(ctx, P));
+  }
+  m->final_norm_done = true;
+  m->h_last = m->hbuf[m->cfg.n_layers % 3];
+  return DP_OK;
+}
+
 static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
   dp_ctx *ctx = m->ctx;
   const dp_model_cfg &c = m->cfg;
@@ -681,20 +780,19 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
   const size_t kv_seq_stride = (size_t)c.max_seq * m->kvdim;
   const int heads = m->nh + 2 * m->nkv;
   const bool single = decode && tokens == 1;
-  // tensor-parallel single-token decode with the one-shot exchange: the kernel that sums the
-  // partial vectors also applies the residual and the NEXT RMSNorm (and emits its digits)
-  const bool fused_ar = single && p > 1 && m->allreduce_mode == 1 && dp_tp_exchange_desc(ctx) != nullptr;
-  bool n_ready = false;  // m->n / digits already hold rmsnorm(h, in_norm of this layer)
+  if (single) {
+    DecodeGroup xd;
+    DP_TRY(decode_group(m, &xd));
+    if (persistent_decode_ok(m, xd)) return run_layers_persistent(m, xd, true);
+    if (p > 1 && m->allreduce_mode == 1)
+      return dp_fail(ctx, DP_ERR_UNSUPPORTED, "decode: the one-shot exchange needs shapes the persistent decode kernel plans (multiples of 256, a split KV range)");
+  }
   for (int l = 0; l < c.n_layers; l++) {
     LayerW &L = m->layers[l];
     const int nqkv = m->qdim + 2 * m->kvdim;
     // ---- q, k, v ----
     bool done = false;
-    if (n_ready) {  // written by the exchange kernel of the previous layer
-      n_ready = false;
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, true));
-      done = true;
-    } else if (single) {
+    if (single) {
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.qkv->dptr, SRC_RMSNORM, m->h, L.in_norm, c.eps, 0, 0, m->qkv, nqkv, H, nullptr, &done));
     }
     if (!done) {
@@ -763,23 +861,13 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       DP_TRY(q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, o_dst, tokens, H, m->qdim, o_res));
     }
     // ---- exchange after o_proj (tensor parallel) and the post-attention norm ----
-    bool gu_digits = false;  // digits of rmsnorm(h, post_norm) already in m->actq
     if (p > 1) {
-      if (fused_ar) {
-        DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h,
-                  (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps, ctx->dev_status);
-        gu_digits = true;
-      } else {
-        DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
-        DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
-      }
+      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
     }
     // ---- gate | up ----
     done = false;
-    if (gu_digits) {
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, true));
-      done = true;
-    } else if (single) {
+    if (single) {
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
                                     nullptr, &done));
     }
@@ -812,18 +900,12 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       DP_TRY(q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, d_dst, tokens, H, m->inter, d_res, emit));
     }
     if (p > 1) {
-      if (fused_ar) {
-        const float *next_w = l + 1 < c.n_layers ? m->layers[l + 1].in_norm : m->final_norm;
-        DP_LAUNCH(ctx, tp_allreduce_rmsnorm_kernel, 1, 256, 0, dp_tp_exchange_desc(ctx), (const float *)m->partial, m->h, next_w,
-                  m->n, m->actq->dptr, H, c.eps, ctx->dev_status);
-        n_ready = true;
-      } else {
-        DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
-        DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
-      }
+      DP_TRY(dp_tp_allreduce_ptr(ctx, m->partial, (size_t)tokens * H));
+      DP_TRY(dpk_residual_add(ctx, m->h, m->partial, m->h, (size_t)tokens * H, 1.0f));
     }
   }
-  m->final_norm_done = n_ready;
+  m->final_norm_done = false;
+  m->h_last = m->h;
   return DP_OK;
 }
 
@@ -839,10 +921,17 @@ static dp_status run_head(dp_model *m, const float *hrow, int rows) {
     DP_TRY(dpk_argmax(ctx, m->logits + (size_t)b * m->vocab_l, m->vocab_l, -1, m->d_tok, b, m->am_vals + (size_t)b * 256,
                       m->am_idx + (size_t)b * 256, m->vocab0, m->am_best + b));
   if (c.tp_size > 1) {
-    float *pairs = (float *)m->am_pair_i;
-    DP_LAUNCH(ctx, pack_pair_kernel, 1, 256, 0, m->am_best, m->d_tok, pairs, rows);
-    DP_TRY(dp_tp_allgather_ptr(ctx, pairs, m->am_gather, (size_t)rows * 8));
-    DP_LAUNCH(ctx, argmax_merge_kernel, 1, 256, 0, m->am_gather, c.tp_size, rows, m->d_tok);
+    dp_tp_exchange *xd = dp_tp_exchange_desc(ctx);
+    ArgmaxExchange xg{};
+    if (m->allreduce_mode == 1 && xd && rows <= DP_TP_MAX_BATCH && dp_tp_exchange_view(ctx, &xg.rank, &xg.nr, xg.area)) {
+      // pairs pushed into every rank's exchange area
+      DP_LAUNCH(ctx, tp_argmax_exchange_kernel, 1, 256, 0, xg, xd, (const float *)m->am_best, m->d_tok, rows, ctx->wait_limit, ctx->dev_status);
+    } else {
+      float *pairs = (float *)m->am_pair_i;
+      DP_LAUNCH(ctx, pack_pair_kernel, 1, 256, 0, m->am_best, m->d_tok, pairs, rows);
+      DP_TRY(dp_tp_allgather_ptr(ctx, pairs, m->am_gather, (size_t)rows * 8));
+      DP_LAUNCH(ctx, argmax_merge_kernel, 1, 256, 0, m->am_gather, c.tp_size, rows, m->d_tok);
+    }
   }
   return DP_OK;
 }
@@ -873,6 +962,7 @@ extern "C" dp_status dp_model_prefill(dp_model *m, int seq, const int32_t *token
   int tok = 0;
   DP_CUDA(ctx, cudaMemcpyAsync(&tok, m->d_tok, 4, cudaMemcpyDeviceToHost, ctx->stream));
   DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  DP_TRY(dp_take_dev_status(ctx));  // a bounded device-side wait that gave up invalidates the result
   if (next_token) *next_token = tok;
   return DP_OK;
 }
@@ -882,7 +972,7 @@ static dp_status record_decode_step(dp_model *m, int batch) {
   DP_TRY(dpk_gather_f16(ctx, m->d_tok, (const __half *)m->embed->dptr, m->h, batch, m->cfg.hidden));
   DP_TRY(run_layers(m, batch, true, 0, 0));
   DP_TRY(run_head(m, m->h, batch));
-  DP_LAUNCH(ctx, advance_kernel, 1, 256, 0, m->d_pos, m->d_kvlen, m->d_tok, m->d_step, (int *)m->out_tokens->dptr, batch);
+  DP_LAUNCH(ctx, advance_kernel, 1, 256, 0, m->d_pos, m->d_kvlen, m->d_tok, m->d_step, (int *)m->out_tokens->dptr, batch, m->d_ticket);
   return DP_OK;
 }
 
@@ -927,6 +1017,7 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
   float ms = 0;
   DP_CUDA(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
   m->last_ms = ms;
+  DP_TRY(dp_take_dev_status(ctx));  // a bounded device-side wait that gave up invalidates the tokens (DP_ERR_TIMEOUT)
   for (int b = 0; b < batch; b++) m->seq_len[b] += steps;
   return DP_OK;
 }
@@ -942,7 +1033,7 @@ extern "C" dp_status dp_model_read_logits(dp_model *m, float *host, int n) {
 extern "C" dp_status dp_model_read_hidden(dp_model *m, float *host, int n) {
   if (!m || !host) return DP_ERR_INVALID;
   DP_CHECK(m->ctx, n > 0 && (size_t)n <= (size_t)m->T * m->cfg.hidden, "readHidden: %d values requested", n);
-  DP_CUDA(m->ctx, cudaMemcpyAsync(host, m->h, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+  DP_CUDA(m->ctx, cudaMemcpyAsync(host, n <= m->cfg.hidden ? m->h_last : m->h, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
   DP_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
   return DP_OK;
 }
@@ -955,31 +1046,48 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
   const int H = c.hidden;
   struct Shape { int N, K; };
   const Shape sh[4] = {{m->qdim + 2 * m->kvdim, H}, {H, m->qdim}, {2 * m->inter, H}, {H, m->inter}};
-  uint64_t n_launch = 0, n_bytes = 0;
-  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
-  DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
+  uint64_t n_bytes = 0;
+  for (int i = 0; i < 4; i++)
+    n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
+  n_bytes *= (uint64_t)c.n_layers * (uint64_t)reps;
+  DecodeGroup xd;
+  DP_TRY(decode_group(m, &xd));
+  const bool persistent = persistent_decode_ok(m, xd) && c.tp_size == 1;  // (under TP the hand-offs would need every rank here)
+  if (!persistent)  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
+    DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
   const uint64_t l0 = ctx->launches;
   ctx->pdl = true;
   DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
-  for (int r = 0; r < reps; r++)
-    for (int l = 0; l < c.n_layers; l++) {
+  dp_status st = DP_OK;
+  for (int r = 0; r < reps && st == DP_OK; r++) {
+    if (persistent) {
+      // the kernels the decode graph launches for the projections, without the attention between them
+      // (the o_proj phase then merges whatever split partials the last step left: same work, stale input)
+      st = run_layers_persistent(m, xd, false);
+      if (st == DP_OK) {  // the next repetition is a new step for the hand-off tickets
+        cudaError_t e = dp_launch_impl(ctx, bump_ticket_kernel, dim3(1), dim3(32), 0, m->d_ticket);
+        ctx->launches++;
+        if (e != cudaSuccess) st = dp_fail(ctx, DP_ERR_CUDA, "bench_gemv: %s", cudaGetErrorString(e));
+      }
+      continue;
+    }
+    for (int l = 0; l < c.n_layers && st == DP_OK; l++) {
       LayerW &L = m->layers[l];
       const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,
                              (const uint8_t *)L.down->dptr};
       const float *X[4] = {m->n, m->att, m->n, m->actv};
       float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
-      for (int i = 0; i < 4; i++) {
-        // digits_ready: in the decode step the producer kernel has already written them
-        DP_TRY(q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K)));
-        n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
-      }
+      for (int i = 0; i < 4 && st == DP_OK; i++)  // digits_ready: in the decode step the producer kernel has already written them
+        st = q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K));
     }
+  }
   ctx->pdl = false;
+  m->final_norm_done = false;
+  DP_TRY(st);
   DP_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
   DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   float ms = 0;
   DP_CUDA(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
-  n_launch = ctx->launches - l0;
-  *ms_total = ms; *launches = n_launch; *bytes = n_bytes;
+  *ms_total = ms; *launches = ctx->launches - l0; *bytes = n_bytes;
   return DP_OK;
 }

@@ -205,7 +205,7 @@ extern "C" dp_status dp_attention(dp_ctx *ctx, dp_recorder *rec, const dp_tensor
   if (o.kv_lens) DP_CHECK(ctx, o.kv_lens->active && o.kv_lens->bytes >= (size_t)o.batch * 4, "attention: kvLenBuffer too small");
   dp_buf obuf = nullptr;
   DP_TRY(dp_out_buffer(ctx, o.out_buf, 0, q_elems * 4, "attention_output", &obuf));
-  dpk_attn_params p;
+  dpk_attn_params p{};
   p.q = (const float *)dp_tptr(Q);
   p.k = (const __half *)dp_tptr(K);
   p.v = (const __half *)dp_tptr(V);

@@ -63,10 +63,11 @@ struct dp_tp_state {
   void *xbuf = nullptr;             // this rank's area
   void *peer[DP_TP_MAX_RANKS] = {}; // every rank's area as seen from this process (peer[rank] == xbuf)
   bool attached = false;
+  bool loopback = false;               // dp_tp_init_loopback: no communicator, every area is local memory
   dp_tp_exchange *dev_desc = nullptr;  // device copy of the descriptor handed to kernels
 };
 
-bool dp_tp_ready(dp_ctx *ctx) { return ctx && ctx->tp && ctx->tp->comm; }
+bool dp_tp_ready(dp_ctx *ctx) { return ctx && ctx->tp && (ctx->tp->comm || ctx->tp->loopback); }
 
 extern "C" dp_status dp_tp_unique_id(void *out128) {
   if (!out128) return DP_ERR_INVALID;
@@ -99,9 +100,47 @@ extern "C" dp_status dp_tp_init(dp_ctx *ctx, int rank, int size, const void *id1
   return DP_OK;
 }
 
+// A group without a communicator whose `size` exchange areas all live on THIS GPU and are written by
+// nobody else.  It exists so that the bounded waits of the decode kernels can be exercised on one
+// GPU: rank `rank` pushes into every area and then waits for flags that the absent ranks never raise,
+// gives up after the context's poll limit and reports DP_ERR_TIMEOUT.  Collectives that need a
+// communicator (prefill under tensor parallelism) return DP_ERR_STATE on such a group.
+extern "C" dp_status dp_tp_init_loopback(dp_ctx *ctx, int rank, int size) {
+  if (!ctx) return DP_ERR_INVALID;
+  DP_CHECK(ctx, size >= 1 && size <= DP_TP_MAX_RANKS && rank >= 0 && rank < size, "tp_init_loopback: rank %d / size %d", rank, size);
+  if (ctx->tp) return dp_fail(ctx, DP_ERR_STATE, "tp_init_loopback: the context already has a group");
+  DP_CUDA(ctx, cudaSetDevice(ctx->device));
+  dp_tp_state *tp = new dp_tp_state();
+  tp->rank = rank; tp->size = size; tp->loopback = true;
+  dp_tp_exchange d;
+  memset(&d, 0, sizeof d);
+  d.rank = rank; d.size = size;
+  cudaError_t e = cudaSuccess;
+  for (int r = 0; r < size && e == cudaSuccess; r++) {
+    e = cudaMalloc(&tp->peer[r], dp_tp_area_bytes());
+    if (e == cudaSuccess) e = cudaMemset(tp->peer[r], 0, dp_tp_area_bytes());
+    d.area[r] = (uint2 *)tp->peer[r];
+  }
+  if (e == cudaSuccess) e = cudaMalloc(&tp->dev_desc, sizeof d + 64);
+  if (e == cudaSuccess) e = cudaMemcpy(tp->dev_desc, &d, sizeof d, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    for (int r = 0; r < size; r++) if (tp->peer[r]) cudaFree(tp->peer[r]);
+    if (tp->dev_desc) cudaFree(tp->dev_desc);
+    delete tp;
+    return dp_fail(ctx, DP_ERR_CUDA, "tp_init_loopback: %s", cudaGetErrorString(e));
+  }
+  tp->xbuf = tp->peer[rank];
+  tp->attached = true;
+  ctx->tp = tp;
+  return DP_OK;
+}
+
 extern "C" dp_status dp_tp_destroy(dp_ctx *ctx) {
   if (!ctx || !ctx->tp) return DP_OK;
   if (ctx->tp->comm) g_nccl.CommDestroy(ctx->tp->comm);
+  if (ctx->tp->loopback) {
+    for (int r = 0; r < ctx->tp->size; r++) if (r != ctx->tp->rank && ctx->tp->peer[r]) cudaFree(ctx->tp->peer[r]);
+  } else
   for (int r = 0; r < ctx->tp->size; r++)
     if (ctx->tp->attached && r != ctx->tp->rank && ctx->tp->peer[r]) cudaIpcCloseMemHandle(ctx->tp->peer[r]);
   if (ctx->tp->dev_desc) cudaFree(ctx->tp->dev_desc);
@@ -112,14 +151,14 @@ extern "C" dp_status dp_tp_destroy(dp_ctx *ctx) {
 }
 
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count) {
-  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "allreduce: no tensor-parallel group on this context");
+  if (!dp_tp_ready(ctx) || !ctx->tp->comm) return dp_fail(ctx, DP_ERR_STATE, "allreduce: no tensor-parallel communicator on this context");
   int rc = g_nccl.AllReduce(ptr, ptr, count, ncclFloat32, ncclSum, ctx->tp->comm, ctx->stream);
   if (rc != ncclSuccess) return dp_fail(ctx, DP_ERR_COMM, "ncclAllReduce failed: %s", g_nccl.GetErrorString(rc));
   return DP_OK;
 }
 
 dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank) {
-  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "allgather: no tensor-parallel group on this context");
+  if (!dp_tp_ready(ctx) || !ctx->tp->comm) return dp_fail(ctx, DP_ERR_STATE, "allgather: no tensor-parallel communicator on this context");
   int rc = g_nccl.AllGather(send, recv, bytes_per_rank, ncclChar, ctx->tp->comm, ctx->stream);
   if (rc != ncclSuccess) return dp_fail(ctx, DP_ERR_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
   return DP_OK;
@@ -135,13 +174,14 @@ extern "C" dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf b
 }
 
 // ---- peer-memory exchange area ------------------------------------------------------------
-// Each rank owns one area: two parity sets of `size` slots of DP_TP_SLOT_FLOATS floats plus one
-// epoch flag per (parity, source rank).  A rank PUSHES its partial vector into its slot of every
-// rank's area with ordinary stores over NVLink and then raises its flag there; the consumer polls
-// flags in its OWN memory only (see tp_fused.cu).
+// Each rank owns one area (layout: tp_exchange.h).  A rank PUSHES its partial vector into its slot of
+// every rank's area with ordinary stores over NVLink and then raises its flag there; the consumer
+// polls flags in its OWN memory only (decode_layer.cu, model.cu).  All ranks must barrier (on the host)
+// between the last decode call and dp_tp_destroy / dp_ctx_destroy: a slower peer may still be pushing
+// into this rank's area.
 extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *out64) {
   if (!ctx || !out64) return DP_ERR_INVALID;
-  if (!dp_tp_ready(ctx)) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_export: call dp_tp_init first");
+  if (!dp_tp_ready(ctx) || ctx->tp->loopback) return dp_fail(ctx, DP_ERR_STATE, "tp_ipc_export: call dp_tp_init first");
   dp_tp_state *tp = ctx->tp;
   DP_CHECK(ctx, tp->size <= DP_TP_MAX_RANKS, "tp_ipc_export: the exchange area holds %d ranks", DP_TP_MAX_RANKS);
   DP_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -177,7 +217,7 @@ extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *handles64_by_rank
   dp_tp_exchange d;
   memset(&d, 0, sizeof d);
   d.rank = tp->rank; d.size = tp->size;
-  for (int r = 0; r < tp->size; r++) d.area[r] = (float *)tp->peer[r];
+  for (int r = 0; r < tp->size; r++) d.area[r] = (uint2 *)tp->peer[r];
   DP_CUDA(ctx, cudaMalloc(&tp->dev_desc, sizeof d + 64));
   DP_CUDA(ctx, cudaMemset(tp->dev_desc, 0, sizeof d + 64));
   DP_CUDA(ctx, cudaMemcpy(tp->dev_desc, &d, sizeof d, cudaMemcpyHostToDevice));
@@ -189,3 +229,31 @@ extern "C" dp_status dp_tp_ipc_attach(dp_ctx *ctx, const void *handles64_by_rank
 dp_tp_exchange *dp_tp_exchange_desc(dp_ctx *ctx) {
   return (ctx && ctx->tp && ctx->tp->attached) ? ctx->tp->dev_desc : nullptr;
 }
+
+// the attached group's areas by value (kernels take them as parameters); false when there is none
+bool dp_tp_exchange_view(dp_ctx *ctx, int *rank, int *size, uint2 **areas) {
+  if (!ctx || !ctx->tp || !ctx->tp->attached) return false;
+  *rank = ctx->tp->rank; *size = ctx->tp->size;
+  for (int r = 0; r < ctx->tp->size; r++) areas[r] = (uint2 *)ctx->tp->peer[r];
+  return true;
+}
+
+// A context without a group: a one-rank exchange area in local memory, so that a single GPU runs the same
+// decode kernels (created on first use, freed with the context).
+dp_status dp_tp_local_area(dp_ctx *ctx, uint2 **area) {
+  if (!ctx->local_xd_area) {
+    void *a = nullptr;
+    DP_CUDA(ctx, cudaMalloc(&a, dp_tp_area_bytes()));
+    cudaError_t e = cudaMemset(a, 0, dp_tp_area_bytes());
+    if (e != cudaSuccess) {
+      cudaFree(a);
+      return dp_fail(ctx, DP_ERR_CUDA, "local exchange area: %s", cudaGetErrorString(e));
+    }
+    ctx->local_xd_area = a;
+  }
+  *area = (uint2 *)ctx->local_xd_area;
+  return DP_OK;
+}
+
+// (kept for the status path: nothing to reset, tickets only ever grow)
+void dp_tp_reset_barrier(dp_ctx *) {}

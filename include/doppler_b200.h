@@ -79,6 +79,12 @@ dp_status dp_ctx_create(int device, dp_ctx **out);
 void dp_ctx_destroy(dp_ctx *ctx);
 const char *dp_last_error(dp_ctx *ctx);
 dp_status dp_ctx_sync(dp_ctx *ctx);
+/* Device-side waits on another CTA or another rank (the hand-offs between the phases of the decode
+ * kernels, within a GPU and across ranks) poll at most `polls` times (default 4,194,304, a few seconds) before the kernel gives up,
+ * raises the status word and returns; the next dp_ctx_sync / dp_model_decode / dp_model_prefill then
+ * reports DP_ERR_TIMEOUT and the context stays usable.  No counterpart in the reference (WebGPU has
+ * no cross-workgroup waits); it plays the role of its device-lost detection, src/gpu/device.js:280-318. */
+dp_status dp_ctx_set_wait_limit(dp_ctx *ctx, unsigned polls);
 void *dp_ctx_stream(dp_ctx *ctx); /* the cudaStream_t all work is ordered on */
 int dp_ctx_device(dp_ctx *ctx);
 /* number of kernels this library launched on the context so far */
@@ -365,6 +371,10 @@ dp_status dp_model_set_allreduce_mode(dp_model *m, int mode);
  * emulation schema src/config/schema/emulation.schema.js:108-143 names TP). */
 dp_status dp_tp_unique_id(void *out128);                               /* ncclGetUniqueId */
 dp_status dp_tp_init(dp_ctx *ctx, int rank, int size, const void *id128);
+/* A group WITHOUT a communicator whose `size` exchange areas all live on this GPU and are written by
+ * nobody else: for exercising the bounded waits on one GPU (rank `rank` waits for flags the absent
+ * ranks never raise and gives up with DP_ERR_TIMEOUT).  Ops that need a communicator return DP_ERR_STATE. */
+dp_status dp_tp_init_loopback(dp_ctx *ctx, int rank, int size);
 dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf buf, size_t offset, size_t count);
 /* peer-memory exchange area: export this rank's handle, attach every rank's */
 dp_status dp_tp_ipc_export(dp_ctx *ctx, void *out64);

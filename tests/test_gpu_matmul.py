@@ -183,18 +183,21 @@ def test_matmul_argument_errors(dev):
 def test_large_m_gemm_takes_the_two_sm_kernel(dev):
     """M = 2048 on N = 12288 is several waves of tiles: the dispatcher then picks the two-SM kernel
     (tcgen05.mma.cta_group::2, 512 x 256 pair tiles); a ragged M checks the rows beyond the last tile.
-    Oracle: the reference's tiled prefill kernel rounds the dequantised weight to f16 before the
-    product (fused_matmul_q4_prefill_tiled_f16.wgsl:118-201), so the expectation is the float64 product
-    with f16-rounded weights, at the 1e-3 gate; against exact weights the same output differs by up to
-    4e-3 of the rms at K = 512 (both tensor-core kernels give bit-identical results)."""
+    Default numerics: the exact product (double-accumulate oracle, 1e-3 gate).  With f16_weights the
+    expectation is the float64 product with f16-rounded weights, the opt-in tiled prefill kernel's
+    numerics (fused_matmul_q4_prefill_tiled_f16.wgsl:118-201); against exact weights that output differs
+    by up to 4e-3 of the rms at K = 512."""
     N, K = 12288, 512
     W = synthetic.q4k_matrix(synthetic.key(91, 0), N, K)
-    w16 = O.q4k_dequant_flat(W, N * K).reshape(N, K).astype(np.float16).astype(np.float64)
+    w32 = O.q4k_dequant_flat(W, N * K).reshape(N, K)
+    w16 = w32.astype(np.float16).astype(np.float64)
     for M in (2048, 1300):
         A = synthetic.normal_f16(synthetic.key(92, M), M * K)
-        exp = A.astype(np.float64).reshape(M, K) @ w16.T
+        a64 = A.astype(np.float64).reshape(M, K)
         got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
-        assert_close(got, exp, f"two-SM gemm [{M},{K}]x[{N},{K}] vs f16-weight product")
+        assert_close(got, a64 @ w32.astype(np.float64).T, f"two-SM gemm [{M},{K}]x[{N},{K}] vs the exact product")
+        got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16", f16_weights=True)
+        assert_close(got, a64 @ w16.T, f"two-SM gemm [{M},{K}]x[{N},{K}], f16_weights, vs the f16-weight product")
 
 
 def test_f32_activation_gemm_runs_on_the_tensor_cores(dev):
@@ -224,20 +227,21 @@ def test_f32_activation_gemm_runs_on_the_tensor_cores(dev):
     assert (np.abs(exact - exp) / (2e-5 * (np.abs(exp) + rms) + 1e-300)).max() <= 1.0
 
 
-def test_few_tiles_split_k(dev):
-    """A problem of few output tiles (here two) is split over K: up to four CTAs per tile take whole
-    super-blocks each and add their share into the zeroed f32 output with atomics.  Oracle as in the two-SM
-    test (float64 product with f16-rounded weights, 1e-3 gate); f32 activations go through the three-pass
-    path, whose second and third pass add onto the first, against the exact-weight oracle per row."""
+def test_few_tiles_long_k_is_deterministic(dev):
+    """A problem of few output tiles and a long K (here two tiles, K = 4096): every tile is summed by one CTA
+    in a fixed order (no atomics), so two runs give the same bits; f16 activations against the exact
+    product, f32 activations (three products added in one f32 accumulator) against it per row."""
     M, N, K = 96, 256, 4096
     W = synthetic.q4k_matrix(synthetic.key(94, 0), N, K)
-    w16 = O.q4k_dequant_flat(W, N * K).reshape(N, K).astype(np.float16).astype(np.float64)
     A = synthetic.normal_f16(synthetic.key(94, 1), M * K)
-    exp = A.astype(np.float64).reshape(M, K) @ w16.T
+    exp = O.q4k_gemm(W, N, K, A.astype(np.float32), M)
     got = _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16")
-    assert_close(got, exp, f"split-K gemm [{M},{K}]x[{N},{K}] vs f16-weight product")
+    assert_close(got, exp, f"few-tile gemm [{M},{K}]x[{N},{K}] vs the exact product")
+    assert np.array_equal(got.view(np.uint32), _matmul(dev, W, N, K, A, M, out_dtype="f32", a_dtype="f16").view(np.uint32))
     A32 = synthetic.normal_f32(synthetic.key(94, 2), M * K)
     exp32 = np.asarray(O.q4k_gemm(W, N, K, A32, M), np.float64).reshape(M, N)
-    got32 = np.asarray(_matmul(dev, W, N, K, A32, M), np.float64).reshape(M, N)
+    got32 = _matmul(dev, W, N, K, A32, M)
+    assert np.array_equal(got32.view(np.uint32), _matmul(dev, W, N, K, A32, M).view(np.uint32))
+    got32 = np.asarray(got32, np.float64).reshape(M, N)
     rms = np.sqrt(np.mean(exp32 * exp32, axis=1, keepdims=True))
     assert (np.abs(got32 - exp32) / (2e-5 * (np.abs(exp32) + rms) + 1e-300)).max() <= 1.0
