@@ -54,7 +54,6 @@ extern "C" void dp_ctx_destroy(dp_ctx *ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   dp_tp_destroy(ctx);
-  if (ctx->local_xd_area) cudaFree(ctx->local_xd_area);
   for (dp_buf_s *b : ctx->all) {
     if (b->dptr) cudaFree(b->dptr);
     delete b;

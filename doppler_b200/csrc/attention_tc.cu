@@ -348,48 +348,6 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attn_tc_kernel(dpk_attn_params
       if (d == 0) { pp[D] = mm; pp[D + 1] = ll; }
     }
   }
-  // Optional: the last CTA of a (query row, head tile) to finish merges the partials of all splits itself and
-  // writes the attention output, so that no separate merge (kernel or consumer prologue) is needed.  Same
-  // arithmetic and order as the merge kernel of attention.cu.
-  if (splits > 1 && p.merge_counters) {
-    __shared__ int s_last;
-    __threadfence();  // this CTA's partials are visible before its arrival is counted
-    __syncthreads();
-    if (tid == 0) {
-      int *cnt = p.merge_counters + (size_t)z * gridDim.y + blockIdx.y;
-      const int old = atomicAdd(cnt, 1);
-      s_last = old == splits - 1;
-      if (s_last) *cnt = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      float *sm_ml = reinterpret_cast<float *>(atc_smem);  // [gt][splits][2]: running max and sum of every split (the rings are idle)
-      for (int i = tid; i < gt * splits; i += ATC_THREADS) {
-        const int hh = i / splits, sp = i % splits;
-        const float *pp = part + (((size_t)z * p.num_heads + h0 + hh) * splits + sp) * (D + 2);
-        sm_ml[2 * i] = __ldcg(pp + D);
-        sm_ml[2 * i + 1] = __ldcg(pp + D + 1);
-      }
-      __syncthreads();
-      for (int idx = tid; idx < gt * D; idx += ATC_THREADS) {
-        const int hh = idx / D, d = idx % D;
-        const float *ml = sm_ml + 2 * hh * splits;
-        float mm = -FLT_MAX;
-        for (int sp = 0; sp < splits; sp++) mm = fmaxf(mm, ml[2 * sp]);
-        const float *pp = part + ((size_t)z * p.num_heads + h0 + hh) * splits * (D + 2) + d;
-        float ll = 0.0f, acc = 0.0f;
-#pragma unroll 8
-        for (int sp = 0; sp < splits; sp++) {
-          const float ms = ml[2 * sp];
-          const float c = (ms == -FLT_MAX) ? 0.0f : exp2f(ms - mm);
-          ll = fmaf(ml[2 * sp + 1], c, ll);
-          acc = fmaf(__ldcg(pp + (size_t)sp * (D + 2)), c, acc);
-        }
-        p.out[((size_t)z * p.num_heads + h0 + hh) * D + d] = ll > 0.0f ? acc / ll : 0.0f;
-      }
-    }
-  }
 }
 
 // Shapes the tensor-core kernel takes: head_dim 64 or 128, GQA groups of up to 8 heads (or a multiple

@@ -45,7 +45,6 @@ struct dp_ctx {
   int *dev_status = nullptr;  // device word raised by a kernel whose bounded wait gave up
   dp_recorder *active_recorder = nullptr;
   dp_tp_state *tp = nullptr;
-  void *local_xd_area = nullptr;       // one-rank exchange area of a context without a group (tp.cu)
   unsigned wait_limit = 1u << 22;      // polls before a device-side wait on another CTA / rank gives up
   // Captured graphs keep device pointers.  While a capture is open or a graph of this context is alive,
   // a context scratch that has to grow is not handed back to the pool (a later acquire could give it to
@@ -194,9 +193,6 @@ struct dpk_attn_params {
   int causal, start_pos, sliding_window, kv_start;
   size_t kv_batch_stride;
   const int *kv_lens;
-  // Tensor-core kernel with a split KV range, optional: zeroed counters, one per (query row, KV head x head tile).
-  // The last CTA of a group to finish then merges the splits and writes `out` (no separate merge needed).
-  int *merge_counters;
 };
 dp_status dpk_attention(dp_ctx *ctx, const dpk_attn_params &p);
 bool dpk_attention_uses_tc(dp_ctx *ctx, const dpk_attn_params &p);

@@ -200,6 +200,9 @@ dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void 
 // its threads leave their loops, and a status word tells the host (DP_ERR_TIMEOUT).
 // ---------------------------------------------------------------------------
 #include "mbar.cuh"
+#include "handoff.cuh"
+#include "tp_exchange.h"
+#include "gemv_exchange.h"
 
 #include <cstdlib>
 
@@ -242,7 +245,12 @@ __host__ __device__ inline TgLayout tg_layout(int K, int cb, int stages) {
 //   SRC_RMSNORM  x = rmsnorm(h, w, eps)                 (rmsnorm.wgsl:119-187)
 //   SRC_SILU     x = silu(gate) * up, gu[2K] = eight gate values, their eight up values, ...   (silu.wgsl:98-104)
 //   SRC_COMBINE  x = merge of the split-K attention partials (layout of attention.cu)
-enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
+//   SRC_XCHG_RMSNORM  tensor parallel: h' = h + the partial vectors every rank pushed into this rank's
+//                exchange area (summed in rank order, so all ranks hold the same bits), x = rmsnorm(h', w, eps);
+//                each CTA also writes its share of h'.  Allreduce + residual add + RMSNorm in the prologue.
+// Output: y[row] (+ residual), or, with GemvExchange::push, the rows go as (value, ticket) words into this
+// rank's slot of every rank's exchange area (plain stores over NVLink): the allreduce's send side in the epilogue.
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4 };
 struct GemvSource {
   const float *x;   // h (SRC_RMSNORM), gu (SRC_SILU), partials (SRC_COMBINE)
   const float *w;   // norm weights
@@ -256,7 +264,7 @@ template <typename OutT, int GROUPS, int SRC>
 __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
-    const float *__restrict__ residual, int *__restrict__ err, const GemvSource gs) {
+    const float *__restrict__ residual, int *__restrict__ err, const __grid_constant__ GemvSource gs, const __grid_constant__ GemvExchange gx) {
   extern __shared__ __align__(128) uint8_t smem[];
   const TgLayout L = tg_layout(K, cb, stages);
   const int tid = threadIdx.x, lane = tid & 31, warp_all = tid >> 5;
@@ -283,10 +291,23 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
   // so under programmatic dependent launch the ring fills while the previous kernel drains.
   // The consumers first wait for the previous kernel (which produced the activation digits).
   if (group < GROUPS) {
-    pdl_wait();
     constexpr int CT = GROUPS * TG_CONSUMERS * 32;  // consumer threads
     constexpr int NW = CT / 32;
     const int cw = tid >> 5;
+    // The norm weights are written by no kernel of the step either: their loads are issued before the wait
+    // for the previous kernel, so that their latency is off the critical path of the prologue.
+    float4 nw[2][2];
+    if constexpr (SRC == SRC_RMSNORM || SRC == SRC_XCHG_RMSNORM) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int b = cw + NW * i;
+        if (b < bpr) {
+          nw[i][0] = __ldg(reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8));
+          nw[i][1] = __ldg(reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8 + 4));
+        }
+      }
+    }
+    pdl_wait();
     if constexpr (SRC == SRC_DIGITS) {
       const uint4 *src = reinterpret_cast<const uint4 *>(limbs);
       uint4 *dst = reinterpret_cast<uint4 *>(smem);
@@ -295,7 +316,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
       for (int i = tid; i < n16; i += CT) dst[i] = __ldg(src + i);
       const int rem_words = (total - n16 * 16) / 4;
       if (tid < rem_words) reinterpret_cast<uint32_t *>(smem)[n16 * 4 + tid] = __ldg(reinterpret_cast<const uint32_t *>(limbs) + n16 * 4 + tid);
-    } else if constexpr (SRC == SRC_RMSNORM) {
+    } else if constexpr (SRC == SRC_RMSNORM || SRC == SRC_XCHG_RMSNORM) {
       float *scratch = reinterpret_cast<float *>(smem + L.red);  // free until the first tile is reduced
       float v[2][8];
       float ss = 0.0f;
@@ -303,13 +324,32 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
       for (int i = 0; i < 2; i++) {
         const int b = cw + NW * i;
         if (b < bpr) {
-          const float4 a = *reinterpret_cast<const float4 *>(gs.x + b * QK_K + lane * 8);
-          const float4 c = *reinterpret_cast<const float4 *>(gs.x + b * QK_K + lane * 8 + 4);
+          const int off = b * QK_K + lane * 8;
+          const float4 a = *reinterpret_cast<const float4 *>(gs.x + off);
+          const float4 c = *reinterpret_cast<const float4 *>(gs.x + off + 4);
           v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+          if constexpr (SRC == SRC_XCHG_RMSNORM) {
+            const unsigned ticket = *reinterpret_cast<const volatile unsigned *>(gx.ticket_step) * gx.ticket_stride + 1u + gx.ticket_in;
+            const uint2 *mine = gx.mine;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int r = 0; r < gx.nr; r++) {  // rank order: every rank computes the same bits
+              float s8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              handoff_take8(mine + dp_tp_slot_offset((unsigned)gx.parity_in, r) + off, ticket, s8, gx.wait_limit, abort_flag);
+#pragma unroll
+              for (int j = 0; j < 8; j++) acc[j] += s8[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[i][j] += acc[j];
+            if (gx.h_out && (b % (int)gridDim.x) == (int)blockIdx.x) {
+              *reinterpret_cast<float4 *>(gx.h_out + off) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+              *reinterpret_cast<float4 *>(gx.h_out + off + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 8; j++) ss = fmaf(v[i][j], v[i][j], ss);
         }
       }
+      __syncwarp();
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (lane == 0) scratch[cw] = ss;
@@ -322,8 +362,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
       for (int i = 0; i < 2; i++) {
         const int b = cw + NW * i;
         if (b < bpr) {
-          const float4 wa = *reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8);
-          const float4 wc = *reinterpret_cast<const float4 *>(gs.w + b * QK_K + lane * 8 + 4);
+          const float4 wa = nw[i][0], wc = nw[i][1];
           const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wc.x, wc.y, wc.z, wc.w};
           float o[8];
 #pragma unroll
@@ -506,8 +545,16 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
           for (int w = 0; w < TG_CONSUMERS; w++) v += rs[w * 16 + lane];
           const int row = rt * 16 + lane;
           v *= alpha;
-          if (residual) v += residual[row];
-          if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
+          if (gx.push) {  // this rank's partial of the row, with the exchange's ticket, into its slot on every rank
+            const unsigned ticket = *reinterpret_cast<const volatile unsigned *>(gx.ticket_step) * gx.ticket_stride + 1u + gx.ticket_out;
+            const size_t off = dp_tp_slot_offset((unsigned)gx.parity_out, gx.rank) + (size_t)row;
+#pragma unroll
+            for (int r = 0; r < 8; r++)  // (static indices: a run-time index would copy the parameter block to local memory)
+              if (r < gx.nr) handoff_put(gx.area[r] + off, v, ticket);
+          } else {
+            if (residual) v += residual[row];
+            if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
+          }
         }
       }
     }
@@ -536,7 +583,7 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
 
 template <typename OutT, int GROUPS, int SRC>
 static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
-                            uint32_t smem, float alpha, const float *residual, const GemvSource &gs) {
+                            uint32_t smem, float alpha, const float *residual, const GemvSource &gs, const GemvExchange &gx = GemvExchange()) {
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
   const float *ssum = limbs ? xscale + K / QK_K : nullptr;
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
@@ -546,7 +593,7 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
     attr_set = true;
   }
   DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
-            N, K, cb, stages, alpha, residual, ctx->dev_status, gs);
+            N, K, cb, stages, alpha, residual, ctx->dev_status, gs, gx);
   return DP_OK;
 }
 
@@ -578,14 +625,26 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
 // f32 GEMV whose input is produced inside the kernel (mode = SRC_RMSNORM / SRC_SILU / SRC_COMBINE).
 // Returns handled = false when the shape has no TMA plan (the caller then runs the separate kernels).
 dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
-                                 int splits, float *y, int N, int K, const float *residual, bool *handled) {
+                                 int splits, float *y, int N, int K, const float *residual, bool *handled, const GemvExchange *gxp) {
   *handled = false;
   int cb, stages;
   uint32_t smem;
   if (gemv_variant() == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
-  if (K > 16 * 2 * QK_K && mode == SRC_RMSNORM) return DP_OK;  // the norm keeps two blocks per warp in registers
+  if (K > 16 * 2 * QK_K && (mode == SRC_RMSNORM || mode == SRC_XCHG_RMSNORM)) return DP_OK;  // the norm keeps two blocks per warp in registers
   GemvSource gs{};
   gs.x = x; gs.w = w; gs.eps = eps; gs.D = D; gs.splits = splits;
+  if (gxp) {
+    const GemvExchange &gx = *gxp;
+    if ((mode == SRC_XCHG_RMSNORM && K > DP_TP_SLOT_FLOATS) || (gx.push && N > DP_TP_SLOT_FLOATS)) return DP_OK;
+    if (mode == SRC_XCHG_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else return DP_OK;
+    *handled = true;
+    return DP_OK;
+  }
+  if (mode == SRC_XCHG_RMSNORM) return DP_OK;
   if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
   else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
   else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));

@@ -18,7 +18,8 @@
 #include "q4k.cuh"
 #include "actq.cuh"
 #include "tp_exchange.h"
-#include "decode_layer.h"
+#include "gemv_exchange.h"
+#include "handoff.cuh"
 
 #include <cfloat>
 #include <cmath>
@@ -38,7 +39,7 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
                                 float alpha, const float *residual, bool *handled);
 size_t dpk_q4k_actq_bytes(int K);
 dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
-                                 int splits, float *y, int N, int K, const float *residual, bool *handled);
+                                 int splits, float *y, int N, int K, const float *residual, bool *handled, const GemvExchange *gx = nullptr);
 bool dpk_gemv_q4k_fast_ok(int N, int K);
 dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits);
 dp_status dp_tp_allreduce_ptr(dp_ctx *ctx, float *ptr, size_t count);
@@ -46,9 +47,7 @@ dp_status dp_tp_allgather_ptr(dp_ctx *ctx, const void *send, void *recv, size_t 
 bool dp_tp_ready(dp_ctx *ctx);
 dp_tp_exchange *dp_tp_exchange_desc(dp_ctx *ctx);
 bool dp_tp_exchange_view(dp_ctx *ctx, int *rank, int *size, uint2 **areas);
-dp_status dp_tp_local_area(dp_ctx *ctx, uint2 **area);
 dp_status dp_take_dev_status(dp_ctx *ctx);
-dp_status dpk_decode_layer(dp_ctx *ctx, const DlParams &P);
 
 struct LayerW {
   dp_buf qkv = nullptr, o = nullptr, gateup = nullptr, down = nullptr;
@@ -68,11 +67,9 @@ struct dp_model {
   float *rope_cos = nullptr, *rope_sin = nullptr;
   dp_buf act = nullptr;  // one slab for all activations
   float *h, *n, *qkv, *q, *att, *gu, *actv, *partial, *logits;
-  float *hbuf[3];       // the residual stream of single-token decode rotates over three buffers (hbuf[0] == h): a launch of the
-                        // persistent kernel reads one and writes the next, so no CTA overwrites what another still has to read
+  float *hbuf[3];       // tensor-parallel single-token decode: the residual stream rotates over three buffers (hbuf[0] == h);
+                        // a kernel reads one and its CTAs write their shares of the next, so none overwrites what another still reads
   float *h_last;        // where the last forward pass left the hidden state
-  int *attn_counters = nullptr;   // zeroed arrival counters of the decode attention's in-kernel split merge
-  uint2 *act_ll = nullptr;        // (value, ticket) words of the silu(gate) * up hand-off inside the persistent kernel
   unsigned *d_ticket = nullptr;   // device counter of decode steps ever run on this CONTEXT (its exchange area outlives a model):
                                   // hand-off tickets derive from it and never repeat
   dp_buf state = nullptr;  // device ints: pos[B], kvlen[B], tok[B], step, then argmax scratch
@@ -85,12 +82,6 @@ struct dp_model {
   int attn_splits_decode = 1;
   bool recording_decode = false;  // set while a decode step is recorded into its CUDA graph
   bool fuse_qk = true;  // decode: QK norm + RoPE + KV append inside the attention kernel
-  // Single-token decode on the per-layer persistent kernel: -1 = when the model is tensor parallel with the
-  // one-shot exchange (there it replaces the collectives), 1 = always, 0 = never (DP_DECODE_PERSISTENT).  On
-  // one GPU the schedule with one launch per projection is faster (measured: 1.93 ms against 2.35 ms per
-  // step of the 9B shape), because the consumer warps' arithmetic, not HBM, sets the pace of the persistent
-  // kernel and its hand-off prologues cannot overlap anything.
-  int persistent = -1;
   std::vector<int> seq_len;
   dp_graph *graph[2] = {nullptr, nullptr};
   int graph_batch[2] = {0, 0};
@@ -186,11 +177,6 @@ __global__ void advance_kernel(int *pos, int *kvlen, const int *tok, int *step, 
   if (b == 0) { *step = s + 1; *ticket += 1u; }
 }
 
-__global__ void bump_ticket_kernel(unsigned *ticket) {
-  pdl_launch();
-  pdl_wait();
-  if (threadIdx.x == 0) *ticket += 1u;
-}
 
 // combine the per-rank (best value, index) pairs of a vocabulary-sharded argmax;
 // ties go to the lower global index (sample.wgsl:45-53)
@@ -369,6 +355,64 @@ __global__ void __launch_bounds__(256) tp_argmax_exchange_kernel(const ArgmaxExc
   }
 }
 
+// Tensor parallel, end of the last layer: h' = h + the partial vectors all ranks pushed after down_proj
+// (rank order), n = rmsnorm(h', w) for the LM head.  One CTA; size % 256 == 0, size <= 8192.
+__global__ void __launch_bounds__(256) xchg_rmsnorm_kernel(const __grid_constant__ GemvExchange gx, const float *__restrict__ h_in, float *__restrict__ h_out,
+                                                           const float *__restrict__ w, float *__restrict__ n_out, int size, float eps,
+                                                           int *__restrict__ err) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sh[8];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, bpr = size / QK_K;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const unsigned ticket = *reinterpret_cast<const volatile unsigned *>(gx.ticket_step) * gx.ticket_stride + 1u + gx.ticket_in;
+  const uint2 *mine = gx.mine;
+  float v[4][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const int off = b * QK_K + lane * 8;
+      const float4 a = *reinterpret_cast<const float4 *>(h_in + off), c = *reinterpret_cast<const float4 *>(h_in + off + 4);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < gx.nr; r++) {
+        float s8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        handoff_take8(mine + dp_tp_slot_offset((unsigned)gx.parity_in, r) + off, ticket, s8, gx.wait_limit, &s_abort);
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] += s8[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) { v[i][j] += acc[j]; ss = fmaf(v[i][j], v[i][j], ss); }
+      *reinterpret_cast<float4 *>(h_out + off) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      *reinterpret_cast<float4 *>(h_out + off + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) sh[warp] = ss;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) total += sh[i];
+  const float inv_rms = 1.0f / sqrtf(total / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int b = warp + 8 * i;
+    if (b < bpr) {
+      const int off = b * QK_K + lane * 8;
+      const float4 wa = *reinterpret_cast<const float4 *>(w + off), wc = *reinterpret_cast<const float4 *>(w + off + 4);
+      *reinterpret_cast<float4 *>(n_out + off) = make_float4(v[i][0] * inv_rms * wa.x, v[i][1] * inv_rms * wa.y, v[i][2] * inv_rms * wa.z, v[i][3] * inv_rms * wa.w);
+      *reinterpret_cast<float4 *>(n_out + off + 4) = make_float4(v[i][4] * inv_rms * wc.x, v[i][5] * inv_rms * wc.y, v[i][6] * inv_rms * wc.z, v[i][7] * inv_rms * wc.w);
+    }
+  }
+  if (s_abort && threadIdx.x == 0) atomicExch(err, 3);
+}
+
 // ---- create / destroy -----------------------------------------------------------
 static size_t q4k_bytes(size_t n, size_t k) { return n * dp_cdiv(k, DP_QK_K) * DP_Q4K_BLOCK_BYTES; }
 static size_t align_up(size_t v, size_t a) { return dp_cdiv(v, a) * a; }
@@ -393,7 +437,6 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   dp_model *m = new dp_model();
   m->ctx = ctx; m->cfg = c; m->cfg.tp_size = p;
   if (m->cfg.max_batch <= 0) m->cfg.max_batch = 1;
-  if (const char *e = getenv("DP_DECODE_PERSISTENT")) m->persistent = atoi(e) != 0 ? 1 : 0;
   m->nh = c.n_heads / p; m->nkv = c.n_kv_heads / p;
   m->qdim = m->nh * c.head_dim; m->kvdim = m->nkv * c.head_dim;
   m->inter = c.inter / p; m->vocab_l = c.vocab / p; m->vocab0 = m->vocab_l * c.tp_rank;
@@ -429,8 +472,8 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   const size_t T = m->T;
   const size_t n_h = align_up(T * H, 64), n_qkv = align_up(T * (m->qdim + 2 * m->kvdim), 64), n_q = align_up(T * m->qdim, 64);
   const size_t n_gu = align_up(T * 2 * m->inter, 64), n_act = align_up(T * m->inter, 64), n_log = align_up((size_t)B * m->vocab_l, 64);
-  acquire((3 * n_h + n_qkv + 2 * n_q + n_gu + n_act + n_log + 2 * align_up(H, 64) + 2 * align_up(m->inter, 64)) * 4, "activations", &m->act);
-  acquire(4096 + 1024 + 2048 + 16384 + (size_t)B * 256 * 8 + 4096, "decode_state", &m->state);
+  acquire((3 * n_h + n_qkv + 2 * n_q + n_gu + n_act + n_log + 2 * align_up(H, 64)) * 4, "activations", &m->act);
+  acquire(4096 + 1024 + 2048 + 16384 + (size_t)B * 256 * 8, "decode_state", &m->state);
   // split-K scratch sized for the longest context
   dpk_attn_params ap{};
   ap.batch = B; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = D;
@@ -454,7 +497,6 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   m->h = a; a += n_h; m->n = a; a += n_h; m->partial = a; a += n_h; m->qkv = a; a += n_qkv; m->q = a; a += n_q;
   m->att = a; a += n_q; m->gu = a; a += n_gu; m->actv = a; a += n_act; m->logits = a; a += n_log;
   m->hbuf[0] = m->h; m->hbuf[1] = a; a += align_up(H, 64); m->hbuf[2] = a; a += align_up(H, 64);
-  m->act_ll = (uint2 *)a;  // 8-byte words: the slab is 256-byte aligned and every part before is a multiple of 64 floats
   m->h_last = m->h;
   int *si = (int *)m->state->dptr;
   m->d_pos = si; m->d_kvlen = si + 256; m->d_tok = si + 512; m->d_step = si + 768;
@@ -463,7 +505,6 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   m->am_pair_i = (int *)sp; sp += 2048;             // (value, index) per sequence, this rank
   m->am_gather = (float *)sp; sp += 16384;          // the pairs of up to 8 ranks
   m->am_vals = (float *)sp; m->am_idx = (int *)(m->am_vals + (size_t)B * 256);
-  m->attn_counters = (int *)((char *)m->state->dptr + m->state->bytes - 4096);  // zeroed below; the kernel leaves them at zero
   m->d_ticket = (unsigned *)(ctx->dev_status + 16);  // zeroed with the context, then only ever incremented
   // rope tables (host build, init-rope.js semantics)
   {
@@ -476,7 +517,6 @@ extern "C" dp_status dp_model_create(dp_ctx *ctx, const dp_model_cfg *cfg, dp_mo
   if (st == DP_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
     st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaEventCreate failed");
   if (st == DP_OK) st = dp_buf_fill(ctx, m->state, 0, 0, m->state->bytes);
-  if (st == DP_OK && cudaMemsetAsync(m->act_ll, 0, (size_t)m->inter * 8, ctx->stream) != cudaSuccess) st = dp_fail(ctx, DP_ERR_CUDA, "model: cudaMemsetAsync failed");
   if (st != DP_OK) { dp_model_destroy(m); return st; }
   *out = m;
   return DP_OK;
@@ -602,7 +642,6 @@ extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
   if (mode == 1) {
     if (m->cfg.tp_size > 1 && !dp_tp_exchange_desc(m->ctx))
       return dp_fail(m->ctx, DP_ERR_STATE, "model: allreduce mode 1 needs the peer-memory exchange area (dp_tp_ipc_export / dp_tp_ipc_attach)");
-    if (m->persistent == 0) return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode 1 lives in the persistent decode kernel (DP_DECODE_PERSISTENT=0 disables it)");
     if (m->cfg.hidden % DP_QK_K || m->cfg.hidden > DP_TP_SLOT_FLOATS)
       return dp_fail(m->ctx, DP_ERR_UNSUPPORTED, "model: allreduce mode 1 carries hidden sizes that are multiples of 256 up to %d", DP_TP_SLOT_FLOATS);
   }
@@ -648,7 +687,7 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   return DP_OK;
 }
 
-enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4 };
 
 // One pass over `tokens` rows already gathered in m->h.  decode: rows are
 // sequences (positions from the device arrays); prefill: rows are consecutive
@@ -658,83 +697,17 @@ enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3 };
 // (RMSNorm, SiLU*up or the split-K merge) while its weight ring fills, so a layer is six kernels:
 //   GEMV qkv [rmsnorm]  ->  qk-norm + rope + KV append  ->  attention split
 //   -> GEMV o [split merge] + residual  ->  GEMV gate|up [rmsnorm]  ->  GEMV down [silu*up] + residual
-// ---- single-token decode on the persistent per-layer kernel (decode_layer.cu) ----
-// Launches per step: gather, [q|k|v of layer 0], then per layer: attention (QK norm + RoPE + KV append +
-// split-K partials) and ONE kernel for o_proj -> gate|up -> down_proj -> q|k|v of the next layer (the last
-// layer ends with the final RMSNorm instead), LM head, argmax.
-struct DecodeGroup {  // the exchange group single-token decode runs on
+// ---- the exchange group of tensor-parallel single-token decode ----
+struct DecodeGroup {
   int rank = 0, nr = 0;
   uint2 *area[DP_TP_MAX_RANKS] = {};
 };
 
-// the group's areas (one-shot mode), a one-rank local area without tensor parallelism, or none (nr == 0:
-// NCCL mode, the per-projection schedule)
+// the group's areas (one-shot mode), or none (nr == 0: one GPU, or NCCL mode)
 static dp_status decode_group(dp_model *m, DecodeGroup *g) {
   *g = DecodeGroup();
-  if (m->cfg.tp_size > 1) {
-    if (m->allreduce_mode == 1 && !dp_tp_exchange_view(m->ctx, &g->rank, &g->nr, g->area)) g->nr = 0;
-    return DP_OK;
-  }
-  DP_TRY(dp_tp_local_area(m->ctx, &g->area[0]));
-  g->rank = 0; g->nr = 1;
+  if (m->cfg.tp_size > 1 && m->allreduce_mode == 1 && !dp_tp_exchange_view(m->ctx, &g->rank, &g->nr, g->area)) g->nr = 0;
   return DP_OK;
-}
-
-// Hand-off tickets of a step: layer l uses 3l (o_proj partials), 3l + 1 (silu(gate) * up) and 3l + 2 (down_proj
-// partials); a step's tickets start at its number (m->d_ticket, never reset) times the stride.
-static bool decode_phase_list(dp_model *m, int l, const DecodeGroup &g, DlParams *P) {
-  const dp_model_cfg &c = m->cfg;
-  const int H = c.hidden, nqkv = m->qdim + 2 * m->kvdim;
-  memset(P, 0, sizeof *P);
-  P->eps = c.eps; P->D = c.head_dim; P->splits = m->attn_splits_decode; P->hidden = H;
-  P->rank = g.rank; P->nr = g.nr;
-  for (int r = 0; r < g.nr; r++) P->area[r] = g.area[r];
-  P->act = m->act_ll;
-  P->ticket_step = m->d_ticket; P->ticket_stride = 3u * (unsigned)c.n_layers + 4u;
-  P->wait_limit = m->ctx->wait_limit; P->err = m->ctx->dev_status;
-  auto qkv_phase = [&](int layer, DlPhase *ph) {
-    ph->W = (const uint8_t *)m->layers[layer].qkv->dptr; ph->N = nqkv; ph->K = H;
-    ph->out = DL_OUT_STORE; ph->y = m->qkv;
-  };
-  if (l < 0) {  // the step's first kernel: q|k|v of layer 0 from the gathered embedding row
-    P->n_phases = 1;
-    P->h_in = m->hbuf[0];
-    qkv_phase(0, &P->ph[0]);
-    P->ph[0].src = DL_SRC_RMSNORM; P->ph[0].norm_w = m->layers[0].in_norm;
-    return dpk_decode_layer_plan(m->ctx, P);
-  }
-  LayerW &L = m->layers[l];
-  P->n_phases = 4;
-  P->h_in = m->hbuf[l % 3];  // the launch reads one buffer and leaves the updated stream in the next
-  DlPhase *o = &P->ph[0], *gu = &P->ph[1], *dn = &P->ph[2], *nx = &P->ph[3];
-  o->W = (const uint8_t *)L.o->dptr; o->N = H; o->K = m->qdim; o->src = DL_SRC_VECTOR; o->x = m->att;  // merged by the attention kernel's last CTAs
-  o->out = DL_OUT_PUSH; o->parity = 0; o->ticket_out = 3u * (unsigned)l;
-  gu->W = (const uint8_t *)L.gateup->dptr; gu->N = 2 * m->inter; gu->K = H; gu->src = DL_SRC_XCHG_RMSNORM; gu->parity = 0; gu->ticket_in = 3u * (unsigned)l;
-  gu->norm_w = L.post_norm; gu->out = DL_OUT_SILU; gu->ticket_out = 3u * (unsigned)l + 1u;
-  dn->W = (const uint8_t *)L.down->dptr; dn->N = H; dn->K = m->inter; dn->src = DL_SRC_ACT; dn->ticket_in = 3u * (unsigned)l + 1u;
-  dn->out = DL_OUT_PUSH; dn->parity = 1; dn->ticket_out = 3u * (unsigned)l + 2u;
-  nx->src = DL_SRC_XCHG_RMSNORM; nx->parity = 1; nx->ticket_in = 3u * (unsigned)l + 2u; nx->h_out = m->hbuf[(l + 1) % 3];
-  if (l + 1 < c.n_layers) {
-    qkv_phase(l + 1, nx);
-    nx->norm_w = m->layers[l + 1].in_norm;
-  } else {  // after the last layer: the final RMSNorm for the LM head, no projection
-    nx->W = nullptr; nx->N = 0; nx->K = H; nx->norm_w = m->final_norm; nx->n_out = m->n; nx->out = DL_OUT_STORE;
-  }
-  return dpk_decode_layer_plan(m->ctx, P);
-}
-
-static bool persistent_decode_ok(dp_model *m, const DecodeGroup &g) {
-  if (m->persistent == 0 || (m->persistent < 0 && g.nr < 2) || g.nr < 1 || !m->ctx->dev_status) return false;
-  const dp_model_cfg &c = m->cfg;
-  if (m->attn_splits_decode < 2 || c.head_dim % 8 || m->qdim % QK_K || c.hidden % QK_K || m->inter % QK_K) return false;
-  if (!m->fuse_qk) return false;
-  dpk_attn_params ap{};
-  ap.batch = 1; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = c.head_dim;
-  if (!dpk_attention_uses_tc(m->ctx, ap)) return false;
-  DlParams P;
-  for (int l = -1; l < c.n_layers; l++)
-    if (!decode_phase_list(m, l, g, &P)) return false;
-  return true;
 }
 
 // attention of one decode step and layer: QK norm + RoPE + KV append + split-K partials in one kernel
@@ -754,23 +727,84 @@ static dp_status decode_attention(dp_model *m, int l, int tokens) {
   ap.fuse.pos = m->d_pos;
   ap.fuse.kc = (__half *)m->kc[l]->dptr; ap.fuse.vc = (__half *)m->vc[l]->dptr;
   ap.fuse.eps = c.eps; ap.fuse.nh = m->nh; ap.fuse.nkv = m->nkv;
-  ap.merge_counters = m->attn_counters;  // the last CTA of every KV-head group merges the splits into m->att
   return dpk_attention_split_only(m->ctx, ap, (float *)m->attn_scratch->dptr, m->attn_splits_decode);
 }
 
-static dp_status run_layers_persistent(dp_model *m, const DecodeGroup &xd, bool with_attention) {
+// ---- tensor-parallel single-token decode, one launch per projection, exchange inside the GEMVs ----
+// Five kernels per layer, as on one GPU; the sum over ranks costs no kernel and no collective call:
+//   q|k|v   [prologue: h += partials of down_proj (all ranks), RMSNorm]      (layer 0: plain RMSNorm)
+//   attention (QK norm + RoPE + KV append + split-K)
+//   o_proj  [prologue: split merge]          epilogue: rows pushed into every rank's exchange area (parity 0)
+//   gate|up [prologue: h += partials of o_proj (all ranks), RMSNorm]
+//   down    [prologue: silu(gate) * up]      epilogue: rows pushed (parity 1)
+// and after the last layer one small kernel: h += partials, final RMSNorm.  The residual stream rotates over
+// three buffers: a kernel reads one and its CTAs write their shares of the next.
+static dp_status run_layers_tp_exchange(dp_model *m, const DecodeGroup &g) {
   dp_ctx *ctx = m->ctx;
-  DlParams P;
-  if (!decode_phase_list(m, -1, xd, &P)) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: no plan for the first projection");
-  DP_TRY(dpk_decode_layer(ctx, P));
-  for (int l = 0; l < m->cfg.n_layers; l++) {
-    if (with_attention) DP_TRY(decode_attention(m, l, 1));
-    if (!decode_phase_list(m, l, xd, &P)) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: no plan for layer %d", l);
-    DP_TRY(dpk_decode_layer(ctx, P));
+  const dp_model_cfg &c = m->cfg;
+  const int H = c.hidden, D = c.head_dim, nqkv = m->qdim + 2 * m->kvdim;
+  GemvExchange base;
+  base.rank = g.rank; base.nr = g.nr;
+  for (int r = 0; r < g.nr; r++) base.area[r] = g.area[r];
+  base.mine = g.area[g.rank];
+  base.ticket_step = m->d_ticket; base.ticket_stride = 3u * (unsigned)c.n_layers + 4u;
+  base.wait_limit = ctx->wait_limit;
+  int cur = 0;  // hbuf index holding the residual stream
+  auto fail = [&](const char *what, int l) { return dp_fail(ctx, DP_ERR_UNSUPPORTED, "decode (one-shot exchange): no kernel plan for %s of layer %d", what, l); };
+  for (int l = 0; l < c.n_layers; l++) {
+    LayerW &L = m->layers[l];
+    bool done = false;
+    if (l == 0) {
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.qkv->dptr, SRC_RMSNORM, m->hbuf[cur], L.in_norm, c.eps, 0, 0, m->qkv, nqkv, H, nullptr, &done));
+    } else {
+      GemvExchange gx = base;
+      gx.ticket_in = 3u * (unsigned)(l - 1) + 2u; gx.parity_in = 1; gx.h_out = m->hbuf[(cur + 1) % 3];
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.qkv->dptr, SRC_XCHG_RMSNORM, m->hbuf[cur], L.in_norm, c.eps, 0, 0, m->qkv, nqkv, H, nullptr, &done, &gx));
+      cur = (cur + 1) % 3;
+    }
+    if (!done) return fail("q|k|v", l);
+    DP_TRY(decode_attention(m, l, 1));
+    {
+      GemvExchange gx = base;
+      gx.push = 1; gx.parity_out = 0; gx.ticket_out = 3u * (unsigned)l;
+      done = false;
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.o->dptr, SRC_COMBINE, (const float *)m->attn_scratch->dptr, nullptr, 0.0f, D,
+                                    m->attn_splits_decode, m->partial, H, m->qdim, nullptr, &done, &gx));
+      if (!done) return fail("o_proj", l);
+    }
+    {
+      GemvExchange gx = base;
+      gx.ticket_in = 3u * (unsigned)l; gx.parity_in = 0; gx.h_out = m->hbuf[(cur + 1) % 3];
+      done = false;
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_XCHG_RMSNORM, m->hbuf[cur], L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
+                                    nullptr, &done, &gx));
+      if (!done) return fail("gate|up", l);
+      cur = (cur + 1) % 3;
+    }
+    {
+      GemvExchange gx = base;
+      gx.push = 1; gx.parity_out = 1; gx.ticket_out = 3u * (unsigned)l + 2u;
+      done = false;
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, nullptr, &done, &gx));
+      if (!done) return fail("down_proj", l);
+    }
   }
+  GemvExchange gx = base;
+  gx.ticket_in = 3u * (unsigned)(c.n_layers - 1) + 2u; gx.parity_in = 1;
+  float *h_out = m->hbuf[(cur + 1) % 3];
+  DP_LAUNCH(ctx, xchg_rmsnorm_kernel, 1, 256, 0, gx, (const float *)m->hbuf[cur], h_out, (const float *)m->final_norm, m->n, H, c.eps, ctx->dev_status);
+  m->h_last = h_out;
   m->final_norm_done = true;
-  m->h_last = m->hbuf[m->cfg.n_layers % 3];
   return DP_OK;
+}
+
+static bool tp_exchange_decode_ok(dp_model *m, const DecodeGroup &g) {
+  const dp_model_cfg &c = m->cfg;
+  if (g.nr < 2 || !m->ctx->dev_status || !m->fuse_qk) return false;
+  if (m->attn_splits_decode < 2 || c.head_dim % 8 || m->qdim % QK_K || c.hidden % QK_K || m->inter % QK_K || c.hidden > 8192) return false;
+  dpk_attn_params ap{};
+  ap.batch = 1; ap.seq_len = 1; ap.kv_len = c.max_seq; ap.num_heads = m->nh; ap.num_kv_heads = m->nkv; ap.head_dim = c.head_dim;
+  return dpk_attention_uses_tc(m->ctx, ap);
 }
 
 static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int start_pos) {
@@ -783,9 +817,9 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
   if (single) {
     DecodeGroup xd;
     DP_TRY(decode_group(m, &xd));
-    if (persistent_decode_ok(m, xd)) return run_layers_persistent(m, xd, true);
+    if (tp_exchange_decode_ok(m, xd)) return run_layers_tp_exchange(m, xd);
     if (p > 1 && m->allreduce_mode == 1)
-      return dp_fail(ctx, DP_ERR_UNSUPPORTED, "decode: the one-shot exchange needs shapes the persistent decode kernel plans (multiples of 256, a split KV range)");
+      return dp_fail(ctx, DP_ERR_UNSUPPORTED, "decode: the one-shot exchange needs shapes its kernels plan (sizes that are multiples of 256, hidden <= 8192, a split KV range)");
   }
   for (int l = 0; l < c.n_layers; l++) {
     LayerW &L = m->layers[l];
@@ -1050,27 +1084,13 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
   for (int i = 0; i < 4; i++)
     n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
   n_bytes *= (uint64_t)c.n_layers * (uint64_t)reps;
-  DecodeGroup xd;
-  DP_TRY(decode_group(m, &xd));
-  const bool persistent = persistent_decode_ok(m, xd) && c.tp_size == 1;  // (under TP the hand-offs would need every rank here)
-  if (!persistent)  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
-    DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
+  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
+  DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
   const uint64_t l0 = ctx->launches;
   ctx->pdl = true;
   DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
   dp_status st = DP_OK;
   for (int r = 0; r < reps && st == DP_OK; r++) {
-    if (persistent) {
-      // the kernels the decode graph launches for the projections, without the attention between them
-      // (the o_proj phase then merges whatever split partials the last step left: same work, stale input)
-      st = run_layers_persistent(m, xd, false);
-      if (st == DP_OK) {  // the next repetition is a new step for the hand-off tickets
-        cudaError_t e = dp_launch_impl(ctx, bump_ticket_kernel, dim3(1), dim3(32), 0, m->d_ticket);
-        ctx->launches++;
-        if (e != cudaSuccess) st = dp_fail(ctx, DP_ERR_CUDA, "bench_gemv: %s", cudaGetErrorString(e));
-      }
-      continue;
-    }
     for (int l = 0; l < c.n_layers && st == DP_OK; l++) {
       LayerW &L = m->layers[l];
       const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,

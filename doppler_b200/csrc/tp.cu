@@ -176,7 +176,7 @@ extern "C" dp_status dp_tp_allreduce_f32(dp_ctx *ctx, dp_recorder *rec, dp_buf b
 // ---- peer-memory exchange area ------------------------------------------------------------
 // Each rank owns one area (layout: tp_exchange.h).  A rank PUSHES its partial vector into its slot of
 // every rank's area with ordinary stores over NVLink and then raises its flag there; the consumer
-// polls flags in its OWN memory only (decode_layer.cu, model.cu).  All ranks must barrier (on the host)
+// re-reads slots in its OWN memory only (gemv_q4k_fast.cu, model.cu).  All ranks must barrier (on the host)
 // between the last decode call and dp_tp_destroy / dp_ctx_destroy: a slower peer may still be pushing
 // into this rank's area.
 extern "C" dp_status dp_tp_ipc_export(dp_ctx *ctx, void *out64) {
@@ -236,23 +236,6 @@ bool dp_tp_exchange_view(dp_ctx *ctx, int *rank, int *size, uint2 **areas) {
   *rank = ctx->tp->rank; *size = ctx->tp->size;
   for (int r = 0; r < ctx->tp->size; r++) areas[r] = (uint2 *)ctx->tp->peer[r];
   return true;
-}
-
-// A context without a group: a one-rank exchange area in local memory, so that a single GPU runs the same
-// decode kernels (created on first use, freed with the context).
-dp_status dp_tp_local_area(dp_ctx *ctx, uint2 **area) {
-  if (!ctx->local_xd_area) {
-    void *a = nullptr;
-    DP_CUDA(ctx, cudaMalloc(&a, dp_tp_area_bytes()));
-    cudaError_t e = cudaMemset(a, 0, dp_tp_area_bytes());
-    if (e != cudaSuccess) {
-      cudaFree(a);
-      return dp_fail(ctx, DP_ERR_CUDA, "local exchange area: %s", cudaGetErrorString(e));
-    }
-    ctx->local_xd_area = a;
-  }
-  *area = (uint2 *)ctx->local_xd_area;
-  return DP_OK;
 }
 
 // (kept for the status path: nothing to reset, tickets only ever grow)

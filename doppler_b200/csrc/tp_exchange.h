@@ -1,5 +1,5 @@
 // Layout of the peer-memory exchange area (tp.cu) used by the decode-step kernels
-// (decode_layer.cu, model.cu).  No counterpart in the reference, which has no collective backend.
+// (gemv_q4k_fast.cu, model.cu; helpers in handoff.cuh).  No counterpart in the reference, which has no collective backend.
 //
 // Every rank owns one area in its own HBM, mapped into every other rank with CUDA IPC.  A rank PUSHES
 // its data into its own slot of every rank's area with ordinary stores over NVLink; a consumer reads

@@ -47,7 +47,7 @@ print("ok")
 
 
 @pytest.mark.parametrize("env", [
-    {"DP_GEMV_VARIANT": "0"}, {"DP_DECODE_PERSISTENT": "1"}, {"DP_ATTN_TC": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_TC": "0"}, {"DP_PREFILL_TC": "0"},
+    {"DP_GEMV_VARIANT": "0"}, {"DP_ATTN_TC": "0"}, {"DP_PDL": "0"}, {"DP_GEMM_TC": "0"}, {"DP_PREFILL_TC": "0"},
 ], ids=lambda e: ",".join(f"{k}={v}" for k, v in e.items()))
 def test_alternative_kernels_stay_correct(tmp_path, env):
     script = tmp_path / "child.py"
