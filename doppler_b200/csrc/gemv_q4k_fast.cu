@@ -260,7 +260,9 @@ struct GemvSource {
 
 // GROUPS consumer groups of eight warps each; consecutive row tiles alternate between the groups, so
 // while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
-template <typename OutT, int GROUPS, int SRC>
+// PUSH: the epilogue pushes the rows into the exchange areas (GemvExchange); instantiated only for the
+// tensor-parallel launches, so the other instantiations carry none of that code.
+template <typename OutT, int GROUPS, int SRC, bool PUSH = false>
 __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
@@ -371,37 +373,79 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
         }
       }
     } else if constexpr (SRC == SRC_SILU) {
-      for (int b = cw; b < bpr; b += NW) {
+      // two blocks per round: the second block's loads are in flight while the first is converted
+      for (int b = cw; b < bpr; b += 2 * NW) {
+        const int b2 = b + NW;
+        const bool two = b2 < bpr;
         const float *gp = gs.x + 2 * (b * QK_K + lane * 8), *up = gp + 8;  // gate|up interleaved in groups of eight
+        const float *gq = gs.x + 2 * ((two ? b2 : b) * QK_K + lane * 8), *uq = gq + 8;
         const float4 g0 = *reinterpret_cast<const float4 *>(gp), g1 = *reinterpret_cast<const float4 *>(gp + 4);
         const float4 u0 = *reinterpret_cast<const float4 *>(up), u1 = *reinterpret_cast<const float4 *>(up + 4);
-        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-        float o[8];
+        const float4 h0 = *reinterpret_cast<const float4 *>(gq), h1 = *reinterpret_cast<const float4 *>(gq + 4);
+        const float4 w0 = *reinterpret_cast<const float4 *>(uq), w1 = *reinterpret_cast<const float4 *>(uq + 4);
+        {
+          const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+          float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const float cl = fminf(fmaxf(g[j], -15.0f), 15.0f);
-          o[j] = (g[j] * (1.0f / (1.0f + expf(-cl)))) * u[j];
+          for (int j = 0; j < 8; j++) {
+            const float cl = fminf(fmaxf(g[j], -15.0f), 15.0f);
+            o[j] = (g[j] * (1.0f / (1.0f + expf(-cl)))) * u[j];
+          }
+          actq_emit_block(o, lane, b, bpr, smem);
         }
-        actq_emit_block(o, lane, b, bpr, smem);
+        if (two) {
+          const float g[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w}, u[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const float cl = fminf(fmaxf(g[j], -15.0f), 15.0f);
+            o[j] = (g[j] * (1.0f / (1.0f + expf(-cl)))) * u[j];
+          }
+          actq_emit_block(o, lane, b2, bpr, smem);
+        }
       }
     } else {
       const int D = gs.D, splits = gs.splits;
+      // Fast form (a half-warp's 128 outputs lie in one head, at most 16 splits): lane j of the half-warp fetches
+      // the running max and sum of split j, so all of them arrive in one round trip, and the partial rows are
+      // read four splits at a time.  Same arithmetic, in the same order, as the sequential form below.
+      const bool fast = (D % 128) == 0 && splits <= 16;
       for (int b = cw; b < bpr; b += NW) {
         const int e0 = b * QK_K + lane * 8, h = e0 / D, d0 = e0 % D;
         const float *pp = gs.x + (size_t)h * splits * (D + 2);
         float mm = -3.402823466e+38f;
-        for (int sp = 0; sp < splits; sp++) mm = fmaxf(mm, pp[sp * (D + 2) + D]);
         float ll = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (fast) {
+          const int hl = lane & 15;
+          float m_mine = -3.402823466e+38f, l_mine = 0.0f;
+          if (hl < splits) { m_mine = pp[hl * (D + 2) + D]; l_mine = pp[hl * (D + 2) + D + 1]; }
+          mm = m_mine;
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+          const float c_mine = (m_mine == -3.402823466e+38f) ? 0.0f : exp2f(m_mine - mm);
+#pragma unroll 4
+          for (int sp = 0; sp < splits; sp++) {
+            const float *ps = pp + sp * (D + 2);
+            const float2 a0 = *reinterpret_cast<const float2 *>(ps + d0), a1 = *reinterpret_cast<const float2 *>(ps + d0 + 2);
+            const float2 a2 = *reinterpret_cast<const float2 *>(ps + d0 + 4), a3 = *reinterpret_cast<const float2 *>(ps + d0 + 6);
+            const float c = __shfl_sync(0xffffffffu, c_mine, (lane & 16) + sp);
+            ll = fmaf(__shfl_sync(0xffffffffu, l_mine, (lane & 16) + sp), c, ll);
+            acc[0] = fmaf(a0.x, c, acc[0]); acc[1] = fmaf(a0.y, c, acc[1]); acc[2] = fmaf(a1.x, c, acc[2]); acc[3] = fmaf(a1.y, c, acc[3]);
+            acc[4] = fmaf(a2.x, c, acc[4]); acc[5] = fmaf(a2.y, c, acc[5]); acc[6] = fmaf(a3.x, c, acc[6]); acc[7] = fmaf(a3.y, c, acc[7]);
+          }
+        } else {
+          for (int sp = 0; sp < splits; sp++) mm = fmaxf(mm, pp[sp * (D + 2) + D]);
 #pragma unroll 2
-        for (int sp = 0; sp < splits; sp++) {
-          const float *ps = pp + sp * (D + 2);
-          const float ms = ps[D];
-          const float c = (ms == -3.402823466e+38f) ? 0.0f : exp2f(ms - mm);
-          ll = fmaf(ps[D + 1], c, ll);
-          const float2 a0 = *reinterpret_cast<const float2 *>(ps + d0), a1 = *reinterpret_cast<const float2 *>(ps + d0 + 2);
-          const float2 a2 = *reinterpret_cast<const float2 *>(ps + d0 + 4), a3 = *reinterpret_cast<const float2 *>(ps + d0 + 6);
-          acc[0] = fmaf(a0.x, c, acc[0]); acc[1] = fmaf(a0.y, c, acc[1]); acc[2] = fmaf(a1.x, c, acc[2]); acc[3] = fmaf(a1.y, c, acc[3]);
-          acc[4] = fmaf(a2.x, c, acc[4]); acc[5] = fmaf(a2.y, c, acc[5]); acc[6] = fmaf(a3.x, c, acc[6]); acc[7] = fmaf(a3.y, c, acc[7]);
+          for (int sp = 0; sp < splits; sp++) {
+            const float *ps = pp + sp * (D + 2);
+            const float ms = ps[D];
+            const float c = (ms == -3.402823466e+38f) ? 0.0f : exp2f(ms - mm);
+            ll = fmaf(ps[D + 1], c, ll);
+            const float2 a0 = *reinterpret_cast<const float2 *>(ps + d0), a1 = *reinterpret_cast<const float2 *>(ps + d0 + 2);
+            const float2 a2 = *reinterpret_cast<const float2 *>(ps + d0 + 4), a3 = *reinterpret_cast<const float2 *>(ps + d0 + 6);
+            acc[0] = fmaf(a0.x, c, acc[0]); acc[1] = fmaf(a0.y, c, acc[1]); acc[2] = fmaf(a1.x, c, acc[2]); acc[3] = fmaf(a1.y, c, acc[3]);
+            acc[4] = fmaf(a2.x, c, acc[4]); acc[5] = fmaf(a2.y, c, acc[5]); acc[6] = fmaf(a3.x, c, acc[6]); acc[7] = fmaf(a3.y, c, acc[7]);
+          }
         }
         float o[8];
 #pragma unroll
@@ -545,7 +589,7 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
           for (int w = 0; w < TG_CONSUMERS; w++) v += rs[w * 16 + lane];
           const int row = rt * 16 + lane;
           v *= alpha;
-          if (gx.push) {  // this rank's partial of the row, with the exchange's ticket, into its slot on every rank
+          if constexpr (PUSH) {  // this rank's partial of the row, with the exchange's ticket, into its slot on every rank
             const unsigned ticket = *reinterpret_cast<const volatile unsigned *>(gx.ticket_step) * gx.ticket_stride + 1u + gx.ticket_out;
             const size_t off = dp_tp_slot_offset((unsigned)gx.parity_out, gx.rank) + (size_t)row;
 #pragma unroll
@@ -581,7 +625,7 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   return true;
 }
 
-template <typename OutT, int GROUPS, int SRC>
+template <typename OutT, int GROUPS, int SRC, bool PUSH = false>
 static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
                             uint32_t smem, float alpha, const float *residual, const GemvSource &gs, const GemvExchange &gx = GemvExchange()) {
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
@@ -589,10 +633,10 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
             N, K, cb, stages, alpha, residual, ctx->dev_status, gs, gx);
   return DP_OK;
 }
@@ -636,11 +680,10 @@ dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const 
   if (gxp) {
     const GemvExchange &gx = *gxp;
     if ((mode == SRC_XCHG_RMSNORM && K > DP_TP_SLOT_FLOATS) || (gx.push && N > DP_TP_SLOT_FLOATS)) return DP_OK;
-    if (mode == SRC_XCHG_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
-    else if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
-    else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
-    else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
-    else return DP_OK;
+    if (mode == SRC_XCHG_RMSNORM && !gx.push) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_SILU && gx.push) DP_TRY((launch_tma<float, 2, SRC_SILU, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_COMBINE && gx.push) DP_TRY((launch_tma<float, 2, SRC_COMBINE, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else return DP_OK;  // (the schedule uses exactly these three)
     *handled = true;
     return DP_OK;
   }
