@@ -384,8 +384,15 @@ dp_status dpk_attention_split_only(dp_ctx *ctx, const dpk_attn_params &p, float 
   return attention_impl(ctx, p, scratch, splits, false);
 }
 
+// query-tiled causal prefill kernel (attention_prefill.cu)
+bool dpk_attention_prefill_eligible(const dpk_attn_params &p);
+dp_status dpk_attention_prefill(dp_ctx *ctx, const dpk_attn_params &p);
+
 static dp_status attention_impl(dp_ctx *ctx, const dpk_attn_params &p, float *scratch, int splits, bool combine) {
   int gt = 1;
+  // several causal query rows: one CTA per tile of query positions shares each K / V tile (DP_ATTN_TC=0: off)
+  static const int tc_mode = [] { const char *e = getenv("DP_ATTN_TC"); return e ? atoi(e) : 1; }();
+  if (tc_mode && combine && dpk_attention_prefill_eligible(p)) return dpk_attention_prefill(ctx, p);
   if (use_tc(ctx, p, &gt)) {
     DP_TRY(dpk_attention_tc_split(ctx, p, scratch, splits));
   } else if (fast_shape(p, &gt)) {

@@ -41,6 +41,7 @@ struct dp_ctx {
   dp_buf argmax_scratch = nullptr;
   dp_buf gemv_scratch = nullptr;  // quantised activation digits of the fast GEMV (stream ordered)
   dp_buf gemm_scratch = nullptr;  // f16 activations (halves, residues, row scales) of the tensor-core GEMM (stream ordered)
+  dp_buf gemm_split_scratch = nullptr;  // partial output tiles of a K-split tensor-core GEMM (stream ordered)
   bool pdl = false;  // launch with programmatic dependent launch (set while the decode step is recorded)
   int *dev_status = nullptr;  // device word raised by a kernel whose bounded wait gave up
   dp_recorder *active_recorder = nullptr;

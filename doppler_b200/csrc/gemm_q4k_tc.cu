@@ -33,7 +33,7 @@
 
 namespace {
 
-constexpr int BM = 256, BK = 64;
+constexpr int BK = 64;
 // The activation ring (filled by TMA) and the weight ring (filled by the dequant warps) have their own
 // depths and barriers: weight stages are smaller, so more of them fit, and the dequant warps can run
 // further ahead of the tensor core than the TMA needs to.
@@ -130,28 +130,34 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 struct TcAlpha {
   float value;
   const float *row_scale;
-  int weight_residue;  // 1: the B tile holds w - f16(w), the part of each weight that f16 rounding drops
-  int accumulate;      // 1: the epilogue adds to C instead of overwriting it (f32 output only)
+  int k_splits;  // one-SM kernel: parts of K per output tile (grid.z); part z writes its f32 sums to C + z * M * N
 };
 
-// two dequantised weights as f16, or their f16 rounding residues
-__device__ __forceinline__ __half2 tc_pack_weights(float a, float b, int residue) {
-  __half2 h = __floats2half2_rn(a, b);
-  if (residue) {
-    const float2 f = __half22float2(h);
-    h = __floats2half2_rn(a - f.x, b - f.y);
-  }
-  return h;
+// Two dequantised weights as f16, and (NPROD >= 2) their f16 rounding residues w - f16(w): the part of each
+// weight that the rounding drops, which a second product adds back.
+__device__ __forceinline__ uint32_t tc_pack_hi(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t tc_pack_lo(float a, float b, uint32_t hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+  const __half2 h = __floats2half2_rn(a - f.x, b - f.y);
+  return *reinterpret_cast<const uint32_t *>(&h);
 }
 
 struct TcSmem {
   uint32_t a, b, bars, tmem_slot, abort_flag, total;
   uint32_t stage_a, stage_b;
 };
-__host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) {
-  TcSmem l;
-  l.stage_a = (uint32_t)MT * 128u * 128u;  // MT 128-row tiles of 64 f16
-  l.stage_b = (uint32_t)BN * 128u;
+// NPROD = products per K step that go into the one f32 accumulator:
+//   1  A . f16(W)                                   (weights rounded to f16: the opt-in tiled kernel's numerics)
+//   2  A . f16(W) + A . (W - f16(W))                (f16 activations, weights to f32 accuracy)
+//   3  A_hi . f16(W) + A_hi . (W - f16(W)) + A_lo . f16(W)   (f32 activations as two f16 halves: the f32-exact product)
+// A weight stage then holds the f16 tile and the residue tile, an activation stage the hi and the lo tiles.
+__host__ __device__ constexpr inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2, int NPROD = 1) {
+  TcSmem l{};
+  l.stage_a = (uint32_t)MT * 128u * 128u * (NPROD == 3 ? 2u : 1u);  // MT 128-row tiles of 64 f16 (x2: hi and lo halves)
+  l.stage_b = (uint32_t)BN * 128u * (NPROD >= 2 ? 2u : 1u);
   l.a = 0;
   l.b = (uint32_t)SA * l.stage_a;
   l.bars = l.b + (uint32_t)SB * l.stage_b;  // full_a[SA], full_b[SB], done[max(SA, SB)], accum
@@ -162,19 +168,27 @@ __host__ __device__ inline TcSmem tc_layout(int BN, int SA, int SB, int MT = 2) 
 }
 
 // MT = number of 128-row accumulators per CTA (output tile 128*MT x BN).
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, int MT = 2>
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, int MT = 2, int NPROD = 1>
 __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                    const __grid_constant__ CUtensorMap tmap_a_lo,
                                                                     const uint8_t *__restrict__ W, OutT *__restrict__ C, int M,
                                                                     int N, int K, TcAlpha alpha, int *__restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(BN, SA, SB, MT);
+  const TcSmem L = tc_layout(BN, SA, SB, MT, NPROD);
   static_assert(MT * BN <= 512, "accumulators exceed tensor memory");
+  constexpr uint32_t A_TILES = (uint32_t)MT * 128u * 128u;  // bytes of the hi (or only) activation tiles of a stage
+  constexpr uint32_t B_TILE = (uint32_t)BN * 128u;          // bytes of the f16 weight tile of a stage
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
+  // Split over K (grid.z parts, whole super-blocks each): a problem of few tiles (N = 4096 at M <= 256 is 32)
+  // fills the GPU with several CTAs per tile.  Every part writes its own f32 tile; a second kernel adds the
+  // parts in a fixed order, so the result does not depend on which CTA finishes first.
+  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
   const int bpr_row = K / QK_K;                       // super-blocks per weight row
-  const int bpr = bpr_row, kb0 = 0;
+  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;  // this CTA's share
   const int num_k = bpr * (QK_K / BK);
+  if (k_splits > 1) C += (size_t)blockIdx.z * (size_t)M * (size_t)N;
   // Every CTA walks K in its own rotation (by whole super-blocks).  All CTAs of a grid row need the same
   // activation tiles; in lockstep they would all ask the same few L2 lines for them at the same time, and
   // the L2 slices holding those lines, not the tensor pipe, would set the pace of every K step.
@@ -222,8 +236,11 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         mbar_expect_tx(full_a(s), L.stage_a);
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+        for (int mt = 0; mt < MT; mt++) {
           tma_load_2d(dst + (uint32_t)mt * 128u * 128u, &tmap_a, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + 128 * mt, full_a(s));
+          if constexpr (NPROD == 3)
+            tma_load_2d(dst + A_TILES + (uint32_t)mt * 128u * 128u, &tmap_a_lo, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + 128 * mt, full_a(s));
+        }
       }
     }
   } else if (warp == 1) {
@@ -243,8 +260,13 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
           const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
 #pragma unroll
-          for (int mt = 0; mt < MT; mt++)
-            umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+          for (int mt = 0; mt < MT; mt++) {
+            const uint64_t adesc = umma_desc_sw128(a_addr + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u);
+            umma_f16(tmem_base + (uint32_t)(mt * BN), adesc, bdesc, idesc, acc);
+            if constexpr (NPROD >= 2) umma_f16(tmem_base + (uint32_t)(mt * BN), adesc, umma_desc_sw128(b_addr + B_TILE + (uint32_t)k16 * 32u), idesc, 1u);
+            if constexpr (NPROD == 3)
+              umma_f16(tmem_base + (uint32_t)(mt * BN), umma_desc_sw128(a_addr + A_TILES + (uint32_t)mt * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, 1u);
+          }
         }
         // both stages are free once these MMAs have read them
         umma_commit(done(kt % SD));
@@ -331,7 +353,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
           const float s_lo = __shfl_sync(0xffffffffu, my_sc0[j], src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1[j], src_lane);
           const float m_lo = __shfl_sync(0xffffffffu, my_mn0[j], src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1[j], src_lane);
           // nibble -> f32 without the conversion pipe: PRMT builds the float 2^23 + q from a byte
-          uint32_t lo[4], hi[4];
+          uint32_t lo[4], hi[4], rlo[4], rhi[4];
+          (void)rlo; (void)rhi;
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             const uint32_t word = i < 2 ? q.x : q.y;
@@ -341,16 +364,21 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
             const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
             const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
-            const __half2 l2 = tc_pack_weights(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo), alpha.weight_residue);
-            const __half2 h2 = tc_pack_weights(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi), alpha.weight_residue);
-            lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
-            hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+            const float wl0 = __fmaf_rn(s_lo, ql0, -m_lo), wl1 = __fmaf_rn(s_lo, ql1, -m_lo);
+            const float wh0 = __fmaf_rn(s_hi, qh0, -m_hi), wh1 = __fmaf_rn(s_hi, qh1, -m_hi);
+            lo[i] = tc_pack_hi(wl0, wl1);
+            hi[i] = tc_pack_hi(wh0, wh1);
+            if constexpr (NPROD >= 2) { rlo[i] = tc_pack_lo(wl0, wl1, lo[i]); rhi[i] = tc_pack_lo(wh0, wh1, hi[i]); }
           }
           // row r of an 8-row group: 16-byte chunk c lives at chunk (c ^ r) of the 128-byte line
           uint8_t *line = bt + (uint32_t)(grp0 + dw + j * DQ_WARPS) * 1024u + (uint32_t)r8 * 128u;
           const uint32_t off_lo = ((uint32_t)oct ^ (uint32_t)r8) << 4, off_hi = ((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4;
           *reinterpret_cast<uint4 *>(line + off_lo) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
           *reinterpret_cast<uint4 *>(line + off_hi) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if constexpr (NPROD >= 2) {  // the residue tile, same layout, behind the f16 tile
+            *reinterpret_cast<uint4 *>(line + B_TILE + off_lo) = make_uint4(rlo[0], rlo[1], rlo[2], rlo[3]);
+            *reinterpret_cast<uint4 *>(line + B_TILE + off_hi) = make_uint4(rhi[0], rhi[1], rhi[2], rhi[3]);
+          }
         }
         if constexpr (!BLOCK_SYNC) {
           // generic-proxy stores -> visible to the tensor core
@@ -375,7 +403,8 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
     if (go) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
       constexpr int ET = DQ_WARPS * 32;  // epilogue threads
-      static_assert(128 * (BN * (int)sizeof(OutT) + 16) <= MT * 128 * 128 * SA + BN * 128 * SB, "the output tile of a pass must fit the idle operand rings");
+      static_assert(128 * (BN * (int)sizeof(OutT) + 16) <= MT * 128 * 128 * SA * (NPROD == 3 ? 2 : 1) + BN * 128 * SB * (NPROD >= 2 ? 2 : 1),
+                    "the output tile of a pass must fit the idle operand rings");
       const int quad = warp & 3;         // the 32 TMEM lanes this warp may read
       const int half = dw >> 2;          // DQ_WARPS/4 warps share a quarter and split the column groups
       constexpr int GROUPS = BN / 32;
@@ -425,13 +454,6 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             if (row0 + lrow >= M) break;  // rows grow with c
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
-            if constexpr (sizeof(OutT) == 4) {
-              if (alpha.accumulate) {
-                const float4 old = *reinterpret_cast<const float4 *>(g);
-                v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
-                v.z = __float_as_uint(__uint_as_float(v.z) + old.z), v.w = __float_as_uint(__uint_as_float(v.w) + old.w);
-              }
-            }
             *reinterpret_cast<uint4 *>(g) = v;
           }
         }
@@ -481,8 +503,9 @@ __device__ __forceinline__ void tma_load_2d_2sm(uint32_t dst, const CUtensorMap 
 // 74 clusters of a B200 cover N = 12288 in one even wave, where uniform 256-wide tiles fill only 48.
 // PS = passes: 256-row MMAs per pair tile (output tile 256*PS x bn).  One pass halves the activation bytes
 // per stage, which buys twice as many stages for the same shared memory.
-template <int BNMAX, typename OutT, int SA, int SB, int CH, int PS>
-__global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ W,
+template <int BNMAX, typename OutT, int SA, int SB, int CH, int PS, int NPROD = 1>
+__global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                  const __grid_constant__ CUtensorMap tmap_a_lo, const uint8_t *__restrict__ W,
                                                                   OutT *__restrict__ C, int M, int N, int K, TcAlpha alpha,
                                                                   int *__restrict__ err, int wide_tiles, int bn_wide, int bn_narrow) {
   constexpr int HBMAX = BNMAX / 2, DQ_WARPS = HBMAX / 8;  // warps 2 .. 2+DQ_WARPS-1: one 8-row group of weights each, then the epilogue
@@ -494,7 +517,9 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
   const int hb = bn / 2, dq = hb / 8;                            // this CTA's weight rows, its active dequant warps
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const TcSmem L = tc_layout(HBMAX, SA, SB, PS);
+  const TcSmem L = tc_layout(HBMAX, SA, SB, PS, NPROD);
+  constexpr uint32_t A_TILES = (uint32_t)PS * 128u * 128u;  // bytes of the hi (or only) activation tiles of a stage
+  constexpr uint32_t B_TILE = (uint32_t)HBMAX * 128u;       // bytes of this CTA's half of the f16 weight tile of a stage
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_ctarank();
   const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
@@ -545,8 +570,11 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
         const uint32_t dst = smem_u32(smem + L.a + (uint32_t)s * L.stage_a);
         const uint32_t bar0 = mapa_shared(full_a(s), 0u);
 #pragma unroll
-        for (int ps = 0; ps < PS; ps++)
+        for (int ps = 0; ps < PS; ps++) {
           tma_load_2d_2sm(dst + (uint32_t)ps * 128u * 128u, &tmap_a, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
+          if constexpr (NPROD == 3)
+            tma_load_2d_2sm(dst + A_TILES + (uint32_t)ps * 128u * 128u, &tmap_a_lo, ((kb0 + ((kt >> 2) + rot_b) % bpr) * 4 + (kt & 3)) * BK, m0 + ps * 256 + (int)rank * 128, bar0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -575,8 +603,13 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
           const uint64_t bdesc = umma_desc_sw128(b_addr + (uint32_t)k16 * 32u);
           const uint32_t acc = (kt > 0 || k16 > 0) ? 1u : 0u;
 #pragma unroll
-          for (int ps = 0; ps < PS; ps++)
-            umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, acc);
+          for (int ps = 0; ps < PS; ps++) {
+            const uint64_t adesc = umma_desc_sw128(a_addr + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u);
+            umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), adesc, bdesc, idesc, acc);
+            if constexpr (NPROD >= 2) umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), adesc, umma_desc_sw128(b_addr + B_TILE + (uint32_t)k16 * 32u), idesc, 1u);
+            if constexpr (NPROD == 3)
+              umma_f16_2sm(tmem_base + (uint32_t)(ps * BNMAX), umma_desc_sw128(a_addr + A_TILES + (uint32_t)ps * 128u * 128u + (uint32_t)k16 * 32u), bdesc, idesc, 1u);
+          }
         }
         umma_commit_2sm(done(kt % SD));  // arrives on both CTAs' barrier: their stages of this step are free
       }
@@ -632,7 +665,8 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
           const float s_lo = __shfl_sync(0xffffffffu, my_sc0, src_lane), s_hi = __shfl_sync(0xffffffffu, my_sc1, src_lane);
           const float m_lo = __shfl_sync(0xffffffffu, my_mn0, src_lane), m_hi = __shfl_sync(0xffffffffu, my_mn1, src_lane);
           const uint2 q = qcur[chunk];
-          uint32_t lo[4], hi[4];
+          uint32_t lo[4], hi[4], rlo[4], rhi[4];
+          (void)rlo; (void)rhi;
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             const uint32_t word = i < 2 ? q.x : q.y;
@@ -642,14 +676,19 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             const float ql1 = __uint_as_float(__byte_perm(wl, 0x4B000000u, sel1)) - 8388608.0f;
             const float qh0 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel0)) - 8388608.0f;
             const float qh1 = __uint_as_float(__byte_perm(wh, 0x4B000000u, sel1)) - 8388608.0f;
-            const __half2 l2 = tc_pack_weights(__fmaf_rn(s_lo, ql0, -m_lo), __fmaf_rn(s_lo, ql1, -m_lo), alpha.weight_residue);
-            const __half2 h2 = tc_pack_weights(__fmaf_rn(s_hi, qh0, -m_hi), __fmaf_rn(s_hi, qh1, -m_hi), alpha.weight_residue);
-            lo[i] = *reinterpret_cast<const uint32_t *>(&l2);
-            hi[i] = *reinterpret_cast<const uint32_t *>(&h2);
+            const float wl0 = __fmaf_rn(s_lo, ql0, -m_lo), wl1 = __fmaf_rn(s_lo, ql1, -m_lo);
+            const float wh0 = __fmaf_rn(s_hi, qh0, -m_hi), wh1 = __fmaf_rn(s_hi, qh1, -m_hi);
+            lo[i] = tc_pack_hi(wl0, wl1);
+            hi[i] = tc_pack_hi(wh0, wh1);
+            if constexpr (NPROD >= 2) { rlo[i] = tc_pack_lo(wl0, wl1, lo[i]); rhi[i] = tc_pack_lo(wh0, wh1, hi[i]); }
           }
           uint8_t *line = smem + L.b + (uint32_t)s * L.stage_b + (uint32_t)dw * 1024u + (uint32_t)r8 * 128u;
           *reinterpret_cast<uint4 *>(line + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
           *reinterpret_cast<uint4 *>(line + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if constexpr (NPROD >= 2) {  // the residue tile, same layout, behind this CTA's half of the f16 tile
+            *reinterpret_cast<uint4 *>(line + B_TILE + (((uint32_t)oct ^ (uint32_t)r8) << 4)) = make_uint4(rlo[0], rlo[1], rlo[2], rlo[3]);
+            *reinterpret_cast<uint4 *>(line + B_TILE + (((uint32_t)(oct + 4) ^ (uint32_t)r8) << 4)) = make_uint4(rhi[0], rhi[1], rhi[2], rhi[3]);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this CTA's stores -> visible to the tensor cores
         __syncwarp();
@@ -670,7 +709,8 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
     if (go) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
       constexpr int ET = DQ_WARPS * 32;  // epilogue threads
-      static_assert(128 * (BNMAX * (int)sizeof(OutT) + 16) <= PS * 128 * 128 * SA + HBMAX * 128 * SB, "the output tile of a pass must fit the idle operand rings");
+      static_assert(128 * (BNMAX * (int)sizeof(OutT) + 16) <= PS * 128 * 128 * SA * (NPROD == 3 ? 2 : 1) + HBMAX * 128 * SB * (NPROD >= 2 ? 2 : 1),
+                    "the output tile of a pass must fit the idle operand rings");
       const int quad = warp & 3, set = dw >> 2;  // DQ_WARPS / 4 sets of four warps share the 16-column groups
       const int groups = bn / 16;
       const uint32_t row_bytes = (uint32_t)bn * (uint32_t)sizeof(OutT), row_pitch = row_bytes + 16u;
@@ -719,13 +759,6 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             if (row0 + lrow >= M) break;  // rows grow with c
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
             char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
-            if constexpr (sizeof(OutT) == 4) {
-              if (alpha.accumulate) {
-                const float4 old = *reinterpret_cast<const float4 *>(g);
-                v.x = __float_as_uint(__uint_as_float(v.x) + old.x), v.y = __float_as_uint(__uint_as_float(v.y) + old.y);
-                v.z = __float_as_uint(__uint_as_float(v.z) + old.z), v.w = __float_as_uint(__uint_as_float(v.w) + old.w);
-              }
-            }
             *reinterpret_cast<uint4 *>(g) = v;
           }
         }
@@ -799,23 +832,33 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
-template <int BN, int DQ_WARPS, typename OutT, int SA, int SB>
-dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
-  const size_t smem = tc_layout(BN, SA, SB).total + 1024;
-  static_assert(2 * 128 * 128 * SA + BN * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  DP_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(N / BN, (M + BM - 1) / BM, 1);
-  DP_LAUNCH(ctx, (gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB>), grid, (DQ_WARPS + 2) * 32, smem, tm, W, C, M, N, K, alpha, ctx->dev_status);
+template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, int MT, int NPROD>
+dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const CUtensorMap &tm_lo, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
+  constexpr size_t smem = tc_layout(BN, SA, SB, MT, NPROD).total + 1024;
+  static_assert(smem <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc_kernel<BN, DQ_WARPS, OutT, SA, SB, MT, NPROD>;
+  DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(N / BN, (M + 128 * MT - 1) / (128 * MT), alpha.k_splits > 1 ? alpha.k_splits : 1);
+  DP_LAUNCH(ctx, kernel, grid, (DQ_WARPS + 2) * 32, smem, tm, tm_lo, W, C, M, N, K, alpha, ctx->dev_status);
   return DP_OK;
 }
 
-// two-SM MMA variant: clusters of two CTAs along x, 512 x 192 tiles
-template <typename OutT, int BNMAX, int SA, int SB, int CH = 2, int PS = 2>
-dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha,
+// parts of K per output tile for a one-SM launch of `tiles` CTAs: as many as fill the GPU, whole super-blocks, four or more each
+static int tc_k_splits(dp_ctx *ctx, int tiles, int K) {
+  const int bpr = K / QK_K;
+  int best = 1;
+  for (int sp = 2; sp <= 8; sp++)
+    if (tiles * sp <= ctx->sm_count && bpr % sp == 0 && bpr / sp >= 4) best = sp;
+  return best;
+}
+
+// two-SM MMA variant: clusters of two CTAs along x, pair tiles of 256 * PS rows
+template <typename OutT, int BNMAX, int SA, int SB, int CH, int PS, int NPROD>
+dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const CUtensorMap &tm_lo, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha,
                         int tiles, int wide_tiles, int bn_wide, int bn_narrow) {
-  const size_t smem = tc_layout(BNMAX / 2, SA, SB, PS).total + 1024;
-  static_assert(PS * 128 * 128 * SA + (BNMAX / 2) * 128 * SB + 2048 <= 227 * 1024, "rings exceed shared memory");
-  auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS>;
+  constexpr size_t smem = tc_layout(BNMAX / 2, SA, SB, PS, NPROD).total + 1024;
+  static_assert(smem <= 227 * 1024, "rings exceed shared memory");
+  auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS, NPROD>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), 1);
@@ -829,14 +872,19 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const uint8_t *W, Ou
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, W, C, M, N, K, alpha, ctx->dev_status, wide_tiles, bn_wide, bn_narrow);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm, tm_lo, W, C, M, N, K, alpha, ctx->dev_status, wide_tiles, bn_wide, bn_narrow);
   ctx->launches++;
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return dp_fail(ctx, DP_ERR_CUDA, "launch of gemm_q4k_tc2_kernel failed: %s", cudaGetErrorString(e));
   return DP_OK;
 }
-template <typename OutT>
-dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
+
+// Ring depths per number of products (a stage grows with the products, shared memory does not):
+//   two-SM, tiles up to 192 wide:  1: 4 + 8 (four K steps per synchronisation)   2: 3 + 4   3: 2 + 4
+//   two-SM, tiles up to 256 wide:  1: 3 + 4   2: 3 + 4   3: 2 + 3 (one K step per synchronisation)
+//   one-SM, 192 / 128 wide:        1: 3 + 3   2: 3 + 2 / 3 + 3   3: 2 + 2 / 2 + 3
+template <typename OutT, int NPROD>
+dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const CUtensorMap &tm_lo, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   // Two-SM kernel (tcgen05.mma.cta_group::2) for M > 256.  On 512 x 256 pair tiles its 256-wide MMAs fetch
   // 8 KB of operands per SM and 128 cycles instead of 10 KB per 96, and the tensor pipe runs about 1.3x
   // faster per SM.  It needs whole waves of 74 clusters to win (at M = 512, 48 uniform tiles of 256 columns
@@ -855,43 +903,68 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const uint8_t 
       const int narrow = (N / 16 / cols) * 16;
       const int n_wide = (N - cols * narrow) / 16;  // cols * narrow + 16 * n_wide == N, n_wide < cols
       const int wide = narrow + 16, widest = n_wide ? wide : narrow;
-      // activation ring of four, weight ring of two whole super-blocks (four K steps per synchronisation)
-      if (narrow >= 128 && widest <= 192) return launch_tc_2sm<OutT, 192, 4, 8, 4>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
-      if (narrow >= 128 && widest <= 256) return launch_tc_2sm<OutT, 256, 3, 4, 2>(ctx, tm, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      if (narrow >= 128 && widest <= 192) {
+        if constexpr (NPROD == 1) return launch_tc_2sm<OutT, 192, 4, 8, 4, 2, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        else if constexpr (NPROD == 2) return launch_tc_2sm<OutT, 192, 3, 4, 2, 2, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        else return launch_tc_2sm<OutT, 192, 2, 4, 2, 2, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      }
+      if (narrow >= 128 && widest <= 256) {
+        if constexpr (NPROD == 1) return launch_tc_2sm<OutT, 256, 3, 4, 2, 2, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        else if constexpr (NPROD == 2) return launch_tc_2sm<OutT, 256, 3, 4, 2, 2, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+        else return launch_tc_2sm<OutT, 256, 2, 3, 1, 2, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, n_wide, wide, narrow);
+      }
     }
   }
-  // one-SM kernel, equal ring depths (3 + 3 measured fastest on 512 x 12288 x 4096)
-  if (bn == 192) return launch_tc<192, 12, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
-  return launch_tc<128, 8, OutT, 3, 3>(ctx, tm, W, C, M, N, K, alpha);
+  // one-SM kernel; up to 128 rows (batched decode steps) one 128-row accumulator per CTA, else two
+  if (M <= 128) {
+    if constexpr (NPROD == 1) {
+      if (bn == 192) return launch_tc<192, 12, OutT, 4, 4, 1, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+      return launch_tc<128, 8, OutT, 4, 4, 1, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    } else if constexpr (NPROD == 2) {
+      if (bn == 192) return launch_tc<192, 12, OutT, 4, 3, 1, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+      return launch_tc<128, 8, OutT, 4, 4, 1, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    } else {
+      if (bn == 192) return launch_tc<192, 12, OutT, 3, 2, 1, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+      return launch_tc<128, 8, OutT, 3, 3, 1, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    }
+  }
+  if constexpr (NPROD == 1) {
+    if (bn == 192) return launch_tc<192, 12, OutT, 3, 3, 2, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    return launch_tc<128, 8, OutT, 3, 3, 2, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+  } else if constexpr (NPROD == 2) {
+    if (bn == 192) return launch_tc<192, 12, OutT, 3, 2, 2, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    return launch_tc<128, 8, OutT, 3, 3, 2, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+  } else {
+    if (bn == 192) return launch_tc<192, 12, OutT, 2, 2, 2, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+    return launch_tc<128, 8, OutT, 2, 3, 2, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha);
+  }
 }
 
 }  // namespace
 
-// C (f16) = f16(alpha-scaled f32 sums), the rounding the reference's f16-output kernels apply at the store
-// (fused_matmul_q4_batched_f16a.wgsl:151)
-__global__ void cast_f32_f16_out_kernel(const float *__restrict__ in, __half *__restrict__ out, size_t n) {
+// C = sum of the `splits` partial tiles of a K-split launch, added in a fixed order
+__global__ void splitk_reduce_kernel(const float *__restrict__ parts, float *__restrict__ C, size_t n, int splits) {
   pdl_launch();
   pdl_wait();
   for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
-    if (i + 4 <= n) {
-      const float4 v = *reinterpret_cast<const float4 *>(in + i);
-      const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-      *reinterpret_cast<uint2 *>(out + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
-    } else {
-      for (size_t j = i; j < n; j++) out[j] = __float2half_rn(in[j]);
+    float4 acc = *reinterpret_cast<const float4 *>(parts + i);
+    for (int z = 1; z < splits; z++) {
+      const float4 v = *reinterpret_cast<const float4 *>(parts + (size_t)z * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    *reinterpret_cast<float4 *>(C + i) = acc;
   }
 }
 
 static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
                                   int N, int K, float alpha, int mode, bool *handled) {
-  // mode 0: A as given (f32 is cast to f16), weights rounded to f16: one product.
-  //      1: f32 rows scaled into f16 range, one product.
-  //      2: as 1, three products A_hi.W_hi + A_lo.W_hi + A_hi.W_lo with the f16 rounding residues of A and W,
-  //         which restores the f32-exact product to about 2^-21 of each term (f32 output only).
+  // mode 0: A as given (f32 is cast to f16), weights rounded to f16: one product per K step.
+  //      1: f32 rows scaled into f16 range, weights rounded to f16: one product.
+  //      2: as 1, three products per K step into the one accumulator, A_hi.W_hi + A_hi.W_lo + A_lo.W_hi with the f16
+  //         rounding residues of A and W: the f32-exact product to about 2^-21 of each term (f32 output only).
   //      3: f16 A, two products A.W_hi + A.W_lo: the product with weights kept to f32 accuracy (what the
   //         reference's rule-selected kernel for f16 activations computes, fused_matmul_q4_batched_f16a.wgsl:107);
-  //         an f16 output is rounded once, from the f32 sum.
+  //         an f16 output is rounded once, from the f32 accumulator.
   const bool row_scaled = mode == 1 || mode == 2;
   *handled = false;
   static int enabled = -1;
@@ -907,11 +980,9 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   if (mode == 3 && a_dtype != DP_F16) return DP_OK;
 
   const __half *a16 = (const __half *)A;
-  // The f16 copies of f32 activations (and the f32 sums of a two-product f16 output) live in one scratch
-  // allocation of the context, reused in stream order.
+  // The f16 copies of f32 activations live in one scratch allocation of the context, reused in stream order.
   const __half *a_lo = nullptr;
   const float *scales = nullptr;
-  float *c32 = nullptr;  // mode 3 with f16 output: the two products are summed here first
   if (a_dtype == DP_F32) {
     if (mode == 2 && c_dtype != DP_F32) return DP_OK;
     const size_t a_bytes = ((size_t)M * K * 2 + 255) / 256 * 256;
@@ -930,46 +1001,46 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
     }
   } else if (a_dtype != DP_F16) {
     return DP_OK;
-  } else if (mode == 3 && c_dtype == DP_F16) {
-    DP_TRY(dp_scratch(ctx, &ctx->gemm_scratch, (size_t)M * N * 4, "matmul_c_f32"));
-    c32 = (float *)ctx->gemm_scratch->dptr;
   }
-  CUtensorMap tm;
+  CUtensorMap tm, tm_lo;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {BK, 128};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a16, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  dp_status st = DP_OK;
-  TcAlpha ta = {alpha, scales, 0, 0};
-  CUtensorMap tm_lo;
-  if (r == CUDA_SUCCESS && a_lo)
-    r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)a_lo, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (r == CUDA_SUCCESS)  // (without a lo half the second map is a copy of the first; the kernel then never uses it)
+    r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)(a_lo ? a_lo : a16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  dp_status st = DP_OK;
+  TcAlpha ta = {alpha, scales, 1};
+  // few output tiles (one-SM kernel, f32 output): split K over several CTAs per tile, partial tiles in a scratch
+  // of the context, summed in a fixed order afterwards
+  float *cdst = (float *)C;
+  if (r == CUDA_SUCCESS && c_dtype == DP_F32 && M <= 256 && ((size_t)M * N) % 4 == 0) {
+    const int tiles = (N / bn) * ((M + (M <= 128 ? 127 : 255)) / (M <= 128 ? 128 : 256));
+    const int sp = tc_k_splits(ctx, tiles, K);
+    if (sp > 1) {
+      DP_TRY(dp_scratch(ctx, &ctx->gemm_split_scratch, (size_t)sp * M * N * 4, "matmul_k_split_parts"));
+      ta.k_splits = sp;
+      cdst = (float *)ctx->gemm_split_scratch->dptr;
+    }
+  }
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
-  } else if (c_dtype == DP_F32 || c32) {
-    float *cf = c32 ? c32 : (float *)C;
-    st = dispatch_tc<float>(ctx, bn, tm, W, cf, M, N, K, ta);
-    if (st == DP_OK && a_lo) {
-      ta.accumulate = 1;
-      st = dispatch_tc<float>(ctx, bn, tm_lo, W, cf, M, N, K, ta);  // + A_lo . W_hi
-    }
-    if (st == DP_OK && (a_lo || mode == 3)) {
-      ta.accumulate = 1;
-      ta.weight_residue = 1;
-      st = dispatch_tc<float>(ctx, bn, tm, W, cf, M, N, K, ta);  // + A_hi . W_lo
-    }
-    if (st == DP_OK && c32) {
+  } else if (c_dtype == DP_F32) {
+    if (mode == 2) st = dispatch_tc<float, 3>(ctx, bn, tm, tm_lo, W, cdst, M, N, K, ta);
+    else if (mode == 3) st = dispatch_tc<float, 2>(ctx, bn, tm, tm_lo, W, cdst, M, N, K, ta);
+    else st = dispatch_tc<float, 1>(ctx, bn, tm, tm_lo, W, cdst, M, N, K, ta);
+    if (st == DP_OK && ta.k_splits > 1) {
       const size_t n = (size_t)M * N;
       size_t grid = (n / 4 + 255) / 256;
-      if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
-      if (grid < 1) grid = 1;
-      DP_LAUNCH(ctx, cast_f32_f16_out_kernel, (unsigned)grid, 256, 0, (const float *)c32, (__half *)C, n);
+      if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
+      DP_LAUNCH(ctx, splitk_reduce_kernel, (unsigned)grid, 256, 0, (const float *)cdst, (float *)C, n, ta.k_splits);
     }
   } else if (c_dtype == DP_F16) {
-    st = dispatch_tc<__half>(ctx, bn, tm, W, (__half *)C, M, N, K, ta);
+    if (mode == 3) st = dispatch_tc<__half, 2>(ctx, bn, tm, tm_lo, W, (__half *)C, M, N, K, ta);
+    else st = dispatch_tc<__half, 1>(ctx, bn, tm, tm_lo, W, (__half *)C, M, N, K, ta);
   } else {
     st = dp_fail(ctx, DP_ERR_INVALID, "matmul: unsupported output dtype");
   }
@@ -988,7 +1059,8 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
 // f32 activations of any range on the tensor-core kernel: every row is scaled into f16 range by a power
 // of two and scaled back in the epilogue.  passes == 1: activations and weights rounded to f16 (11-bit
 // significands, what the reference's tiled f16 prefill kernel computes).  passes == 3: the rounding
-// residues of both are multiplied in as well, which gives the f32-exact product to f32 accuracy.
+// residues of both are multiplied in as well (three products per K step in one kernel), which gives the
+// f32-exact product to f32 accuracy.
 dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
                                     bool *handled) {
   return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, alpha, passes == 3 ? 2 : 1, handled);

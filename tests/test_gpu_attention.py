@@ -166,6 +166,29 @@ def test_prefill_rows_on_tensor_cores(dev, H, Hkv, D, T, start):
     assert_close(got, exp, f"prefill rows H{H}/Hkv{Hkv}/D{D}/T{T}/start{start}")
 
 
+@pytest.mark.parametrize("H,Hkv,T,start", [(32, 8, 1024, 0), (8, 8, 257, 3), (16, 8, 100, 1000), (8, 1, 77, 0), (32, 8, 4096, 0)])
+def test_prefill_query_tiled(dev, H, Hkv, T, start):
+    """Causal prefill on the query-tiled kernel (head_dim 128, groups of 1 / 2 / 4 / 8 heads per KV head):
+    tiles of query positions share each K / V tile; ragged last tiles, a start position inside the cache,
+    and the BASELINE prompt lengths.  Semantics: tests/kernels/reference/attention.js:129-151.  At T = 4096
+    the oracle checks a sample of the rows (every row of the first and the last tile, every 37th between)."""
+    D = 128
+    s = synthetic.key(58, H * 10000 + T)
+    kv = start + T
+    q = synthetic.normal_f32(s, T * H * D)
+    k16, v16 = synthetic.normal_f16(s + 1, kv * Hkv * D), synthetic.normal_f16(s + 2, kv * Hkv * D)
+    got = np.asarray(_attn(dev, q, k16, v16, H, D, seq_len=T, kv_len=kv, num_kv_heads=Hkv, causal=True, start_pos=start)).reshape(T, H * D)
+    if T <= 1024:
+        exp = np.asarray(O.attention_f16kv(q, k16, v16, T, kv, H, Hkv, D, causal=True, start_pos=start)).reshape(T, H * D)
+        assert_close(got, exp, f"query-tiled prefill H{H}/Hkv{Hkv}/T{T}/start{start}")
+    else:
+        rows = sorted(set(list(range(0, 32)) + list(range(T - 32, T)) + list(range(0, T, 37))))
+        qm = q.reshape(T, H * D)
+        for r in rows:  # a single query row at position start + r sees keys 0 .. start + r
+            exp = O.attention_f16kv(qm[r], k16, v16, 1, start + r + 1, H, Hkv, D, causal=True, start_pos=start + r)
+            assert_close(got[r], np.asarray(exp).ravel(), f"query-tiled prefill row {r} of {T}")
+
+
 def test_attention_argument_errors(dev):
     q = dev.tensor_from(np.zeros(8 * 128, np.float32))
     kv = dev.tensor_from(np.zeros(16 * 2 * 128, np.float16))
