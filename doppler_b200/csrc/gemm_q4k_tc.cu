@@ -1048,6 +1048,12 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   return st;
 }
 
+// f32 rows -> f16 halves, rounding residues and per-row inverse scales (see scale_cast_rows_kernel); lo may be null.
+dp_status dpk_scale_cast_rows(dp_ctx *ctx, const float *A, __half *hi, __half *lo, float *row_scale, int M, int K) {
+  DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, A, hi, lo, row_scale, K);
+  return DP_OK;
+}
+
 // f16 (or f32, cast to f16) activations.  f16_weights: one product with the dequantised weights rounded to f16,
 // the numerics of the reference's opt-in tiled kernel (fused_matmul_q4_prefill_tiled_f16.wgsl:201).  Otherwise,
 // for f16 activations, two products that keep the weights to f32 accuracy (the rule-selected kernel's numerics).

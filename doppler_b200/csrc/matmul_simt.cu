@@ -343,6 +343,11 @@ dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_
     }
     return DP_OK;
   }
+  if (M >= 2) {
+    bool handled = false;
+    DP_TRY(dpk_gemm_f16w_rows(ctx, W, A, a_dtype, C, c_dtype, M, N, K, alpha, &handled));
+    if (handled) return DP_OK;
+  }
   if (a_dtype == DP_F32 && c_dtype == DP_F32) return launch_f16w<float, float>(ctx, W, (const float *)A, (float *)C, M, N, K, alpha);
   if (a_dtype == DP_F32 && c_dtype == DP_F16) return launch_f16w<float, __half>(ctx, W, (const float *)A, (__half *)C, M, N, K, alpha);
   if (a_dtype == DP_F16 && c_dtype == DP_F32) return launch_f16w<__half, float>(ctx, W, (const __half *)A, (float *)C, M, N, K, alpha);

@@ -154,6 +154,27 @@ def test_f16_weight_gemv_lm_head_shape(dev):
         assert_close(gotm[m], O.f16_gemv(W, N, K, A[m]), f"f16-weight gemv row {m}")
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 8192, 1024), (20, 1000, 512), (9, 136, 256), (70, 256, 128)])
+def test_f16_weight_rows_kernel(dev, M, N, K):
+    """Batched LM head: the weights are streamed once for all rows; ragged row tiles, ragged batches, a batch over 64
+    and activations of a wide range (the per-row scaling) all reach the f32 result."""
+    W = synthetic.normal_f16(synthetic.key(32, N), N * K, 0.02)
+    A = synthetic.normal_f32(synthetic.key(32, M), M * K).reshape(M, K)
+    A[1] *= 3.0e6
+    A[M - 1] *= 1.0e-6
+    got = _matmul(dev, W, N, K, A, M, wdtype="f16")
+    for m in range(M):
+        assert_close(got[m], O.f16_gemv(W, N, K, A[m]), f"f16-weight rows M={M} row {m}")
+    again = _matmul(dev, W, N, K, A, M, wdtype="f16")
+    assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+    # f16 activations, f16 output
+    Ah = synthetic.normal_f32(synthetic.key(33, M), M * K).reshape(M, K).astype(np.float16)
+    goth = _matmul(dev, W, N, K, Ah, M, wdtype="f16", a_dtype="f16", out_dtype="f16")
+    for m in (0, M - 1):
+        ref = O.f16_gemv(W, N, K, Ah[m].astype(np.float32))
+        assert_close(goth[m].astype(np.float32), ref, f"f16-weight rows f16 act row {m}", rtol=2e-3)
+
+
 def test_matmul_argument_errors(dev):
     N, K = 8, 256
     W = synthetic.q4k_matrix(synthetic.key(41, 0), N, K)
