@@ -266,6 +266,19 @@ def gemm_case(dev, ops, synthetic, M, N, K, copies, reps, peak, variant="default
             "frac_of_nominal_2250": fl / dt / 1e12 / 2250.0, "dtype": "f16 x q4k -> f16, f32 accumulate"}
 
 
+def lm_head_case(dev, ops, synthetic, M, N, K, reps, peak):
+    """f16 [N, K] head times M f32 activation rows (the batched decode step's logits matmul); the weights of
+    the default shape (311 MB) are larger than L2."""
+    w = dev.weight_from(synthetic.normal_f16(synthetic.key(6, 0), N * K, 0.02), "f16", [N, K])
+    a = dev.tensor_from(synthetic.normal_f32(synthetic.key(6, 1), M * K).reshape(M, K))
+    out = dev.acquire_buffer(M * N * 4, "logits")
+    dt = _graph_time(dev, ops, lambda rec: [ops.record_matmul(rec, a, w, M, N, K, output_dtype="f32", output_buffer=out)], 1, reps)
+    b = N * K * 2 + M * K * 4 + M * N * 4
+    dev.release_buffer(w.buffer); dev.release_buffer(a.buffer); dev.release_buffer(out); dev.pool_trim()
+    return {"case": "lm_head_f16w", "shape": [M, N, K], "us_per_call": dt * 1e6, "GBps": b / dt / 1e9, "frac_of_measured_hbm": b / dt / 1e9 / peak["hbm_gbs"],
+            "algorithmic_bytes": b, "note": "one call = row scaling pre-pass (M > 1) + kernel"}
+
+
 def attention_case(dev, ops, synthetic, B, kv, reps, peak):
     H, Hkv, D = 32, 8, 128
     s = synthetic.key(synthetic.DEFAULT_SEED, 20)
@@ -317,6 +330,9 @@ def kernel_case(args):
     elif args.case == "gemm":
         M, N, K = tuple(int(v) for v in args.shape.split(",")) if args.shape else (512, 12288, 4096)
         out_lines.append(gemm_case(dev, ops, synthetic, M, N, K, args.copies, reps, peak, variant=args.variant))
+    elif args.case == "lm_head":
+        M, N, K = tuple(int(v) for v in args.shape.split(",")) if args.shape else (64, 151936, 4096)
+        out_lines.append(lm_head_case(dev, ops, synthetic, M, N, K, max(reps, 5), peak))
     elif args.case == "prefill":
         # whole-model prefill of the 9B-shaped decoder (f32 activations, f32-exact product on the tensor cores).
         # Times model.prefill(), prompt upload and first-token read-back included.
@@ -346,6 +362,35 @@ def kernel_case(args):
 
 
 # ----------------------------------------------------------------------------------------
+def kernel_trace(model, dev, tokens, steps, path, barrier, world, batch):
+    """One region of `steps` decode steps under torch.profiler's CUDA activity tracing (every rank runs it, rank 0
+    writes the table).  Times under a tracer are for SHARES; the bench value never comes from here."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.init()
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        model.decode(tokens, steps)
+        dev.sync()
+    barrier()
+    if path is None:
+        return
+    rows = []
+    for e in prof.key_averages():
+        t = float(getattr(e, "device_time_total", 0.0) or getattr(e, "cuda_time_total", 0.0) or 0.0)
+        if t > 0.0:
+            rows.append((t, int(e.count), str(e.key)))
+    rows.sort(reverse=True)
+    total = sum(r[0] for r in rows) or 1.0
+    with open(path, "w") as f:
+        f.write(f"# decode step kernels, rank 0 of {world}, batch {batch}, {steps} steps traced (CUPTI activity records)\n")
+        f.write(f"# device time in kernels per step: {total / steps:.1f} us; wall time of the traced region per step: {model.last_decode_ms * 1000.0 / steps:.1f} us\n")
+        f.write("share_pct\ttotal_us\tlaunches\tavg_us\tkernel\n")
+        for t, c, k in rows:
+            f.write(f"{100.0 * t / total:.1f}\t{t:.0f}\t{c}\t{t / max(c, 1):.2f}\t{k[:160]}\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -357,7 +402,7 @@ def main():
     ap.add_argument("--workload", default="9b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the config 0/1/2 kernel record")
-    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "attention", "prefill"],
+    ap.add_argument("--case", default=None, choices=["gemv", "gemm", "attention", "prefill", "lm_head"],
                     help="time ONE kernel of the path on a BASELINE configuration instead of the decoder "
                          "(gemv: configs 0 and 9B shapes, gemm: config 1, attention: config 2); also the small "
                          "command the profiler captures use")
@@ -366,6 +411,9 @@ def main():
     ap.add_argument("--copies", type=int, default=0, help="--case: distinct weight copies per pass (0 = enough to exceed L2)")
     ap.add_argument("--only-timed", action="store_true",
                     help="stop after the first device-resident timed region (used for profiler launch lists)")
+    ap.add_argument("--kernel-trace", default=None, metavar="FILE",
+                    help="with --only-timed: run one more region of --steps decode steps under torch.profiler (CUPTI activity "
+                         "records, no kernel replay) and have rank 0 write a per-kernel table (launches, device time, share) to FILE")
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
                     help="N>1: one-shot peer-memory exchange fused into the decode kernels, or NCCL")
     args = ap.parse_args()
@@ -472,6 +520,8 @@ def main():
             raise SystemExit(f"ranks decoded different tokens: crc per rank {all_crc}")
 
     if args.only_timed:
+        if args.kernel_trace:
+            kernel_trace(model, dev, nxt, args.steps, args.kernel_trace if rank == 0 else None, barrier, world, B)
         if rank == 0:
             print(json.dumps({"metric": "decode_tokens_per_s", "value": B * args.steps / (ms / 1000.0), "unit": "tokens/s",
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
