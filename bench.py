@@ -250,20 +250,25 @@ def gemv_case(dev, ops, synthetic, N, K, copies, reps, peak):
             "note": "one call = activation digit pre-pass + GEMV kernel, graph of `copies` calls over distinct matrices"}
 
 
-def gemm_case(dev, ops, synthetic, M, N, K, copies, reps, peak, variant="default"):
+def gemm_case(dev, ops, synthetic, M, N, K, copies, reps, peak, variant="default", adtype="f16"):
     copies = copies or 4
     ws = [dev.weight_from(synthetic.q4k_matrix(synthetic.key(5, i), N, K), "q4k", [N, K]) for i in range(copies)]
-    a = dev.tensor_from(synthetic.normal_f16(synthetic.key(5, 100), M * K).reshape(M, K))
-    out = dev.acquire_buffer(M * N * 2, "c")
+    if adtype == "f32":  # the runner's case: f32 activations and output, f32-exact product (three tensor-core products)
+        a = dev.tensor_from(synthetic.normal_f32(synthetic.key(5, 100), M * K).reshape(M, K))
+    else:
+        a = dev.tensor_from(synthetic.normal_f16(synthetic.key(5, 100), M * K).reshape(M, K))
+    odt = "f32" if adtype == "f32" else "f16"
+    out = dev.acquire_buffer(M * N * (4 if adtype == "f32" else 2), "c")
     kw = {"f16_weights": True} if variant == "f16_weights" else {}
-    dt = _graph_time(dev, ops, lambda rec: [ops.record_matmul(rec, a, w, M, N, K, output_dtype="f16", output_buffer=out, **kw) for w in ws], copies, reps)
+    dt = _graph_time(dev, ops, lambda rec: [ops.record_matmul(rec, a, w, M, N, K, output_dtype=odt, output_buffer=out, **kw) for w in ws], copies, reps)
     fl = 2.0 * M * N * K
     for w in ws:
         dev.release_buffer(w.buffer)
     dev.release_buffer(a.buffer); dev.release_buffer(out); dev.pool_trim()
     return {"case": "q4k_gemm_tcgen05", "variant": variant, "shape": [M, N, K], "us_per_call": dt * 1e6, "TFLOPs": fl / dt / 1e12,
             "frac_of_measured_burst": fl / dt / 1e12 / peak["tf_burst"], "frac_of_measured_sustained": fl / dt / 1e12 / peak["tf_sustained"],
-            "frac_of_nominal_2250": fl / dt / 1e12 / 2250.0, "dtype": "f16 x q4k -> f16, f32 accumulate"}
+            "frac_of_nominal_2250": fl / dt / 1e12 / 2250.0, "dtype": f"{adtype} x q4k -> {odt}, f32 accumulate",
+            "weights_per_s": N * K / dt, "q4k_GBps": N * K * 0.5625 / dt / 1e9}
 
 
 def lm_head_case(dev, ops, synthetic, M, N, K, reps, peak):
@@ -329,7 +334,7 @@ def kernel_case(args):
             out_lines.append(gemv_case(dev, ops, synthetic, N, K, args.copies, reps, peak))
     elif args.case == "gemm":
         M, N, K = tuple(int(v) for v in args.shape.split(",")) if args.shape else (512, 12288, 4096)
-        out_lines.append(gemm_case(dev, ops, synthetic, M, N, K, args.copies, reps, peak, variant=args.variant))
+        out_lines.append(gemm_case(dev, ops, synthetic, M, N, K, args.copies, reps, peak, variant=args.variant, adtype=args.adtype))
     elif args.case == "lm_head":
         M, N, K = tuple(int(v) for v in args.shape.split(",")) if args.shape else (64, 151936, 4096)
         out_lines.append(lm_head_case(dev, ops, synthetic, M, N, K, max(reps, 5), peak))
@@ -408,6 +413,7 @@ def main():
                          "command the profiler captures use")
     ap.add_argument("--shape", default=None, help="--case gemv/gemm: N,K or M,N,K; --case attention: batch,kv_len")
     ap.add_argument("--variant", default="default", choices=["default", "f16_weights"], help="--case gemm: exact product or f16-rounded weights")
+    ap.add_argument("--adtype", default="f16", choices=["f16", "f32"], help="--case gemm: activation (and output) dtype")
     ap.add_argument("--copies", type=int, default=0, help="--case: distinct weight copies per pass (0 = enough to exceed L2)")
     ap.add_argument("--only-timed", action="store_true",
                     help="stop after the first device-resident timed region (used for profiler launch lists)")

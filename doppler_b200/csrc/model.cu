@@ -681,7 +681,7 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   bool handled = false;
   // (batched decode steps recorded into a CUDA graph take the same path: the f16 scratch belongs to the
   // context and is never recycled while a graph is alive)
-  if (prefill_tc && M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
+  if (prefill_tc && M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;

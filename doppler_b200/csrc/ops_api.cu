@@ -114,7 +114,7 @@ extern "C" dp_status dp_matmul(dp_ctx *ctx, dp_recorder *rec, const dp_tensor *A
         st = dpk_gemm_q4k_tc(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha, o.f16_weights != 0, &handled);
       // f32 activations select the f32-exact product (matmul.rules.json:15-22): from 32 rows on the tensor
       // cores compute it in three passes (f16 halves and rounding residues of activations and weights)
-      else if (!o.exact_weights && M >= 32 && A->dtype == DP_F32 && o.out_dtype == DP_F32)
+      else if (!o.exact_weights && M >= 2 && A->dtype == DP_F32 && o.out_dtype == DP_F32)
         st = dpk_gemm_q4k_tc_rowscaled(ctx, (const uint8_t *)bptr, (const float *)aptr, (float *)cptr, M, N, K, o.alpha, 3, &handled);
       if (st == DP_OK && !handled)
         st = dpk_gemm_q4k_simt(ctx, (const uint8_t *)bptr, aptr, A->dtype, cptr, o.out_dtype, M, N, K, o.alpha);
@@ -471,7 +471,7 @@ static dp_status fused_matvec(dp_ctx *ctx, dp_dtype wdtype, const char *w, const
       return DP_OK;
     }
     bool handled = false;
-    if (M >= 32) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, (const uint8_t *)w, x, y, M, N, K, alpha, 3, &handled));
+    if (M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, (const uint8_t *)w, x, y, M, N, K, alpha, 3, &handled));
     if (handled) return DP_OK;
     return dpk_gemm_q4k_simt(ctx, (const uint8_t *)w, x, DP_F32, y, DP_F32, M, N, K, alpha);
   }

@@ -249,6 +249,35 @@ def test_f32_activation_gemm_runs_on_the_tensor_cores(dev):
     assert (np.abs(exact - exp) / (2e-5 * (np.abs(exp) + rms) + 1e-300)).max() <= 1.0
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 12288), (64, 6144, 4096), (40, 1536, 2048), (2, 256, 256), (17, 128, 512), (33, 384, 1024)])
+def test_small_batch_gemm_weights_on_the_m_side(dev, M, N, K):
+    """2..64 activation rows (batched decode steps): the kernel with the 128 weight rows of a tile on the MMA's M
+    side, units of (tile, super-block column) dealt evenly to one CTA per SM, split tiles added in CTA order.
+    f32 activations spanning ten decades against the exact product per row (gate 2e-5 up to K = 2048, growing
+    with sqrt(K) beyond); two runs give the same
+    bits; f16 activations with both weight numerics."""
+    W = synthetic.q4k_matrix(synthetic.key(95, N + K), N, K)
+    A = synthetic.normal_f32(synthetic.key(95, M), M * K).reshape(M, K)
+    A = (A * (10.0 ** np.linspace(-3.0, 7.0, M).astype(np.float32))[:, None]).astype(np.float32)
+    if M > 8:
+        A[5] = 0.0
+    exp = np.asarray(O.q4k_gemm(W, N, K, A.ravel(), M), np.float64).reshape(M, N)
+    got32 = _matmul(dev, W, N, K, A, M)
+    got = np.asarray(got32, np.float64).reshape(M, N)
+    assert np.all(np.isfinite(got))
+    rms = np.sqrt(np.mean(exp * exp, axis=1, keepdims=True))
+    gate = 2e-5 * max(1.0, (K / 2048.0) ** 0.5)  # f32 accumulation error grows with the square root of K
+    ratio = np.abs(got - exp) / (gate * (np.abs(exp) + rms) + 1e-300)
+    print(f"[parity] small-batch gemm [{M},{K}]x[{N},{K}]: worst per-row gate ratio {ratio.max():.3f} at gate {gate:.1e}")
+    assert ratio.max() <= 1.0
+    assert np.array_equal(got32.view(np.uint32), _matmul(dev, W, N, K, A, M).view(np.uint32)), "not run-to-run deterministic"
+    A16 = synthetic.normal_f16(synthetic.key(96, M), M * K)
+    got16 = _matmul(dev, W, N, K, A16, M, out_dtype="f32", a_dtype="f16")
+    assert_close(got16, O.q4k_gemm(W, N, K, A16.astype(np.float32), M), "small-batch gemm, f16 activations")
+    gotw = _matmul(dev, W, N, K, A16, M, out_dtype="f32", a_dtype="f16", f16_weights=True)
+    assert_close(gotw, O.q4k_gemm_f16_weights(W, N, K, A16.astype(np.float32), M), "small-batch gemm, f16 activations, f16-rounded weights")
+
+
 def test_few_tiles_long_k_is_deterministic(dev):
     """A problem of few output tiles and a long K (here two tiles, K = 4096) is split over K: several CTAs per
     tile take whole super-blocks each, write their own partial tile, and a second kernel adds the parts in a
