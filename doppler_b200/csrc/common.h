@@ -219,5 +219,7 @@ dp_status dpk_silu_mul(dp_ctx *ctx, const float *up, const float *gate, float *o
 dp_status dpk_residual_add(dp_ctx *ctx, const float *a, const float *b, float *out, size_t n, float scale);
 dp_status dpk_gather_f16(dp_ctx *ctx, const int *ids, const __half *table, float *out, int n_ids, int hidden);
 dp_status dpk_kv_write(dp_ctx *ctx, const float *src, __half *dst, size_t n);
+dp_status dpk_argmax_rows(dp_ctx *ctx, const float *logits, int n, size_t row_stride, int rows, int *out, float *scratch_vals,
+                          int *scratch_idx, int index_base, float *best_vals);
 dp_status dpk_argmax(dp_ctx *ctx, const float *logits, int n, int pad_id, int *out, int out_index,
                      float *scratch_vals, int *scratch_idx, int index_base, float *best_val_out);

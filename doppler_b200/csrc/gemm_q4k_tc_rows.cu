@@ -427,21 +427,20 @@ __global__ void __launch_bounds__((DQW + 2) * 32, 1) gemm_q4k_tc_rows_kernel(con
 __global__ void __launch_bounds__(256) rows_reduce_kernel(const float *__restrict__ parts, float *__restrict__ C, int M, int N, RowsPlan plan) {
   pdl_launch();
   pdl_wait();
-  const int n4 = N / 4;
-  const long total = (long)M * n4;
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    const int m = (int)(i / n4), n = (int)(i % n4) * 4;
-    const int tile = n / TILE_N;
-    const int cf = rows_unit_owner((long)tile * plan.bpr, plan.units, plan.ctas);
-    const int cl = rows_unit_owner((long)tile * plan.bpr + plan.bpr - 1, plan.units, plan.ctas);
-    if (cf == cl) continue;
+  // one thread per four columns of a tile row; blockIdx.y = tile, so the owners are computed once per block
+  const int tile = blockIdx.y;
+  const int units = (int)plan.units, ctas = plan.ctas, bpr = plan.bpr;
+  const int cf = rows_unit_owner((long)tile * bpr, units, ctas), cl = rows_unit_owner((long)tile * bpr + bpr - 1, units, ctas);
+  if (cf == cl) return;  // one CTA computed the whole tile and wrote C itself
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < M * (TILE_N / 4); i += gridDim.x * blockDim.x) {
+    const int m = i / (TILE_N / 4), n = (i - m * (TILE_N / 4)) * 4;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int c = cf; c <= cl; c++) {
-      const int seg = tile - (int)(rows_unit_begin(c, plan.units, plan.ctas) / plan.bpr);
-      const float4 v = *reinterpret_cast<const float4 *>(parts + ((size_t)c * plan.max_segs + seg) * (size_t)M * TILE_N + (size_t)m * TILE_N + (n - tile * TILE_N));
+      const int seg = tile - (int)(rows_unit_begin(c, units, ctas) / bpr);
+      const float4 v = *reinterpret_cast<const float4 *>(parts + ((size_t)c * plan.max_segs + seg) * (size_t)M * TILE_N + (size_t)m * TILE_N + n);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
-    *reinterpret_cast<float4 *>(C + (size_t)m * N + n) = acc;
+    *reinterpret_cast<float4 *>(C + (size_t)m * N + (size_t)tile * TILE_N + n) = acc;
   }
 }
 
@@ -512,10 +511,8 @@ dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_
   else st = f32a ? launch_rows<64, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan) : launch_rows<64, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan);
   if (st != DP_OK) return st;
   if (plan.units % plan.ctas != 0 || (plan.units / plan.ctas) % plan.bpr != 0) {  // some tile is shared between CTAs
-    const long n = (long)M * N / 4;
-    long grid = (n + 255) / 256;
-    if (grid > (long)ctx->sm_count * 4) grid = (long)ctx->sm_count * 4;
-    DP_LAUNCH(ctx, rows_reduce_kernel, (unsigned)grid, 256, 0, (const float *)parts, C, M, N, plan);
+    const int per_tile = M * (TILE_N / 4);
+    DP_LAUNCH(ctx, rows_reduce_kernel, dim3((unsigned)((per_tile + 255) / 256), (unsigned)plan.tiles), 256, 0, (const float *)parts, C, M, N, plan);
   }
   *handled = true;
   return DP_OK;

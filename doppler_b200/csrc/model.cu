@@ -951,9 +951,10 @@ static dp_status run_head(dp_model *m, const float *hrow, int rows) {
     DP_TRY(dpk_rmsnorm(ctx, hrow, m->final_norm, false, nullptr, false, nullptr, m->n, rows, c.hidden, c.eps, false, 1.0f));
   m->final_norm_done = false;
   DP_TRY(dpk_gemv_f16w(ctx, (const __half *)m->lm_head->dptr, m->n, DP_F32, m->logits, DP_F32, rows, m->vocab_l, c.hidden, 1.0f));
-  for (int b = 0; b < rows; b++)
-    DP_TRY(dpk_argmax(ctx, m->logits + (size_t)b * m->vocab_l, m->vocab_l, -1, m->d_tok, b, m->am_vals + (size_t)b * 256,
-                      m->am_idx + (size_t)b * 256, m->vocab0, m->am_best + b));
+  if (rows == 1)
+    DP_TRY(dpk_argmax(ctx, m->logits, m->vocab_l, -1, m->d_tok, 0, m->am_vals, m->am_idx, m->vocab0, m->am_best));
+  else  // all rows in two launches
+    DP_TRY(dpk_argmax_rows(ctx, m->logits, m->vocab_l, (size_t)m->vocab_l, rows, m->d_tok, m->am_vals, m->am_idx, m->vocab0, m->am_best));
   if (c.tp_size > 1) {
     dp_tp_exchange *xd = dp_tp_exchange_desc(ctx);
     ArgmaxExchange xg{};

@@ -315,6 +315,62 @@ __global__ void __launch_bounds__(256) argmax_phase2(const float *__restrict__ v
   }
 }
 
+// the same two phases for `rows` independent logit rows in two launches: grid (groups, rows) and (rows);
+// row r uses scratch entries [r * ARGMAX_BLOCKS, (r + 1) * ARGMAX_BLOCKS)
+__global__ void __launch_bounds__(256) argmax_rows_phase1(const float *__restrict__ logits, int n, size_t row_stride,
+                                                          float *__restrict__ vals, int *__restrict__ idxs) {
+  pdl_launch();
+  pdl_wait();
+  const float *row = logits + (size_t)blockIdx.y * row_stride;
+  float best = -3.402823e+38f;
+  int bi = 0;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const float v = row[i];
+    if (beats(v, i, best, bi)) { best = v; bi = i; }
+  }
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  sv[threadIdx.x] = best; si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s && beats(sv[threadIdx.x + s], si[threadIdx.x + s], sv[threadIdx.x], si[threadIdx.x])) {
+      sv[threadIdx.x] = sv[threadIdx.x + s]; si[threadIdx.x] = si[threadIdx.x + s];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { vals[blockIdx.y * ARGMAX_BLOCKS + blockIdx.x] = sv[0]; idxs[blockIdx.y * ARGMAX_BLOCKS + blockIdx.x] = si[0]; }
+}
+
+__global__ void __launch_bounds__(256) argmax_rows_phase2(const float *__restrict__ vals, const int *__restrict__ idxs, int groups,
+                                                          int *__restrict__ out, int index_base, float *__restrict__ best_vals) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int t = threadIdx.x, r = blockIdx.x;
+  sv[t] = t < groups ? vals[r * ARGMAX_BLOCKS + t] : -3.402823e+38f;
+  si[t] = t < groups ? idxs[r * ARGMAX_BLOCKS + t] : 0x7fffffff;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (t < s && beats(sv[t + s], si[t + s], sv[t], si[t])) { sv[t] = sv[t + s]; si[t] = si[t + s]; }
+    __syncthreads();
+  }
+  if (t == 0) {
+    out[r] = si[0] + index_base;
+    if (best_vals) best_vals[r] = sv[0];
+  }
+}
+
+dp_status dpk_argmax_rows(dp_ctx *ctx, const float *logits, int n, size_t row_stride, int rows, int *out, float *scratch_vals,
+                          int *scratch_idx, int index_base, float *best_vals) {
+  int groups = (n + 255) / 256;
+  if (groups > 64) groups = 64;  // rows x groups blocks: enough to fill the GPU from a few rows on
+  if (groups < 1) groups = 1;
+  DP_LAUNCH(ctx, argmax_rows_phase1, dim3((unsigned)groups, (unsigned)rows), 256, 0, logits, n, row_stride, scratch_vals, scratch_idx);
+  DP_LAUNCH(ctx, argmax_rows_phase2, (unsigned)rows, 256, 0, (const float *)scratch_vals, (const int *)scratch_idx, groups, out, index_base, best_vals);
+  return DP_OK;
+}
+
 dp_status dpk_argmax(dp_ctx *ctx, const float *logits, int n, int pad_id, int *out, int out_index, float *scratch_vals,
                      int *scratch_idx, int index_base, float *best_val_out) {
   int groups = (n + 255) / 256;
