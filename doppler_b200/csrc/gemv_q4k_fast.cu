@@ -334,9 +334,17 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
             const unsigned ticket = *reinterpret_cast<const volatile unsigned *>(gx.ticket_step) * gx.ticket_stride + 1u + gx.ticket_in;
             const uint2 *mine = gx.mine;
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int r = 0; r < gx.nr; r++) {  // rank order: every rank computes the same bits
+            // rank order: every rank computes the same bits; two ranks' words are fetched together
+            for (int r = 0; r + 1 < gx.nr; r += 2) {
+              float s8[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              handoff_take8x2(mine + dp_tp_slot_offset((unsigned)gx.parity_in, r) + off, mine + dp_tp_slot_offset((unsigned)gx.parity_in, r + 1) + off,
+                              ticket, s8, t8, gx.wait_limit, abort_flag);
+#pragma unroll
+              for (int j = 0; j < 8; j++) acc[j] = (acc[j] + s8[j]) + t8[j];
+            }
+            if (gx.nr & 1) {
               float s8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-              handoff_take8(mine + dp_tp_slot_offset((unsigned)gx.parity_in, r) + off, ticket, s8, gx.wait_limit, abort_flag);
+              handoff_take8(mine + dp_tp_slot_offset((unsigned)gx.parity_in, gx.nr - 1) + off, ticket, s8, gx.wait_limit, abort_flag);
 #pragma unroll
               for (int j = 0; j < 8; j++) acc[j] += s8[j];
             }
