@@ -582,7 +582,7 @@ def main():
             "gpu_launches": int(launches),
             "tokens_crc": f"{crc:08x}",
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "Q4_K decode GEMV kernels as the decode graph launches them (all matrices of the model, back to back)",
+            "roofline": {"bound": "hbm", "kernel": "Q4_K decode GEMV kernels, the instantiations the decode graph launches (RMSNorm / split-merge / silu*up prologues included), all matrices of the model back to back, each reading its predecessor's output",
                          "achieved": gemv_gbs, "peak": peak["hbm_gbs"], "peak_source": peak["source"], "unit": "GB/s",
                          "frac": gemv_gbs / peak["hbm_gbs"], "frac_of_nominal_8000": gemv_gbs / 8000.0,
                          "launches": g["launches"], "avg_launch_us": gemv_ms * 1000.0 / max(g["launches"], 1),

@@ -1085,8 +1085,13 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
   for (int i = 0; i < 4; i++)
     n_bytes += (uint64_t)sh[i].N * dp_cdiv((size_t)sh[i].K, DP_QK_K) * DP_Q4K_BLOCK_BYTES + 4ull * sh[i].K + 4ull * sh[i].N;
   n_bytes *= (uint64_t)c.n_layers * (uint64_t)reps;
-  // valid digits for every K in use (the timed loop launches the GEMV kernels only, as the decode step does)
+  // The timed loop launches, per layer, the four GEMV kernels of the single-token decode step with the prologues
+  // that step uses (RMSNorm for q|k|v and gate|up, split merge for o_proj, silu(gate)*up for down_proj), each
+  // reading what its predecessor wrote, back to back without the attention kernel.  Shapes the fused kernels do
+  // not plan fall back to the kernel that takes ready-made digits.
   DP_TRY(dpk_q4k_prep_act(ctx, m->actv, m->actq->dptr, m->inter > H ? (m->inter / QK_K) * QK_K : H));
+  const int splits = m->attn_splits_decode > 1 ? m->attn_splits_decode : 2;
+  const bool fused_ok = c.tp_size == 1 && m->attn_scratch && c.head_dim % 8 == 0 && m->qdim % QK_K == 0 && m->inter % QK_K == 0;
   const uint64_t l0 = ctx->launches;
   ctx->pdl = true;
   DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
@@ -1094,12 +1099,27 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
   for (int r = 0; r < reps && st == DP_OK; r++) {
     for (int l = 0; l < c.n_layers && st == DP_OK; l++) {
       LayerW &L = m->layers[l];
-      const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,
-                             (const uint8_t *)L.down->dptr};
-      const float *X[4] = {m->n, m->att, m->n, m->actv};
-      float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
-      for (int i = 0; i < 4 && st == DP_OK; i++)  // digits_ready: in the decode step the producer kernel has already written them
-        st = q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K));
+      bool done[4] = {false, false, false, false};
+      if (fused_ok) {
+        st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.qkv->dptr, SRC_RMSNORM, m->h, L.in_norm, c.eps, 0, 0, m->qkv, sh[0].N, H, nullptr, &done[0]);
+        if (st == DP_OK && !done[0]) st = q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, 1, sh[0].N, sh[0].K, nullptr, dpk_gemv_q4k_fast_ok(sh[0].N, sh[0].K));
+        if (st == DP_OK)
+          st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.o->dptr, SRC_COMBINE, (const float *)m->attn_scratch->dptr, nullptr, 0.0f, c.head_dim, splits,
+                                      m->partial, H, m->qdim, m->h, &done[1]);
+        if (st == DP_OK && !done[1]) st = q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, 1, sh[1].N, sh[1].K, nullptr, dpk_gemv_q4k_fast_ok(sh[1].N, sh[1].K));
+        if (st == DP_OK)
+          st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, sh[2].N, H, nullptr, &done[2]);
+        if (st == DP_OK && !done[2]) st = q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, 1, sh[2].N, sh[2].K, nullptr, dpk_gemv_q4k_fast_ok(sh[2].N, sh[2].K));
+        if (st == DP_OK) st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, m->h, &done[3]);
+        if (st == DP_OK && !done[3]) st = q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, 1, sh[3].N, sh[3].K, nullptr, dpk_gemv_q4k_fast_ok(sh[3].N, sh[3].K));
+      } else {
+        const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,
+                               (const uint8_t *)L.down->dptr};
+        const float *X[4] = {m->n, m->att, m->n, m->actv};
+        float *Y[4] = {m->qkv, m->partial, m->gu, m->partial};
+        for (int i = 0; i < 4 && st == DP_OK; i++)
+          st = q4k_linear(m, W[i], X[i], Y[i], 1, sh[i].N, sh[i].K, nullptr, dpk_gemv_q4k_fast_ok(sh[i].N, sh[i].K));
+      }
     }
   }
   ctx->pdl = false;
