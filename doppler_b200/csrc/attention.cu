@@ -331,8 +331,9 @@ static int tc_splits(dp_ctx *ctx, const dpk_attn_params &p, int gt) {
   for (long s = 1; s <= 32; s++) {
     const long keys = (p.kv_len + s - 1) / s;
     // at least two rounds of the CTA's four warps per split: finer splits only lengthen the merge that
-    // follows (9B-shaped decode at context 1024: 8 splits 2.08 ms per step, 17 splits 2.21 ms)
-    if (s > 1 && keys < 128) break;
+    // follows (9B-shaped decode at context 1024, cache of 1450 keys: 4 / 6 / 8 / 11 / 16 splits 1.962 / 1.944 / 1.966 /
+    // 1.989 / 2.046 ms per step)
+    if (s > 1 && keys < 192) break;
     const long waves = (base * s + slots - 1) / slots;
     const long cost = waves * (keys + 64);
     if (best_cost < 0 || cost < best_cost) { best = s; best_cost = cost; }

@@ -250,7 +250,10 @@ __host__ __device__ inline TgLayout tg_layout(int K, int cb, int stages) {
 //                each CTA also writes its share of h'.  Allreduce + residual add + RMSNorm in the prologue.
 // Output: y[row] (+ residual), or, with GemvExchange::push, the rows go as (value, ticket) words into this
 // rank's slot of every rank's exchange area (plain stores over NVLink): the allreduce's send side in the epilogue.
-enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4 };
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4, SRC_PLAIN = 5 };
+// mode flag of dpk_gemv_q4k_tma_fused: the rows are gate|up pairs (eight gate rows, then their eight up rows per
+// 16-row tile) and the kernel stores silu(gate) * up, N / 2 values, instead of the N raw rows
+enum { SRC_FLAG_SILU_OUT = 0x100 };
 struct GemvSource {
   const float *x;   // h (SRC_RMSNORM), gu (SRC_SILU), partials (SRC_COMBINE)
   const float *w;   // norm weights
@@ -262,7 +265,7 @@ struct GemvSource {
 // while one group is in the latency-bound tail of a tile the other keeps the tensor pipe busy.
 // PUSH: the epilogue pushes the rows into the exchange areas (GemvExchange); instantiated only for the
 // tensor-parallel launches, so the other instantiations carry none of that code.
-template <typename OutT, int GROUPS, int SRC, bool PUSH = false>
+template <typename OutT, int GROUPS, int SRC, bool PUSH = false, bool SILU_OUT = false>
 __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_tma_kernel(
     const uint8_t *__restrict__ W, const int8_t *__restrict__ limbs, const float *__restrict__ xscale,
     const float *__restrict__ ssum, OutT *__restrict__ y, int N, int K, int cb, int stages, float alpha,
@@ -378,6 +381,23 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
 #pragma unroll
           for (int j = 0; j < 8; j++) o[j] = v[i][j] * inv_rms * wv[j];
           actq_emit_block(o, lane, b, bpr, smem);
+        }
+      }
+    } else if constexpr (SRC == SRC_PLAIN) {
+      // the input vector as it is (the previous kernel stored silu(gate) * up); two blocks per round
+      for (int b = cw; b < bpr; b += 2 * NW) {
+        const int b2 = b + NW;
+        const bool two = b2 < bpr;
+        const float *xp = gs.x + b * QK_K + lane * 8, *xq = gs.x + (two ? b2 : b) * QK_K + lane * 8;
+        const float4 a0 = *reinterpret_cast<const float4 *>(xp), a1 = *reinterpret_cast<const float4 *>(xp + 4);
+        const float4 c0 = *reinterpret_cast<const float4 *>(xq), c1 = *reinterpret_cast<const float4 *>(xq + 4);
+        {
+          const float o[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          actq_emit_block(o, lane, b, bpr, smem);
+        }
+        if (two) {
+          const float o[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          actq_emit_block(o, lane, b2, bpr, smem);
         }
       }
     } else if constexpr (SRC == SRC_SILU) {
@@ -603,6 +623,14 @@ __global__ void __launch_bounds__((GROUPS * TG_CONSUMERS + 1) * 32, 1) gemv_q4k_
 #pragma unroll
             for (int r = 0; r < 8; r++)  // (static indices: a run-time index would copy the parameter block to local memory)
               if (r < gx.nr) handoff_put(gx.area[r] + off, v, ticket);
+          } else if constexpr (SILU_OUT) {
+            // lanes 0..7 hold gate rows 8 rt .. 8 rt + 7, lanes 8..15 their up rows (the rows are stored in that order)
+            const float u = __shfl_down_sync(0x0000ffffu, v, 8);
+            if (lane < 8) {
+              const float cl = fminf(fmaxf(v, -15.0f), 15.0f);
+              const float a = (v * (1.0f / (1.0f + expf(-cl)))) * u;
+              if constexpr (sizeof(OutT) == 4) y[rt * 8 + lane] = a; else y[rt * 8 + lane] = __float2half_rn(a);
+            }
           } else {
             if (residual) v += residual[row];
             if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
@@ -633,7 +661,7 @@ static bool tma_plan(dp_ctx *ctx, int N, int K, int *cb_out, int *stages_out, ui
   return true;
 }
 
-template <typename OutT, int GROUPS, int SRC, bool PUSH = false>
+template <typename OutT, int GROUPS, int SRC, bool PUSH = false, bool SILU_OUT = false>
 static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, OutT *y, int N, int K, int cb, int stages,
                             uint32_t smem, float alpha, const float *residual, const GemvSource &gs, const GemvExchange &gx = GemvExchange()) {
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
@@ -641,10 +669,10 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
-    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH, SILU_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
+  DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH, SILU_OUT>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
             N, K, cb, stages, alpha, residual, ctx->dev_status, gs, gx);
   return DP_OK;
 }
@@ -679,6 +707,9 @@ dp_status dpk_gemv_q4k_actq_tma(dp_ctx *ctx, const uint8_t *W, const void *actq,
 dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
                                  int splits, float *y, int N, int K, const float *residual, bool *handled, const GemvExchange *gxp) {
   *handled = false;
+  const bool silu_out = (mode & SRC_FLAG_SILU_OUT) != 0;
+  mode &= ~SRC_FLAG_SILU_OUT;
+  if (silu_out && (residual || (mode != SRC_RMSNORM && mode != SRC_XCHG_RMSNORM))) return DP_OK;
   int cb, stages;
   uint32_t smem;
   if (gemv_variant() == 0 || !ctx->dev_status || !tma_plan(ctx, N, K, &cb, &stages, &smem)) return DP_OK;
@@ -688,7 +719,9 @@ dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const 
   if (gxp) {
     const GemvExchange &gx = *gxp;
     if ((mode == SRC_XCHG_RMSNORM && K > DP_TP_SLOT_FLOATS) || (gx.push && N > DP_TP_SLOT_FLOATS)) return DP_OK;
-    if (mode == SRC_XCHG_RMSNORM && !gx.push) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    if (mode == SRC_XCHG_RMSNORM && !gx.push && silu_out) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM, false, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_XCHG_RMSNORM && !gx.push) DP_TRY((launch_tma<float, 2, SRC_XCHG_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
+    else if (mode == SRC_PLAIN && gx.push) DP_TRY((launch_tma<float, 2, SRC_PLAIN, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
     else if (mode == SRC_SILU && gx.push) DP_TRY((launch_tma<float, 2, SRC_SILU, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
     else if (mode == SRC_COMBINE && gx.push) DP_TRY((launch_tma<float, 2, SRC_COMBINE, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs, gx)));
     else return DP_OK;  // (the schedule uses exactly these three)
@@ -696,7 +729,9 @@ dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const 
     return DP_OK;
   }
   if (mode == SRC_XCHG_RMSNORM) return DP_OK;
-  if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  if (mode == SRC_RMSNORM && silu_out) DP_TRY((launch_tma<float, 2, SRC_RMSNORM, false, true>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  else if (mode == SRC_RMSNORM) DP_TRY((launch_tma<float, 2, SRC_RMSNORM>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
+  else if (mode == SRC_PLAIN) DP_TRY((launch_tma<float, 2, SRC_PLAIN>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
   else if (mode == SRC_SILU) DP_TRY((launch_tma<float, 2, SRC_SILU>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
   else if (mode == SRC_COMBINE) DP_TRY((launch_tma<float, 2, SRC_COMBINE>(ctx, W, nullptr, y, N, K, cb, stages, smem, 1.0f, residual, gs)));
   else return DP_OK;

@@ -687,7 +687,7 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   return DP_OK;
 }
 
-enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4 };
+enum { SRC_DIGITS = 0, SRC_RMSNORM = 1, SRC_SILU = 2, SRC_COMBINE = 3, SRC_XCHG_RMSNORM = 4, SRC_PLAIN = 5, SRC_FLAG_SILU_OUT = 0x100 };
 
 // One pass over `tokens` rows already gathered in m->h.  decode: rows are
 // sequences (positions from the device arrays); prefill: rows are consecutive
@@ -776,8 +776,9 @@ static dp_status run_layers_tp_exchange(dp_model *m, const DecodeGroup &g) {
       GemvExchange gx = base;
       gx.ticket_in = 3u * (unsigned)l; gx.parity_in = 0; gx.h_out = m->hbuf[(cur + 1) % 3];
       done = false;
-      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_XCHG_RMSNORM, m->hbuf[cur], L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
-                                    nullptr, &done, &gx));
+      // (the reducing warps store silu(gate) * up: down_proj then reads a plain vector of half the size)
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_XCHG_RMSNORM | SRC_FLAG_SILU_OUT, m->hbuf[cur], L.post_norm, c.eps, 0, 0, m->actv,
+                                    2 * m->inter, H, nullptr, &done, &gx));
       if (!done) return fail("gate|up", l);
       cur = (cur + 1) % 3;
     }
@@ -785,7 +786,7 @@ static dp_status run_layers_tp_exchange(dp_model *m, const DecodeGroup &g) {
       GemvExchange gx = base;
       gx.push = 1; gx.parity_out = 1; gx.ticket_out = 3u * (unsigned)l + 2u;
       done = false;
-      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, nullptr, &done, &gx));
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_PLAIN, m->actv, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, nullptr, &done, &gx));
       if (!done) return fail("down_proj", l);
     }
   }
@@ -901,9 +902,16 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     }
     // ---- gate | up ----
     done = false;
+    bool act_ready = false;  // the gate|up kernel stored silu(gate) * up itself
     if (single) {
-      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
-                                    nullptr, &done));
+      if (m->inter % QK_K == 0 && dpk_gemv_q4k_fast_ok(H, m->inter)) {
+        DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM | SRC_FLAG_SILU_OUT, m->h, L.post_norm, c.eps, 0, 0, m->actv,
+                                      2 * m->inter, H, nullptr, &done));
+        act_ready = done;
+      }
+      if (!done)
+        DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, 2 * m->inter, H,
+                                      nullptr, &done));
     }
     if (!done) {
       const bool emit = single && H % QK_K == 0 && H <= 8192 && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
@@ -918,7 +926,10 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     float *d_dst = p == 1 ? m->h : m->partial;
     const float *d_res = p == 1 ? m->h : nullptr;
     done = false;
-    if (single && m->inter % QK_K == 0)
+    if (act_ready) {
+      DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_PLAIN, m->actv, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
+      if (!done) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: down_proj cannot read the fused silu(gate) * up vector");
+    } else if (single && m->inter % QK_K == 0)
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
     if (!done) {
       const bool emit = single && m->inter % QK_K == 0 && dpk_gemv_q4k_fast_ok(H, m->inter);
@@ -1108,9 +1119,9 @@ extern "C" dp_status dp_model_bench_gemv(dp_model *m, int reps, double *ms_total
                                       m->partial, H, m->qdim, m->h, &done[1]);
         if (st == DP_OK && !done[1]) st = q4k_linear(m, (const uint8_t *)L.o->dptr, m->att, m->partial, 1, sh[1].N, sh[1].K, nullptr, dpk_gemv_q4k_fast_ok(sh[1].N, sh[1].K));
         if (st == DP_OK)
-          st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM, m->h, L.post_norm, c.eps, 0, 0, m->gu, sh[2].N, H, nullptr, &done[2]);
+          st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM | SRC_FLAG_SILU_OUT, m->h, L.post_norm, c.eps, 0, 0, m->actv, sh[2].N, H, nullptr, &done[2]);
         if (st == DP_OK && !done[2]) st = q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, 1, sh[2].N, sh[2].K, nullptr, dpk_gemv_q4k_fast_ok(sh[2].N, sh[2].K));
-        if (st == DP_OK) st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, m->h, &done[3]);
+        if (st == DP_OK) st = dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_PLAIN, m->actv, nullptr, 0.0f, 0, 0, m->partial, H, m->inter, m->h, &done[3]);
         if (st == DP_OK && !done[3]) st = q4k_linear(m, (const uint8_t *)L.down->dptr, m->actv, m->partial, 1, sh[3].N, sh[3].K, nullptr, dpk_gemv_q4k_fast_ok(sh[3].N, sh[3].K));
       } else {
         const uint8_t *W[4] = {(const uint8_t *)L.qkv->dptr, (const uint8_t *)L.o->dptr, (const uint8_t *)L.gateup->dptr,
