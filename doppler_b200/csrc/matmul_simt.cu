@@ -281,8 +281,9 @@ __global__ void __launch_bounds__(256) gemv_f16w_kernel(const __half *__restrict
   }
 }
 
-// M == 1, f32 activations: x is staged once per CTA in shared memory and the weight row is
-// streamed with four 16-byte loads in flight per lane.
+// M == 1, f32 activations: x is staged once per CTA in shared memory; a warp streams FOUR weight rows at a time
+// (four 16-byte loads in flight per lane and pass, two passes unrolled), so the shared-memory reads of x are
+// shared by four rows and the shuffle reduction is paid once per 32 KB of weights instead of once per 8 KB.
 template <typename OutT>
 __global__ void __launch_bounds__(256) gemv_f16w_m1_kernel(const __half *__restrict__ W, const float *__restrict__ x,
                                                            OutT *__restrict__ y, int N, int K, float alpha) {
@@ -293,24 +294,37 @@ __global__ void __launch_bounds__(256) gemv_f16w_m1_kernel(const __half *__restr
     reinterpret_cast<float4 *>(xs)[i] = __ldg(reinterpret_cast<const float4 *>(x) + i);
   __syncthreads();
   const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int row = blockIdx.x * warps + (threadIdx.x >> 5); row < N; row += gridDim.x * warps) {
-    const uint4 *wr = reinterpret_cast<const uint4 *>(W + (size_t)row * K);
-    float acc = 0.0f;
-    const int n16 = K / 8;
-#pragma unroll 4
+  const int n16 = K / 8;
+  for (int row0 = (blockIdx.x * warps + (threadIdx.x >> 5)) * 4; row0 < N; row0 += gridDim.x * warps * 4) {
+    const uint4 *wr[4];
+#pragma unroll
+    for (int r = 0; r < 4; r++) wr[r] = reinterpret_cast<const uint4 *>(W + (size_t)min(row0 + r, N - 1) * K);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 2
     for (int c = lane; c < n16; c += 32) {
-      const uint4 wv = __ldg(wr + c);
-      const __half2 *h = reinterpret_cast<const __half2 *>(&wv);
+      uint4 wv[4];
+#pragma unroll
+      for (int r = 0; r < 4; r++) wv[r] = __ldg(wr[r] + c);
       const float4 x0 = *reinterpret_cast<const float4 *>(xs + 8 * c), x1 = *reinterpret_cast<const float4 *>(xs + 8 * c + 4);
-      const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
-      acc = fmaf(f0.x, x0.x, acc); acc = fmaf(f0.y, x0.y, acc); acc = fmaf(f1.x, x0.z, acc); acc = fmaf(f1.y, x0.w, acc);
-      acc = fmaf(f2.x, x1.x, acc); acc = fmaf(f2.y, x1.y, acc); acc = fmaf(f3.x, x1.z, acc); acc = fmaf(f3.y, x1.w, acc);
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&wv[r]);
+        const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+        float a = acc[r];
+        a = fmaf(f0.x, x0.x, a); a = fmaf(f0.y, x0.y, a); a = fmaf(f1.x, x0.z, a); a = fmaf(f1.y, x0.w, a);
+        a = fmaf(f2.x, x1.x, a); a = fmaf(f2.y, x1.y, a); a = fmaf(f3.x, x1.z, a); a = fmaf(f3.y, x1.w, a);
+        acc[r] = a;
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-      const float v = acc * alpha;
-      if constexpr (sizeof(OutT) == 4) y[row] = v; else y[row] = __float2half_rn(v);
+    for (int r = 0; r < 4; r++) {
+      float a = acc[r];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0 && row0 + r < N) {
+        const float v = a * alpha;
+        if constexpr (sizeof(OutT) == 4) y[row0 + r] = v; else y[row0 + r] = __float2half_rn(v);
+      }
     }
   }
 }
@@ -334,7 +348,7 @@ static dp_status launch_f16w(dp_ctx *ctx, const __half *W, const AT *A, OutT *C,
 dp_status dpk_gemv_f16w(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
                         int N, int K, float alpha) {
   if (M == 1 && a_dtype == DP_F32 && K % 8 == 0 && (size_t)K * 4 <= 48 * 1024) {
-    int grid = (N + 7) / 8;
+    int grid = (N + 31) / 32;  // eight warps of four rows
     if (grid > ctx->sm_count * 8) grid = ctx->sm_count * 8;
     if (c_dtype == DP_F32) {
       DP_LAUNCH(ctx, gemv_f16w_m1_kernel<float>, grid, 256, (size_t)K * 4, W, (const float *)A, (float *)C, N, K, alpha);
