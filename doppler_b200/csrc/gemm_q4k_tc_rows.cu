@@ -70,6 +70,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                : "r"(taddr)
                : "memory");
 }
+// bounded wait that backs off between polls: for the drain warps, whose spinning would otherwise take issue slots
+// from the tile-building warps of the same schedulers
+__device__ __forceinline__ bool mbar_wait_bounded_backoff(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t i = 0; i < (1u << 20); i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(100);
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
 __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -376,7 +387,7 @@ __global__ void __launch_bounds__((DQW + 2) * 32, 1) gemm_q4k_tc_rows_kernel(con
       const uint32_t hd = hd_next;
       hd_next = fetch_hd(uj + 1);
       const int buf = uj & 1, g = uj * 2 + 1;
-      const bool ready = mbar_wait_bounded(done(g % STAGES), (uint32_t)(g / STAGES) & 1u, abort_flag);
+      const bool ready = mbar_wait_bounded_backoff(done(g % STAGES), (uint32_t)(g / STAGES) & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) break;  // tcgen05.ld is warp-wide: enter together or not at all
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int u = u0 + uj, tile = u / bpr, sb = u - tile * bpr;
