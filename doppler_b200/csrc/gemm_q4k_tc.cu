@@ -421,10 +421,15 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
   const uint32_t rank = cluster_ctarank();
   const int n0 = cluster_x < wide_tiles ? cluster_x * bn_wide : wide_tiles * bn_wide + (cluster_x - wide_tiles) * bn_narrow;
   const int m0 = blockIdx.y * (256 * PS);
+  // Split over K (grid.z parts of whole super-blocks, f32 output only): a problem of few pair tiles (N = 4096 at
+  // M = 1024 is 32) fills the GPU with several clusters per tile; part z writes its sums to C + z * M * N and
+  // splitk_reduce_kernel adds the parts in a fixed order.
+  const int k_splits = alpha.k_splits > 1 ? alpha.k_splits : 1;
   const int bpr_row = K / QK_K;
-  const int bpr = bpr_row, kb0 = 0;
+  const int bpr = bpr_row / k_splits, kb0 = (int)blockIdx.z * bpr;
   const int num_k = bpr * (QK_K / BK);
   const int rot_b = cluster_x % bpr;  // K rotation of this pair (see the one-SM kernel)
+  if (k_splits > 1) C += (size_t)blockIdx.z * (size_t)M * (size_t)N;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
   const uint32_t bars = smem_u32(smem + L.bars);
@@ -741,7 +746,7 @@ dp_status launch_tc_2sm(dp_ctx *ctx, const CUtensorMap &tm, const CUtensorMap &t
   auto kernel = gemm_q4k_tc2_kernel<BNMAX, OutT, SA, SB, CH, PS, NPROD>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), 1);
+  cfg.gridDim = dim3(2 * tiles, (M + 256 * PS - 1) / (256 * PS), alpha.k_splits > 1 ? alpha.k_splits : 1);
   cfg.blockDim = dim3((BNMAX / 16 + 2) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
@@ -774,6 +779,12 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const CUtensor
   // three waves of 55 tiles (53 x 224 + 2 x 208).  Tiles narrower than 128 columns are left to the one-SM
   // kernel (every SM re-reads its activation rows once per tile column, so narrow tiles are bound by L2).
   // Measurements of the alternatives that were tried and dropped: profiles/gemm_q4k_tc__config1.md.
+  if (M > 256 && alpha.k_splits > 1 && N % 256 == 0) {  // few pair tiles: uniform 256-wide tiles, several clusters per tile along K
+    const int cols = N / 256;
+    if constexpr (NPROD == 1) return launch_tc_2sm<OutT, 256, 3, 4, 2, 2, 1>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, 0, 256, 256);
+    else if constexpr (NPROD == 2) return launch_tc_2sm<OutT, 256, 3, 4, 2, 2, 2>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, 0, 256, 256);
+    else return launch_tc_2sm<OutT, 256, 2, 3, 1, 2, 3>(ctx, tm, tm_lo, W, C, M, N, K, alpha, cols, 0, 256, 256);
+  }
   if (M > 256 && N % 16 == 0) {
     const int clusters = ctx->sm_count / 2, rows = (M + 511) / 512;
     const int waves = (rows * ((N + 255) / 256) + clusters - 1) / clusters;
@@ -907,6 +918,17 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
     const int tiles = (N / bn) * ((M + (M <= 128 ? 127 : 255)) / (M <= 128 ? 128 : 256));
     const int sp = tc_k_splits(ctx, tiles, K);
     if (sp > 1) {
+      DP_TRY(dp_scratch(ctx, &ctx->gemm_split_scratch, (size_t)sp * M * N * 4, "matmul_k_split_parts"));
+      ta.k_splits = sp;
+      cdst = (float *)ctx->gemm_split_scratch->dptr;
+    }
+  } else if (r == CUDA_SUCCESS && c_dtype == DP_F32 && M > 256 && N % 256 == 0 && ((size_t)M * N) % 4 == 0) {
+    // two-SM kernel on few pair tiles (512 x 256): as many parts of K as keep the clusters within one wave
+    const int pair_tiles = ((M + 511) / 512) * (N / 256), clusters = ctx->sm_count / 2, bpr = K / QK_K;
+    int sp = 1;
+    for (int s2 = 2; s2 <= 8; s2++)
+      if (pair_tiles * s2 <= clusters && bpr % s2 == 0 && bpr / s2 >= 4) sp = s2;
+    if (sp > 1 && pair_tiles * 2 <= clusters) {
       DP_TRY(dp_scratch(ctx, &ctx->gemm_split_scratch, (size_t)sp * M * N * 4, "matmul_k_split_parts"));
       ta.k_splits = sp;
       cdst = (float *)ctx->gemm_split_scratch->dptr;
