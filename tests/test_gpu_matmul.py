@@ -278,6 +278,27 @@ def test_small_batch_gemm_weights_on_the_m_side(dev, M, N, K):
     assert_close(gotw, O.q4k_gemm_f16_weights(W, N, K, A16.astype(np.float32), M), "small-batch gemm, f16 activations, f16-rounded weights")
 
 
+def test_two_sm_gemm_split_over_k(dev):
+    """More than 256 rows on few 512 x 256 pair tiles (here two): the two-SM kernel runs several clusters per tile
+    along K, every part writes its own partial tile and the parts are added in a fixed order.  f32 activations
+    (three products per K step) against the exact product per row, a ragged row count, and the same bits twice."""
+    M, N, K = 300, 512, 4096
+    W = synthetic.q4k_matrix(synthetic.key(97, 0), N, K)
+    A = synthetic.normal_f32(synthetic.key(97, 1), M * K).reshape(M, K)
+    A = (A * (10.0 ** np.linspace(-2.0, 5.0, M).astype(np.float32))[:, None]).astype(np.float32)
+    exp = np.asarray(O.q4k_gemm(W, N, K, A.ravel(), M), np.float64).reshape(M, N)
+    l0 = dev.launch_count
+    got32 = _matmul(dev, W, N, K, A, M)
+    assert dev.launch_count - l0 == 3, "expected the scaling cast, one tensor-core kernel and the reduction of the K parts"
+    got = np.asarray(got32, np.float64).reshape(M, N)
+    rms = np.sqrt(np.mean(exp * exp, axis=1, keepdims=True))
+    gate = 2e-5 * (K / 2048.0) ** 0.5
+    ratio = np.abs(got - exp) / (gate * (np.abs(exp) + rms) + 1e-300)
+    print(f"[parity] two-SM gemm split over K [{M},{K}]x[{N},{K}]: worst per-row gate ratio {ratio.max():.3f}")
+    assert ratio.max() <= 1.0
+    assert np.array_equal(got32.view(np.uint32), _matmul(dev, W, N, K, A, M).view(np.uint32)), "not run-to-run deterministic"
+
+
 def test_few_tiles_long_k_is_deterministic(dev):
     """A problem of few output tiles and a long K (here two tiles, K = 4096) is split over K: several CTAs per
     tile take whole super-blocks each, write their own partial tile, and a second kernel adds the parts in a
