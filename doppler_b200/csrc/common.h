@@ -167,8 +167,15 @@ dp_status dpk_gemv_q4k(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, d
                        int N, int K, float alpha, const float *residual);
 dp_status dpk_gemm_q4k_simt(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C,
                             dp_dtype c_dtype, int M, int N, int K, float alpha);
+enum { DPK_ROWS_PRE_NONE = 0, DPK_ROWS_PRE_RMSNORM = 1, DPK_ROWS_PRE_SILU = 2 };
+struct dpk_rows_fuse {
+  int pre = 0;                      // operation on the input rows folded into the pre-pass
+  const float *norm_w = nullptr;    // DPK_ROWS_PRE_RMSNORM
+  float eps = 0.0f;
+  const float *residual = nullptr;  // added to the output [M, N] (may be the output buffer itself)
+};
 dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, float *C, int M, int N, int K, float alpha,
-                               bool *handled);
+                               bool *handled, const dpk_rows_fuse *fuse = nullptr);
 dp_status dpk_scale_cast_rows(dp_ctx *ctx, const float *A, __half *hi, __half *lo, float *row_scale, int M, int K);
 // f16 weights times 2..64+ activation rows, the weights streamed once (gemm_f16w_rows.cu)
 dp_status dpk_gemm_f16w_rows(dp_ctx *ctx, const __half *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M, int N, int K,

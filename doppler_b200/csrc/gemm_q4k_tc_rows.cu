@@ -64,12 +64,6 @@ struct RowsPlan {
   long units;
 };
 
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
 // bounded wait that backs off between polls: for the drain warps, whose spinning would otherwise take issue slots
 // from the tile-building warps of the same schedulers
 __device__ __forceinline__ bool mbar_wait_bounded_backoff(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -163,12 +157,114 @@ __global__ void __launch_bounds__(1024) rows_prepass_kernel(const AT *__restrict
   }
 }
 
-template <int BM, bool LO>
+// The same pre-pass with the operation that precedes the projection in the layer folded in (f32 rows, up to 32 of them).
+// One block per activation row.  f32 rows: the row is scaled by a power of two so that its largest magnitude
+// lands in [2^13, 2^14) and split into an f16 half and an f16 rounding residue (x * 2^-e = hi + lo to about 22
+// bits; row_scale receives 2^e for the epilogue).  Both kinds: the f32 sums of the (scaled) row over every
+// 32-wide sub-block, divided by 64, as f16 half and rounding residue: 16 halves per super-block.
+// PRE (f32 rows) applies the operation that precedes the projection in the layer, so that it costs no kernel
+// and no pass over global memory of its own:
+//   1  x = rmsnorm(in) * w      (rmsnorm.wgsl:119-187: x * 1/sqrt(mean(x^2) + eps) * w)
+//   2  x = silu(gate) * up      (silu.wgsl:98-104, sigmoid argument clamped to +-15); `in` rows hold 2K values,
+//                               eight gate values, then their eight up values, and so on
+// A thread keeps its share of the row (elements tid, tid + 1024, ...; up to PREPASS_MAXV of them, K <= 16384) in
+// registers, so the row is read from memory once whatever PRE is; a warp then holds 32 consecutive elements of
+// every round, i.e. one sub-block, and sums it with shuffles.
+constexpr int PREPASS_MAXV = 16;
+template <typename AT, int PRE>
+__global__ void __launch_bounds__(1024) rows_prepass_fused_kernel(const AT *__restrict__ in, __half *__restrict__ hi, __half *__restrict__ lo,
+                                                                  float *__restrict__ row_scale, __half *__restrict__ xs16, int K,
+                                                                  const float *__restrict__ norm_w, float eps) {
+  pdl_launch();
+  pdl_wait();
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const AT *x = in + (size_t)row * (PRE == 2 ? 2 * K : K);
+  __shared__ float wred[32];
+  const int rounds = K / 1024 + ((K % 1024) ? 1 : 0);
+  float v[PREPASS_MAXV];
+#pragma unroll
+  for (int j = 0; j < PREPASS_MAXV; j++) {
+    const int i = tid + j * 1024;
+    v[j] = 0.0f;
+    if (j < rounds && i < K) {
+      if constexpr (PRE == 2) {
+        const int gi = (i >> 3) * 16 + (i & 7);
+        const float g = (float)x[gi], u = (float)x[gi + 8];
+        const float cl = fminf(fmaxf(g, -15.0f), 15.0f);
+        v[j] = (g * (1.0f / (1.0f + expf(-cl)))) * u;
+      } else {
+        v[j] = (float)x[i];
+      }
+    }
+  }
+  if constexpr (PRE == 1) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PREPASS_MAXV; j++) ss = fmaf(v[j], v[j], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) wred[warp] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 32; w++) total += wred[w];
+    const float inv_rms = 1.0f / sqrtf(total / (float)K + eps);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < PREPASS_MAXV; j++) {
+      const int i = tid + j * 1024;
+      if (j < rounds && i < K) v[j] = v[j] * inv_rms * __ldg(norm_w + i);
+    }
+  }
+  float down = 1.0f;
+  if constexpr (sizeof(AT) == 4) {
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PREPASS_MAXV; j++) mx = fmaxf(mx, fabsf(v[j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) wred[warp] = mx;
+    __syncthreads();
+    mx = wred[0];
+#pragma unroll
+    for (int w = 1; w < 32; w++) mx = fmaxf(mx, wred[w]);
+    int e = 0;  // exponent of the row maximum (0 for an all-zero or non-finite row: no scaling)
+    if (mx > 0.0f && mx < __int_as_float(0x7f800000)) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 13;
+    e = max(-100, min(100, e));
+    down = __int_as_float((uint32_t)(127 - e) << 23);
+    if (tid == 0) row_scale[row] = __int_as_float((uint32_t)(127 + e) << 23);
+  }
+  const int nsub = K / 32;
+#pragma unroll
+  for (int j = 0; j < PREPASS_MAXV; j++) {
+    const int s = j * 32 + warp;  // the sub-block this warp holds in round j
+    if (j >= rounds || s >= nsub) continue;  // (warp-uniform)
+    float t = v[j];
+    if constexpr (sizeof(AT) == 4) {
+      t *= down;
+      const __half h = __float2half_rn(t);
+      hi[(size_t)row * K + s * 32 + lane] = h;
+      lo[(size_t)row * K + s * 32 + lane] = __float2half_rn(t - __half2float(h));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) {  // [row][super-block][8 halves | 8 residues]
+      const float q = t * 0.015625f;
+      const __half h = __float2half_rn(q);
+      __half *at = xs16 + ((size_t)row * (nsub >> 3) + (s >> 3)) * 16 + (s & 7);
+      at[0] = h;
+      at[8] = __float2half_rn(q - __half2float(h));
+    }
+  }
+}
+
+template <int BM, bool LO, bool RESID>
 __global__ void __launch_bounds__((DQW + 2) * 32, 1) gemm_q4k_tc_rows_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                               const __grid_constant__ CUtensorMap tmap_x_lo,
                                                                               const uint8_t *__restrict__ W, const __half *__restrict__ xs16,
                                                                               float *__restrict__ C, float *__restrict__ parts, int M, int N,
-                                                                              TcAlpha alpha, RowsPlan plan, int *__restrict__ err) {
+                                                                              TcAlpha alpha, RowsPlan plan, const float *__restrict__ residual,
+                                                                              int *__restrict__ err) {
   using L = RowsSmem<BM, LO>;
   static_assert(BM == 32 || BM == 64, "activation rows per MMA: 32 or 64");
   extern __shared__ uint8_t smem_raw[];
@@ -419,7 +515,11 @@ __global__ void __launch_bounds__((DQW + 2) * 32, 1) gemm_q4k_tc_rows_kernel(con
 #pragma unroll
         for (int i = 0; i < CW; i++) {
           const int m = half * CW + i;
-          if (m < M) dst[(size_t)m * pitch + quad * 32 + lane] = acc[i] * (alpha.row_scale ? alpha.value * __ldg(alpha.row_scale + m) : alpha.value);
+          if (m < M) {
+            float v = acc[i] * (alpha.row_scale ? alpha.value * __ldg(alpha.row_scale + m) : alpha.value);
+            if constexpr (RESID) if (whole) v += residual[(size_t)m * N + (size_t)tile * TILE_N + quad * 32 + lane];  // (may be C itself: same element, same thread)
+            dst[(size_t)m * pitch + quad * 32 + lane] = v;
+          }
           acc[i] = 0.0f;
         }
         seg++;
@@ -435,7 +535,8 @@ __global__ void __launch_bounds__((DQW + 2) * 32, 1) gemm_q4k_tc_rows_kernel(con
 
 // C[m, tile columns] = sum over the CTAs that share the tile, in CTA order, of their partial slots.  Tiles one CTA
 // computed alone were written to C by that CTA and are skipped.
-__global__ void __launch_bounds__(256) rows_reduce_kernel(const float *__restrict__ parts, float *__restrict__ C, int M, int N, RowsPlan plan) {
+__global__ void __launch_bounds__(256) rows_reduce_kernel(const float *__restrict__ parts, float *__restrict__ C, int M, int N, RowsPlan plan,
+                                                          const float *__restrict__ residual) {
   pdl_launch();
   pdl_wait();
   // one thread per four columns of a tile row; blockIdx.y = tile, so the owners are computed once per block
@@ -451,18 +552,22 @@ __global__ void __launch_bounds__(256) rows_reduce_kernel(const float *__restric
       const float4 v = *reinterpret_cast<const float4 *>(parts + ((size_t)c * plan.max_segs + seg) * (size_t)M * TILE_N + (size_t)m * TILE_N + n);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (residual) {
+      const float4 rv = *reinterpret_cast<const float4 *>(residual + (size_t)m * N + (size_t)tile * TILE_N + n);
+      acc.x += rv.x; acc.y += rv.y; acc.z += rv.z; acc.w += rv.w;
+    }
     *reinterpret_cast<float4 *>(C + (size_t)m * N + (size_t)tile * TILE_N + n) = acc;
   }
 }
 
-template <int BM, bool LO>
+template <int BM, bool LO, bool RESID>
 dp_status launch_rows(dp_ctx *ctx, const CUtensorMap *tm, const uint8_t *W, const __half *xs16, float *C, float *parts, int M, int N,
-                      TcAlpha alpha, const RowsPlan &plan) {
+                      TcAlpha alpha, const RowsPlan &plan, const float *residual) {
   constexpr size_t smem = RowsSmem<BM, LO>::total + 1024;
   static_assert(smem <= 227 * 1024, "rings exceed shared memory");
-  auto kernel = gemm_q4k_tc_rows_kernel<BM, LO>;
+  auto kernel = gemm_q4k_tc_rows_kernel<BM, LO, RESID>;
   DP_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  DP_LAUNCH(ctx, kernel, (unsigned)plan.ctas, (DQW + 2) * 32, smem, tm[0], tm[1], W, xs16, C, parts, M, N, alpha, plan, ctx->dev_status);
+  DP_LAUNCH(ctx, kernel, (unsigned)plan.ctas, (DQW + 2) * 32, smem, tm[0], tm[1], W, xs16, C, parts, M, N, alpha, plan, residual, ctx->dev_status);
   return DP_OK;
 }
 
@@ -470,10 +575,17 @@ dp_status launch_rows(dp_ctx *ctx, const CUtensorMap *tm, const uint8_t *W, cons
 
 // A: f32 (multiplied in as two f16 halves: the f32-exact product) or f16 activations [M, K].  The dequantised
 // weights enter exactly in both cases.  *handled stays false for shapes this kernel does not take.
+// fuse (optional): an operation on the f32 input rows folded into the pre-pass (DPK_ROWS_PRE_RMSNORM: A is the
+// un-normalised row, norm_w / eps the norm; DPK_ROWS_PRE_SILU: A rows hold 2K interleaved gate|up values) and a
+// residual added to the output (may be C itself).
 dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, float *C, int M, int N, int K, float alpha,
-                               bool *handled) {
+                               bool *handled, const dpk_rows_fuse *fuse) {
   *handled = false;
+  const int pre = fuse ? fuse->pre : 0;
+  const float *residual = fuse ? fuse->residual : nullptr;
+  if (pre && a_dtype != DP_F32) return DP_OK;
   if (M < 2 || M > 64 || N % TILE_N || K % QK_K || !ctx->dev_status) return DP_OK;
+  if (pre && K > 1024 * PREPASS_MAXV) return DP_OK;
   if (a_dtype != DP_F32 && a_dtype != DP_F16) return DP_OK;
   EncodeTiledFn encode = get_encode();
   if (!encode) return DP_OK;
@@ -498,7 +610,11 @@ dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_
   __half *xs16 = (__half *)(base + 2 * a_bytes);
   float *scales = (float *)(base + 2 * a_bytes + s_bytes);
   if (f32a) {
-    DP_LAUNCH(ctx, rows_prepass_kernel<float>, (unsigned)M, 1024, 0, (const float *)A, hi, lo, scales, xs16, K);
+    const float *nw = fuse ? fuse->norm_w : nullptr;
+    const float eps = fuse ? fuse->eps : 0.0f;
+    if (pre == DPK_ROWS_PRE_RMSNORM) DP_LAUNCH(ctx, (rows_prepass_fused_kernel<float, 1>), (unsigned)M, 1024, 0, (const float *)A, hi, lo, scales, xs16, K, nw, eps);
+    else if (pre == DPK_ROWS_PRE_SILU) DP_LAUNCH(ctx, (rows_prepass_fused_kernel<float, 2>), (unsigned)M, 1024, 0, (const float *)A, hi, lo, scales, xs16, K, nw, eps);
+    else DP_LAUNCH(ctx, rows_prepass_kernel<float>, (unsigned)M, 1024, 0, (const float *)A, hi, lo, scales, xs16, K);
   } else {
     DP_LAUNCH(ctx, rows_prepass_kernel<__half>, (unsigned)M, 1024, 0, (const __half *)A, (__half *)nullptr, (__half *)nullptr, (float *)nullptr, xs16, K);
     hi = (__half *)A;
@@ -518,12 +634,14 @@ dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_
   }
   const TcAlpha ta = {alpha, f32a ? scales : nullptr, 1};
   dp_status st;
-  if (bm == 32) st = f32a ? launch_rows<32, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan) : launch_rows<32, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan);
-  else st = f32a ? launch_rows<64, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan) : launch_rows<64, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan);
+  if (residual && f32a && bm == 32) st = launch_rows<32, true, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, residual);
+  else if (residual) return DP_OK;  // (the residual is folded in for up to 32 f32 rows only)
+  else if (bm == 32) st = f32a ? launch_rows<32, true, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr) : launch_rows<32, false, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr);
+  else st = f32a ? launch_rows<64, true, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr) : launch_rows<64, false, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr);
   if (st != DP_OK) return st;
   if (plan.units % plan.ctas != 0 || (plan.units / plan.ctas) % plan.bpr != 0) {  // some tile is shared between CTAs
     const int per_tile = M * (TILE_N / 4);
-    DP_LAUNCH(ctx, rows_reduce_kernel, dim3((unsigned)((per_tile + 255) / 256), (unsigned)plan.tiles), 256, 0, (const float *)parts, C, M, N, plan);
+    DP_LAUNCH(ctx, rows_reduce_kernel, dim3((unsigned)((per_tile + 255) / 256), (unsigned)plan.tiles), 256, 0, (const float *)parts, C, M, N, plan, residual);
   }
   *handled = true;
   return DP_OK;
