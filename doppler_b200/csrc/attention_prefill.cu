@@ -53,15 +53,19 @@ __global__ void __launch_bounds__(APF_THREADS, 1) attn_prefill_tc_kernel(dpk_att
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int QT = 16 * APF_WARPS / G;              // query positions per CTA
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // Causal tiles cost in proportion to their position, and blocks start in index order: hand the tiles out
+  // last (longest) first, all KV heads of a tile together, so the short ones fill the tail of the launch.
+  const int lin = blockIdx.x + gridDim.x * blockIdx.y;
+  const int kvh = lin % p.num_kv_heads, b = blockIdx.z;
+  const int qtile = (int)gridDim.x - 1 - lin / p.num_kv_heads;
   const int hh = warp % G, rb = warp / G;         // this warp: head hh of the group, 16-row block rb of the tile
   const int h = kvh * G + hh;
-  const int q0 = blockIdx.x * QT + rb * 16;       // first query row (within the call) of this warp
+  const int q0 = qtile * QT + rb * 16;       // first query row (within the call) of this warp
   const int rowA = q0 + g, rowB = q0 + g + 8;     // the two query rows this lane's accumulators belong to
   const int posA = p.start_pos + rowA, posB = p.start_pos + rowB;  // their absolute positions
   // keys this CTA needs: up to the position of its last query (and what the cache holds)
   int kv_len = p.kv_lens ? min(max(p.kv_lens[b], 0), p.kv_len) : p.kv_len;
-  const int last_q = min(blockIdx.x * QT + QT, p.seq_len) - 1;
+  const int last_q = min(qtile * QT + QT, p.seq_len) - 1;
   const int cta_keys = min(kv_len, p.start_pos + last_q + 1);
   const int warp_keys = min(kv_len, p.start_pos + min(q0 + 15, p.seq_len - 1) + 1);  // beyond this every key is masked for the warp
   const int n_tiles = (cta_keys + APF_KT - 1) / APF_KT;
