@@ -77,6 +77,8 @@ struct dp_model {
   float *am_vals; int *am_idx; float *am_best; int *am_pair_i; float *am_gather;
   dp_buf out_tokens = nullptr;
   int out_tokens_cap = 0;
+  int *pin_state = nullptr;   // page-locked staging of the per-call state block (1024 words) + the status word read back
+  int *pin_out = nullptr;     // page-locked staging of the decoded tokens (out_tokens_cap words)
   dp_buf attn_scratch = nullptr;
   dp_buf actq = nullptr;  // fixed-point activation digits of the decode GEMV (sized for the largest K)
   int attn_splits_decode = 1;
@@ -532,6 +534,8 @@ extern "C" void dp_model_destroy(dp_model *m) {
   rel(m->norms); rel(m->embed); rel(m->lm_head); rel(m->rope); rel(m->act); rel(m->state); rel(m->out_tokens); rel(m->attn_scratch); rel(m->actq);
   for (dp_buf b : m->kc) rel(b);
   for (dp_buf b : m->vc) rel(b);
+  if (m->pin_state) cudaFreeHost(m->pin_state);
+  if (m->pin_out) cudaFreeHost(m->pin_out);
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
   delete m;
@@ -1076,12 +1080,19 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
   if (m->out_tokens_cap < steps * batch) {
     if (m->out_tokens) { dp_buf_release(ctx, m->out_tokens); m->out_tokens = nullptr; }
     for (int i = 0; i < 2; i++) if (m->graph[i]) { dp_graph_destroy(m->graph[i]); m->graph[i] = nullptr; }
+    if (m->pin_out) { cudaFreeHost(m->pin_out); m->pin_out = nullptr; }
+    m->out_tokens_cap = 0;
     DP_TRY(dp_buf_acquire(ctx, (size_t)steps * batch * 4, "decode_out_tokens", &m->out_tokens));
+    DP_CUDA(ctx, cudaMallocHost(&m->pin_out, (size_t)steps * batch * 4));
     m->out_tokens_cap = steps * batch;
   }
-  std::vector<int> st(1024, 0);
+  if (!m->pin_state) DP_CUDA(ctx, cudaMallocHost(&m->pin_state, 4096 + 16));
+  // The state block goes up from page-locked memory without a synchronisation of its own: the previous call
+  // ended with a stream synchronisation, so the staging block is free, and the step's graph follows it in stream order.
+  int *st = m->pin_state;
+  memset(st, 0, 4096);
   for (int b = 0; b < batch; b++) { st[b] = m->seq_len[b]; st[256 + b] = m->seq_len[b] + 1; st[512 + b] = first_tokens[b]; }
-  DP_TRY(dp_buf_upload(ctx, m->state, st.data(), 0, 4096));
+  DP_CUDA(ctx, cudaMemcpyAsync(m->state->dptr, st, 4096, cudaMemcpyHostToDevice, ctx->stream));
   const int slot = 0;
   if (!m->graph[slot] || m->graph_batch[slot] != batch) {
     if (m->graph[slot]) { dp_graph_destroy(m->graph[slot]); m->graph[slot] = nullptr; }
@@ -1099,12 +1110,15 @@ extern "C" dp_status dp_model_decode(dp_model *m, int batch, const int32_t *firs
   DP_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
   for (int s = 0; s < steps; s++) DP_TRY(dp_graph_launch(m->graph[slot]));
   DP_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
-  DP_CUDA(ctx, cudaMemcpyAsync(out_tokens, m->out_tokens->dptr, (size_t)steps * batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  // tokens and the device status word come back together, one synchronisation per call
+  DP_CUDA(ctx, cudaMemcpyAsync(m->pin_out, m->out_tokens->dptr, (size_t)steps * batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  DP_CUDA(ctx, cudaMemcpyAsync(st + 1024, ctx->dev_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
   DP_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   float ms = 0;
   DP_CUDA(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
   m->last_ms = ms;
-  DP_TRY(dp_take_dev_status(ctx));  // a bounded device-side wait that gave up invalidates the tokens (DP_ERR_TIMEOUT)
+  if (st[1024]) DP_TRY(dp_take_dev_status(ctx));  // a bounded device-side wait that gave up invalidates the tokens (DP_ERR_TIMEOUT)
+  memcpy(out_tokens, m->pin_out, (size_t)steps * batch * 4);
   for (int b = 0; b < batch; b++) m->seq_len[b] += steps;
   return DP_OK;
 }
