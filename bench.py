@@ -247,7 +247,7 @@ def gemv_case(dev, ops, synthetic, N, K, copies, reps, peak):
     dev.release_buffer(x.buffer); dev.release_buffer(out); dev.pool_trim()
     return {"case": "q4k_gemv", "shape": [1, N, K], "us_per_call": dt * 1e6, "GBps": b / dt / 1e9, "frac_of_measured_hbm": b / dt / 1e9 / peak["hbm_gbs"],
             "algorithmic_bytes": b, "distinct_weight_copies": copies,
-            "note": "one call = activation digit pre-pass + GEMV kernel, graph of `copies` calls over distinct matrices"}
+            "note": "one call = dp_matmul of one f32 vector (one kernel: the digits are built in its prologue), graph of `copies` calls over distinct matrices"}
 
 
 def gemm_case(dev, ops, synthetic, M, N, K, copies, reps, peak, variant="default", adtype="f16"):

@@ -231,10 +231,10 @@ dp_status dpk_attention_prefill(dp_ctx *ctx, const dpk_attn_params &p) {
   const int G = p.num_heads / p.num_kv_heads;
   const int QT = 16 * APF_WARPS / G;
   const size_t smem = 2 * APF_STAGE;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static dp_per_device_once attr;
+  if (attr.pending(ctx->device)) {
     DP_CUDA(ctx, cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
+    attr.done(ctx->device);
   }
   dim3 grid((p.seq_len + QT - 1) / QT, p.num_kv_heads, p.batch);
   DP_LAUNCH(ctx, attn_prefill_tc_kernel, grid, APF_THREADS, smem, p, G);

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <atomic>
 #include <map>
 #include <string>
 #include <vector>
@@ -20,6 +21,14 @@ struct dp_buf_s {
   dp_ctx *ctx = nullptr;
   bool active = false;
   std::string label;
+};
+
+// A function attribute (the opt-in shared-memory size) is set per device: a kernel that sets it only on its first
+// launch keeps one of these, so that a second device used by the same process gets the attribute too.
+struct dp_per_device_once {
+  std::atomic<uint64_t> mask{0};
+  bool pending(int dev) const { return ((mask.load(std::memory_order_acquire) >> (dev & 63)) & 1ull) == 0; }
+  void done(int dev) { mask.fetch_or(1ull << (dev & 63), std::memory_order_release); }
 };
 
 struct dp_tp_state;     // tp.cu

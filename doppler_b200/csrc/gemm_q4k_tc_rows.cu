@@ -591,6 +591,7 @@ dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_
   if (!encode) return DP_OK;
   const int bm = M <= 32 ? 32 : 64;
   const bool f32a = a_dtype == DP_F32;
+  if (residual && !(f32a && bm == 32)) return DP_OK;  // the residual is folded in for up to 32 f32 rows only (nothing launched yet)
   RowsPlan plan;
   plan.tiles = N / TILE_N;
   plan.bpr = K / QK_K;
@@ -634,8 +635,7 @@ dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_
   }
   const TcAlpha ta = {alpha, f32a ? scales : nullptr, 1};
   dp_status st;
-  if (residual && f32a && bm == 32) st = launch_rows<32, true, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, residual);
-  else if (residual) return DP_OK;  // (the residual is folded in for up to 32 f32 rows only)
+  if (residual) st = launch_rows<32, true, true>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, residual);
   else if (bm == 32) st = f32a ? launch_rows<32, true, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr) : launch_rows<32, false, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr);
   else st = f32a ? launch_rows<64, true, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr) : launch_rows<64, false, false>(ctx, tm, W, xs16, C, parts, M, N, ta, plan, nullptr);
   if (st != DP_OK) return st;

@@ -172,10 +172,21 @@ size_t dpk_q4k_actq_bytes(int K) { return actq_bytes(K); }
 
 bool dpk_gemv_q4k_fast_ok(int N, int K) { return N > 0 && K > 0 && (K % QK_K) == 0 && (N % 16) == 0; }
 
+struct GemvExchange;
+dp_status dpk_gemv_q4k_tma_fused(dp_ctx *ctx, const uint8_t *W, int mode, const float *x, const float *w, float eps, int D,
+                                 int splits, float *y, int N, int K, const float *residual, bool *handled, const GemvExchange *gxp);
+
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
                             float alpha, const float *residual, bool *handled) {
   *handled = false;
   if (!dpk_gemv_q4k_fast_ok(N, K) || (y_dtype != DP_F32 && y_dtype != DP_F16)) return DP_OK;
+  // One launch when the shape has a TMA plan: the kernel splits the f32 vector into digits in its own prologue
+  // (the same digits the pre-pass below writes), which is what a launch-bound GEMV of a couple of MB is made of.
+  if (y_dtype == DP_F32 && alpha == 1.0f && ((uintptr_t)x & 15u) == 0) {
+    bool one = false;
+    DP_TRY(dpk_gemv_q4k_tma_fused(ctx, W, 5 /* SRC_PLAIN */, x, nullptr, 0.0f, 0, 0, (float *)y, N, K, residual, &one, nullptr));
+    if (one) { *handled = true; return DP_OK; }
+  }
   DP_TRY(dp_scratch(ctx, &ctx->gemv_scratch, actq_bytes(K), "gemv_activation_digits"));
   DP_TRY(dpk_q4k_prep_act(ctx, x, ctx->gemv_scratch->dptr, K));
   bool tma = false;
@@ -667,10 +678,10 @@ static dp_status launch_tma(dp_ctx *ctx, const uint8_t *W, const int8_t *limbs, 
   const float *xscale = limbs ? (const float *)(limbs + (size_t)K * 4) : nullptr;
   const float *ssum = limbs ? xscale + K / QK_K : nullptr;
   const int grid = N / 16 < ctx->sm_count ? N / 16 : ctx->sm_count;
-  static bool attr_set = false;  // per instantiation
-  if (!attr_set) {
+  static dp_per_device_once attr;  // per instantiation
+  if (attr.pending(ctx->device)) {
     DP_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH, SILU_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
+    attr.done(ctx->device);
   }
   DP_LAUNCH(ctx, (gemv_q4k_tma_kernel<OutT, GROUPS, SRC, PUSH, SILU_OUT>), grid, (GROUPS * TG_CONSUMERS + 1) * 32, smem, W, limbs, xscale, ssum, y,
             N, K, cb, stages, alpha, residual, ctx->dev_status, gs, gx);
