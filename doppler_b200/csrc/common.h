@@ -183,6 +183,17 @@ struct dpk_rows_fuse {
   float eps = 0.0f;
   const float *residual = nullptr;  // added to the output [M, N] (may be the output buffer itself)
 };
+// Optional fusions of the row-scaled tensor-core GEMM (f32 in, f32 out).  The caller asks by filling the pointers;
+// the *_done flags say what the launch took over, the rest stays with the caller.
+struct dpk_tc_fuse {
+  float *silu_dst = nullptr;        // [M, N / 2]: silu(gate) * up of gate|up column pairs, stored by the epilogue instead of C
+  const float *residual = nullptr;  // added by the fixed-order reduction of a K-split launch ...
+  float *residual_out = nullptr;    // ... which then writes here (may be the residual itself) instead of C
+  bool silu_done = false, residual_done = false;
+};
+dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
+                                    bool *handled, dpk_tc_fuse *fuse = nullptr);
+
 dp_status dpk_gemm_q4k_tc_rows(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, float *C, int M, int N, int K, float alpha,
                                bool *handled, const dpk_rows_fuse *fuse = nullptr);
 dp_status dpk_scale_cast_rows(dp_ctx *ctx, const float *A, __half *hi, __half *lo, float *row_scale, int M, int K);

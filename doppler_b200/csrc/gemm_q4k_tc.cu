@@ -321,7 +321,14 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
             tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * BN + cg * 32), r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             uint8_t *dst = stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 32u * (uint32_t)sizeof(OutT);
-            if constexpr (sizeof(OutT) == 4) {
+            if (sizeof(OutT) == 4 && alpha.silu_out) {
+              float o[16];
+              tc_silu_group(r, arow, o);
+              tc_silu_group(r + 16, arow, o + 8);
+              float4 *d4 = reinterpret_cast<float4 *>(stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 64u);
+#pragma unroll
+              for (int i = 0; i < 4; i++) d4[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            } else if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
                 *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow,
@@ -342,15 +349,17 @@ __global__ void __launch_bounds__((DQ_WARPS + 2) * 32, 1) gemm_q4k_tc_kernel(con
         }
         asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the tile of these 128 rows is staged
         if (go) {
-          constexpr int cpr = (int)(row_bytes >> 4);  // 16-byte chunks per row
-          constexpr int total = 128 * cpr;
-          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * N + n0);
+          const int fold = (sizeof(OutT) == 4 && alpha.silu_out) ? 2 : 1;  // silu(gate) * up: half the columns
+          const int cpr = (int)(row_bytes >> 4) / fold;  // 16-byte chunks per row
+          const int total = 128 * cpr;
+          const size_t n_out = (size_t)(N / fold);
+          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * n_out + (size_t)(n0 / fold));
 #pragma unroll 2
           for (int c = et; c < total; c += ET) {
             const int lrow = c / cpr, ch = c - lrow * cpr;
             if (row0 + lrow >= M) break;  // rows grow with c
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
-            char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
+            char *g = cbase + (size_t)lrow * n_out * sizeof(OutT) + ((size_t)ch << 4);
             *reinterpret_cast<uint4 *>(g) = v;
           }
         }
@@ -631,7 +640,13 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
             tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ps * BNMAX + cg * 16), r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             uint8_t *dst = stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 16u * (uint32_t)sizeof(OutT);
-            if constexpr (sizeof(OutT) == 4) {
+            if (sizeof(OutT) == 4 && alpha.silu_out) {
+              float o[8];
+              tc_silu_group(r, arow, o);
+              float4 *d4 = reinterpret_cast<float4 *>(stage + (uint32_t)lrow * row_pitch + (uint32_t)cg * 32u);
+              d4[0] = make_float4(o[0], o[1], o[2], o[3]);
+              d4[1] = make_float4(o[4], o[5], o[6], o[7]);
+            } else if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
               for (int i = 0; i < 16; i += 4)
                 *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(__uint_as_float(r[i]) * arow, __uint_as_float(r[i + 1]) * arow,
@@ -652,15 +667,17 @@ __global__ void __launch_bounds__((BNMAX / 16 + 2) * 32, 1) gemm_q4k_tc2_kernel(
         }
         asm volatile("bar.sync 1, %0;" ::"r"(ET) : "memory");  // the pass's tile is staged
         if (go) {
-          const int cpr = (int)(row_bytes >> 4);  // 16-byte chunks per row
+          const int fold = (sizeof(OutT) == 4 && alpha.silu_out) ? 2 : 1;  // silu(gate) * up: half the columns
+          const int cpr = (int)(row_bytes >> 4) / fold;  // 16-byte chunks per row
           const int total = 128 * cpr;
-          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * N + n0);
+          const size_t n_out = (size_t)(N / fold);
+          char *cbase = reinterpret_cast<char *>(C + (size_t)row0 * n_out + (size_t)(n0 / fold));
 #pragma unroll 2
           for (int c = et; c < total; c += ET) {
             const int lrow = c / cpr, ch = c - lrow * cpr;
             if (row0 + lrow >= M) break;  // rows grow with c
             uint4 v = *reinterpret_cast<const uint4 *>(stage + (uint32_t)lrow * row_pitch + ((uint32_t)ch << 4));
-            char *g = cbase + (size_t)lrow * N * sizeof(OutT) + ((size_t)ch << 4);
+            char *g = cbase + (size_t)lrow * n_out * sizeof(OutT) + ((size_t)ch << 4);
             *reinterpret_cast<uint4 *>(g) = v;
           }
         }
@@ -834,7 +851,8 @@ dp_status dispatch_tc(dp_ctx *ctx, int bn, const CUtensorMap &tm, const CUtensor
 }  // namespace
 
 // C = sum of the `splits` partial tiles of a K-split launch, added in a fixed order
-__global__ void splitk_reduce_kernel(const float *__restrict__ parts, float *__restrict__ C, size_t n, int splits) {
+// (+ residual, which may be C itself: every element is read and written by the same thread)
+__global__ void splitk_reduce_kernel(const float *__restrict__ parts, float *C, size_t n, int splits, const float *residual) {
   pdl_launch();
   pdl_wait();
   for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
@@ -843,12 +861,16 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ parts, float *__r
       const float4 v = *reinterpret_cast<const float4 *>(parts + (size_t)z * n + i);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (residual) {
+      const float4 v = *reinterpret_cast<const float4 *>(residual + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
     *reinterpret_cast<float4 *>(C + i) = acc;
   }
 }
 
 static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype, int M,
-                                  int N, int K, float alpha, int mode, bool *handled) {
+                                  int N, int K, float alpha, int mode, bool *handled, dpk_tc_fuse *fuse = nullptr) {
   // mode 0: A as given (f32 is cast to f16), weights rounded to f16: one product per K step.
   //      1: f32 rows scaled into f16 range, weights rounded to f16: one product.
   //      2: as 1, three products per K step into the one accumulator, A_hi.W_hi + A_hi.W_lo + A_lo.W_hi with the f16
@@ -910,7 +932,7 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
     r = encode(&tm_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)(a_lo ? a_lo : a16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   dp_status st = DP_OK;
-  TcAlpha ta = {alpha, scales, 1};
+  TcAlpha ta = {alpha, scales, 1, 0};
   // few output tiles (one-SM kernel, f32 output): split K over several CTAs per tile, partial tiles in a scratch
   // of the context, summed in a fixed order afterwards
   float *cdst = (float *)C;
@@ -934,6 +956,23 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
       cdst = (float *)ctx->gemm_split_scratch->dptr;
     }
   }
+  // Optional fusions (f32 output): silu(gate) * up in the epilogue of an unsplit launch, written to fuse->silu_dst
+  // [M, N / 2] instead of C; a residual added by the reduction that follows a K-split launch, written to
+  // fuse->residual_out (which may be the residual itself).  What was not fused is left to the caller.
+  float *c_final = (float *)C;
+  const float *red_residual = nullptr;
+  if (fuse && r == CUDA_SUCCESS && c_dtype == DP_F32) {
+    if (fuse->silu_dst && ta.k_splits == 1 && N % 32 == 0) {
+      ta.silu_out = 1;
+      cdst = fuse->silu_dst;
+      fuse->silu_done = true;
+    }
+    if (fuse->residual && fuse->residual_out && ta.k_splits > 1) {
+      red_residual = fuse->residual;
+      c_final = fuse->residual_out;
+      fuse->residual_done = true;
+    }
+  }
   if (r != CUDA_SUCCESS) {
     st = dp_fail(ctx, DP_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed (%d) for A[%d,%d]", (int)r, M, K);
   } else if (c_dtype == DP_F32) {
@@ -944,7 +983,7 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
       const size_t n = (size_t)M * N;
       size_t grid = (n / 4 + 255) / 256;
       if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
-      DP_LAUNCH(ctx, splitk_reduce_kernel, (unsigned)grid, 256, 0, (const float *)cdst, (float *)C, n, ta.k_splits);
+      DP_LAUNCH(ctx, splitk_reduce_kernel, (unsigned)grid, 256, 0, (const float *)cdst, c_final, n, ta.k_splits, red_residual);
     }
   } else if (c_dtype == DP_F16) {
     if (mode == 3) st = dispatch_tc<__half, 2>(ctx, bn, tm, tm_lo, W, (__half *)C, M, N, K, ta);
@@ -976,6 +1015,7 @@ dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype
 // residues of both are multiplied in as well (three products per K step in one kernel), which gives the
 // f32-exact product to f32 accuracy.
 dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,
-                                    bool *handled) {
-  return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, alpha, passes == 3 ? 2 : 1, handled);
+                                    bool *handled, dpk_tc_fuse *fuse) {
+  if (fuse) fuse->silu_done = fuse->residual_done = false;
+  return gemm_q4k_tc_impl(ctx, W, A, DP_F32, C, DP_F32, M, N, K, alpha, passes == 3 ? 2 : 1, handled, fuse);
 }

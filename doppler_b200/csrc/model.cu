@@ -27,7 +27,6 @@
 #include <cstring>
 #include <vector>
 
-dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes, bool *handled);
 dp_status dpk_gemm_q4k_tc(dp_ctx *ctx, const uint8_t *W, const void *A, dp_dtype a_dtype, void *C, dp_dtype c_dtype,
                           int M, int N, int K, float alpha, bool f16_weights, bool *handled);
 dp_status dpk_gemv_q4k_fast(dp_ctx *ctx, const uint8_t *W, const float *x, void *y, dp_dtype y_dtype, int N, int K,
@@ -655,8 +654,10 @@ extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
 }
 
 // ---- the schedule ---------------------------------------------------------------------
+// silu_dst / silu_done (rows of gate|up pairs, M >= 2): the tensor-core GEMM may store silu(gate) * up, [M, N / 2], to
+// silu_dst instead of y; *silu_done says whether it did.
 static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float *y, int M, int N, int K,
-                            const float *residual, bool digits_ready = false) {
+                            const float *residual, bool digits_ready = false, float *silu_dst = nullptr, bool *silu_done = nullptr) {
   dp_ctx *ctx = m->ctx;
   if (M == 1) {
     if (dpk_gemv_q4k_fast_ok(N, K)) {
@@ -685,9 +686,13 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   bool handled = false;
   // (batched decode steps recorded into a CUDA graph take the same path: the f16 scratch belongs to the
   // context and is never recycled while a graph is alive)
-  if (prefill_tc && M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled));
+  dpk_tc_fuse f;
+  f.silu_dst = silu_dst;
+  if (residual) { f.residual = residual; f.residual_out = y; }  // a K-split launch adds it in its reduction, in place
+  if (prefill_tc && M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled, &f));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
-  if (residual) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
+  if (silu_done) *silu_done = handled && f.silu_done;
+  if (residual && !(handled && f.residual_done)) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
   return DP_OK;
 }
 
@@ -938,6 +943,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
     // ---- gate | up ----
     done = false;
     bool act_ready = false;  // the gate|up kernel stored silu(gate) * up itself
+    bool act_rows_ready = false;  // ... and so did the tensor-core GEMM of a multi-row pass
     if (single) {
       if (m->inter % QK_K == 0 && dpk_gemv_q4k_fast_ok(H, m->inter)) {
         DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.gateup->dptr, SRC_RMSNORM | SRC_FLAG_SILU_OUT, m->h, L.post_norm, c.eps, 0, 0, m->actv,
@@ -960,7 +966,9 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       } else {
         DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
       }
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, emit));
+      // (rows on the tensor-core kernel: its epilogue stores silu(gate) * up and the raw gate|up rows are never written)
+      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, emit,
+                        (!single && p == 1) ? m->actv : nullptr, &act_rows_ready));
     }
     // ---- silu(gate) * up, down ----
     float *d_dst = p == 1 ? m->h : m->partial;
@@ -971,7 +979,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       if (!done) return dp_fail(ctx, DP_ERR_STATE, "decode schedule: down_proj cannot read the fused silu(gate) * up vector");
     } else if (single && m->inter % QK_K == 0)
       DP_TRY(dpk_gemv_q4k_tma_fused(ctx, (const uint8_t *)L.down->dptr, SRC_SILU, m->gu, nullptr, 0.0f, 0, 0, d_dst, H, m->inter, d_res, &done));
-    if (!done && !single && p == 1) {  // silu(gate) * up in the pre-pass, h += down_proj(...) in the epilogue
+    if (!done && !single && p == 1 && !act_rows_ready) {  // silu(gate) * up in the pre-pass, h += down_proj(...) in the epilogue
       dpk_rows_fuse f;
       f.pre = DPK_ROWS_PRE_SILU; f.residual = m->h;
       DP_TRY(rows_linear_fused(m, (const uint8_t *)L.down->dptr, m->gu, m->h, tokens, H, m->inter, f, &done));
@@ -981,7 +989,7 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       if (emit) {
         const int blocks = m->inter / QK_K;
         DP_LAUNCH(ctx, silu_actq_kernel, (blocks + 7) / 8, 256, 0, (const float *)m->gu, m->actv, m->actq->dptr, m->inter);
-      } else {
+      } else if (!act_rows_ready) {
         const size_t total = (size_t)tokens * m->inter;
         size_t grid = (total + 255) / 256;
         if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;

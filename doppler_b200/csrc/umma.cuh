@@ -103,7 +103,20 @@ struct TcAlpha {
   float value;
   const float *row_scale;
   int k_splits;  // one-SM kernel: parts of K per output tile (grid.z); part z writes its f32 sums to C + z * M * N
+  // f32 output, k_splits == 1: the columns are gate|up pairs (eight gate columns, then their eight up columns, per
+  // group of sixteen) and the epilogue stores silu(gate) * up, N / 2 columns per row, instead of the N raw ones
+  int silu_out;
 };
+
+// silu(gate) * up of one group of sixteen accumulator columns (silu.wgsl:30-37,98-104: sigmoid argument clamped to +-15)
+__device__ __forceinline__ void tc_silu_group(const uint32_t *r, float arow, float *o) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float g = __uint_as_float(r[j]) * arow, u = __uint_as_float(r[8 + j]) * arow;
+    const float cl = fminf(fmaxf(g, -15.0f), 15.0f);
+    o[j] = (g * (1.0f / (1.0f + expf(-cl)))) * u;
+  }
+}
 
 // Two dequantised weights as f16, and (NPROD >= 2) their f16 rounding residues w - f16(w): the part of each
 // weight that the rounding drops, which a second product adds back.
