@@ -189,6 +189,8 @@ struct dpk_tc_fuse {
   float *silu_dst = nullptr;        // [M, N / 2]: silu(gate) * up of gate|up column pairs, stored by the epilogue instead of C
   const float *residual = nullptr;  // added by the fixed-order reduction of a K-split launch ...
   float *residual_out = nullptr;    // ... which then writes here (may be the residual itself) instead of C
+  const float *norm_w = nullptr;    // RMSNorm weights: A holds the un-normalised rows and the norm is folded into their conversion to f16
+  float eps = 0.0f;                 //   (the call is left unhandled, nothing launched, where that conversion cannot take it)
   bool silu_done = false, residual_done = false;
 };
 dp_status dpk_gemm_q4k_tc_rowscaled(dp_ctx *ctx, const uint8_t *W, const float *A, float *C, int M, int N, int K, float alpha, int passes,

@@ -734,6 +734,96 @@ __global__ void __launch_bounds__(256) scale_cast_rows_kernel(const float *__res
   if (threadIdx.x == 0) row_scale[blockIdx.x] = up;
 }
 
+// The same conversion with the row kept in registers (K % 4 == 0, K <= 1024 * NV): one pass over the input, 16-byte
+// loads, 8-byte stores.  With norm_w the row is RMS-normalised first (rmsnorm.wgsl:119-187), element for element and
+// reduction step for reduction step as rmsnorm_vec_kernel (small_ops.cu) does it for rows of 1024..4096 values, so
+// the halves are the ones the two separate kernels produce.
+__device__ __forceinline__ float sc_block_sum(float v, float *sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float t = (lane < 8) ? sh[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  __syncthreads();
+  return t;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) scale_cast_rows_vec_kernel(const float *__restrict__ in, __half *__restrict__ out, __half *__restrict__ out_lo,
+                                                                  float *__restrict__ row_scale, int K, const float *__restrict__ norm_w, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sh[32];
+  const size_t base = (size_t)blockIdx.x * K;
+  const int n4 = K >> 2;
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int idx = threadIdx.x + i * 256;
+    v[i] = idx < n4 ? *reinterpret_cast<const float4 *>(in + base + 4 * idx) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+  if (norm_w) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+    const float total = sc_block_sum(ss, sh);
+    const float inv_rms = 1.0f / sqrtf(total / (float)K + eps);
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < n4) {
+        const float4 w = *reinterpret_cast<const float4 *>(norm_w + 4 * idx);
+        v[i].x = v[i].x * inv_rms * w.x; v[i].y = v[i].y * inv_rms * w.y; v[i].z = v[i].z * inv_rms * w.z; v[i].w = v[i].w * inv_rms * w.w;
+      }
+    }
+  }
+  float mx = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = sh[0];
+#pragma unroll
+  for (int w = 1; w < 8; w++) mx = fmaxf(mx, sh[w]);
+  int e = 0;  // exponent of the row maximum (0 for an all-zero or non-finite row: no scaling), as in scale_cast_rows_kernel
+  if (mx > 0.0f && mx < __int_as_float(0x7f800000)) e = (int)((__float_as_uint(mx) >> 23) & 0xffu) - 127 - 13;
+  e = max(-100, min(100, e));
+  const float down = __int_as_float((uint32_t)(127 - e) << 23), up = __int_as_float((uint32_t)(127 + e) << 23);
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx >= n4) continue;
+    const float s0 = v[i].x * down, s1 = v[i].y * down, s2 = v[i].z * down, s3 = v[i].w * down;
+    const __half2 h01 = __halves2half2(__float2half_rn(s0), __float2half_rn(s1)), h23 = __halves2half2(__float2half_rn(s2), __float2half_rn(s3));
+    *reinterpret_cast<uint2 *>(out + base + 4 * idx) = make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
+    if (out_lo) {
+      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+      const __half2 l01 = __halves2half2(__float2half_rn(s0 - f01.x), __float2half_rn(s1 - f01.y));
+      const __half2 l23 = __halves2half2(__float2half_rn(s2 - f23.x), __float2half_rn(s3 - f23.y));
+      *reinterpret_cast<uint2 *>(out_lo + base + 4 * idx) = make_uint2(*reinterpret_cast<const uint32_t *>(&l01), *reinterpret_cast<const uint32_t *>(&l23));
+    }
+  }
+  if (threadIdx.x == 0) row_scale[blockIdx.x] = up;
+}
+
+static dp_status launch_scale_cast(dp_ctx *ctx, const float *A, __half *hi, __half *lo, float *row_scale, int M, int K, const float *norm_w, float eps) {
+  if (K % 4 == 0 && K <= 16384 && (((uintptr_t)A | (uintptr_t)hi | (uintptr_t)lo) & 15) == 0 && (!norm_w || (((uintptr_t)norm_w & 15) == 0 && K <= 4096))) {
+    if (K <= 4096) DP_LAUNCH(ctx, scale_cast_rows_vec_kernel<4>, (unsigned)M, 256, 0, A, hi, lo, row_scale, K, norm_w, eps);
+    else if (K <= 8192) DP_LAUNCH(ctx, scale_cast_rows_vec_kernel<8>, (unsigned)M, 256, 0, A, hi, lo, row_scale, K, norm_w, eps);
+    else if (K <= 12288) DP_LAUNCH(ctx, scale_cast_rows_vec_kernel<12>, (unsigned)M, 256, 0, A, hi, lo, row_scale, K, norm_w, eps);
+    else DP_LAUNCH(ctx, scale_cast_rows_vec_kernel<16>, (unsigned)M, 256, 0, A, hi, lo, row_scale, K, norm_w, eps);
+    return DP_OK;
+  }
+  if (norm_w) return dp_fail(ctx, DP_ERR_STATE, "matmul: the fused RMSNorm needs rows of 1024..4096 values");
+  DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, A, hi, lo, row_scale, K);
+  return DP_OK;
+}
+
 template <int BN, int DQ_WARPS, typename OutT, int SA, int SB, int MT, int NPROD>
 dp_status launch_tc(dp_ctx *ctx, const CUtensorMap &tm, const CUtensorMap &tm_lo, const uint8_t *W, OutT *C, int M, int N, int K, TcAlpha alpha) {
   constexpr size_t smem = tc_layout(BN, SA, SB, MT, NPROD).total + 1024;
@@ -891,6 +981,10 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
   EncodeTiledFn encode = get_encode();
   if (!encode) return DP_OK;
   if (mode == 3 && a_dtype != DP_F16) return DP_OK;
+  // an RMSNorm folded into the activation conversion: row-scaled f32 rows of 1024..4096 values on the kernels below only
+  if (fuse && fuse->norm_w && !(row_scaled && a_dtype == DP_F32 && c_dtype == DP_F32 && M > 64 && K % 4 == 0 && K >= 1024 && K <= 4096 &&
+                                 ((uintptr_t)fuse->norm_w & 15) == 0 && ((uintptr_t)A & 15) == 0))
+    return DP_OK;
   // up to 64 rows, f32 out, exact weights (modes 2 and 3): the integer-tile kernel (gemm_q4k_tc_rows.cu)
   if (M <= 64 && c_dtype == DP_F32 && ((mode == 2 && a_dtype == DP_F32) || mode == 3)) {
     DP_TRY(dpk_gemm_q4k_tc_rows(ctx, W, A, a_dtype, (float *)C, M, N, K, alpha, handled));
@@ -911,8 +1005,8 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
     if (row_scaled) {
       if (mode == 2) a_lo = (const __half *)(base + a_bytes);
       scales = (const float *)(base + 2 * a_bytes);
-      DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, (const float *)A, (__half *)base, mode == 2 ? (__half *)(base + a_bytes) : (__half *)nullptr,
-                (float *)(base + 2 * a_bytes), K);
+      DP_TRY(launch_scale_cast(ctx, (const float *)A, (__half *)base, mode == 2 ? (__half *)(base + a_bytes) : (__half *)nullptr,
+                               (float *)(base + 2 * a_bytes), M, K, fuse ? fuse->norm_w : nullptr, fuse ? fuse->eps : 0.0f));
     } else {
       size_t n = (size_t)M * K, grid = (n + 255) / 256;
       if (grid > (size_t)ctx->sm_count * 16) grid = (size_t)ctx->sm_count * 16;
@@ -997,8 +1091,7 @@ static dp_status gemm_q4k_tc_impl(dp_ctx *ctx, const uint8_t *W, const void *A, 
 
 // f32 rows -> f16 halves, rounding residues and per-row inverse scales (see scale_cast_rows_kernel); lo may be null.
 dp_status dpk_scale_cast_rows(dp_ctx *ctx, const float *A, __half *hi, __half *lo, float *row_scale, int M, int K) {
-  DP_LAUNCH(ctx, scale_cast_rows_kernel, (unsigned)M, 256, 0, A, hi, lo, row_scale, K);
-  return DP_OK;
+  return launch_scale_cast(ctx, A, hi, lo, row_scale, M, K, nullptr, 0.0f);
 }
 
 // f16 (or f32, cast to f16) activations.  f16_weights: one product with the dequantised weights rounded to f16,

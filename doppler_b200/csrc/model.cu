@@ -656,9 +656,17 @@ extern "C" dp_status dp_model_set_allreduce_mode(dp_model *m, int mode) {
 // ---- the schedule ---------------------------------------------------------------------
 // silu_dst / silu_done (rows of gate|up pairs, M >= 2): the tensor-core GEMM may store silu(gate) * up, [M, N / 2], to
 // silu_dst instead of y; *silu_done says whether it did.
+// norm_w / eps: x holds un-normalised rows and y = q4k_linear(rmsnorm(x, norm_w, eps)); the multi-row tensor-core path
+// folds the norm into its conversion of the rows, every other path runs it as a kernel of its own into m->n.
 static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float *y, int M, int N, int K,
-                            const float *residual, bool digits_ready = false, float *silu_dst = nullptr, bool *silu_done = nullptr) {
+                            const float *residual, bool digits_ready = false, float *silu_dst = nullptr, bool *silu_done = nullptr,
+                            const float *norm_w = nullptr, float eps = 0.0f) {
   dp_ctx *ctx = m->ctx;
+  if (norm_w && M == 1) {
+    DP_TRY(dpk_rmsnorm(ctx, x, norm_w, false, nullptr, false, nullptr, m->n, M, K, eps, false, 1.0f));
+    x = m->n;
+    norm_w = nullptr;
+  }
   if (M == 1) {
     if (dpk_gemv_q4k_fast_ok(N, K)) {
       if (!digits_ready) DP_TRY(dpk_q4k_prep_act(ctx, x, m->actq->dptr, K));
@@ -689,7 +697,18 @@ static dp_status q4k_linear(dp_model *m, const uint8_t *W, const float *x, float
   dpk_tc_fuse f;
   f.silu_dst = silu_dst;
   if (residual) { f.residual = residual; f.residual_out = y; }  // a K-split launch adds it in its reduction, in place
-  if (prefill_tc && M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled, &f));
+  if (norm_w) {
+    if (prefill_tc) {
+      f.norm_w = norm_w; f.eps = eps;
+      DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled, &f));
+      f.norm_w = nullptr;
+    }
+    if (!handled) {  // (nothing was launched): the norm as a kernel of its own
+      DP_TRY(dpk_rmsnorm(ctx, x, norm_w, false, nullptr, false, nullptr, m->n, M, K, eps, false, 1.0f));
+      x = m->n;
+    }
+  }
+  if (!handled && prefill_tc && M >= 2) DP_TRY(dpk_gemm_q4k_tc_rowscaled(ctx, W, x, dst, M, N, K, 1.0f, prefill_tc == 1 ? 1 : 3, &handled, &f));
   if (!handled) DP_TRY(dpk_gemm_q4k_simt(ctx, W, x, DP_F32, dst, DP_F32, M, N, K, 1.0f));
   if (silu_done) *silu_done = handled && f.silu_done;
   if (residual && !(handled && f.residual_done)) DP_TRY(dpk_residual_add(ctx, residual, dst, y, (size_t)M * N, 1.0f));
@@ -868,10 +887,11 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       const bool emit = single && H % QK_K == 0 && H <= 8192 && dpk_gemv_q4k_fast_ok(nqkv, H);
       if (emit) {
         DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.in_norm, m->n, m->actq->dptr, H, c.eps);
-      } else {
+      } else if (single) {
         DP_TRY(dpk_rmsnorm(ctx, m->h, L.in_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
       }
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, emit));
+      if (single) DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->n, m->qkv, tokens, nqkv, H, nullptr, emit));
+      else DP_TRY(q4k_linear(m, (const uint8_t *)L.qkv->dptr, m->h, m->qkv, tokens, nqkv, H, nullptr, false, nullptr, nullptr, L.in_norm, c.eps));
     }
     // ---- attention parameters ----
     dpk_attn_params ap{};
@@ -963,12 +983,14 @@ static dp_status run_layers(dp_model *m, int tokens, bool decode, int seq, int s
       const bool emit = single && H % QK_K == 0 && H <= 8192 && dpk_gemv_q4k_fast_ok(2 * m->inter, H);
       if (emit) {
         DP_LAUNCH(ctx, rmsnorm_actq_kernel, 1, 256, 0, (const float *)m->h, (const float *)L.post_norm, m->n, m->actq->dptr, H, c.eps);
-      } else {
+      } else if (single) {
         DP_TRY(dpk_rmsnorm(ctx, m->h, L.post_norm, false, nullptr, false, nullptr, m->n, tokens, H, c.eps, false, 1.0f));
       }
-      // (rows on the tensor-core kernel: its epilogue stores silu(gate) * up and the raw gate|up rows are never written)
-      DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, emit,
-                        (!single && p == 1) ? m->actv : nullptr, &act_rows_ready));
+      // (rows on the tensor-core kernel: the norm is folded into the conversion of the rows, the epilogue stores
+      // silu(gate) * up and the raw gate|up rows are never written)
+      if (single) DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->n, m->gu, tokens, 2 * m->inter, H, nullptr, emit));
+      else DP_TRY(q4k_linear(m, (const uint8_t *)L.gateup->dptr, m->h, m->gu, tokens, 2 * m->inter, H, nullptr, false,
+                             p == 1 ? m->actv : nullptr, &act_rows_ready, L.post_norm, c.eps));
     }
     // ---- silu(gate) * up, down ----
     float *d_dst = p == 1 ? m->h : m->partial;
