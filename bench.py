@@ -593,6 +593,23 @@ def main():
                          "weights_GBps": model.weight_bytes / (ms / args.steps / 1000.0) / 1e9, "per": "GPU"},
             "model_weight_bytes_per_gpu": model.weight_bytes,
         }
+        if world == 1 and B == 1 and not args.no_kernels:
+            # whole-model prefill of the same prompt on the same model (host clock around the call, prompt upload and
+            # first-token read-back included), a secondary figure like the `kernels` record below
+            try:
+                times_p = []
+                for _ in range(3):
+                    model.reset()
+                    dev.sync()
+                    t0 = time.perf_counter()
+                    model.prefill(prompts[0], seq=0)
+                    dev.sync()
+                    times_p.append((time.perf_counter() - t0) * 1e3)
+                pms = statistics.median(times_p)
+                line["prefill"] = {"prompt_tokens": context, "ms": pms, "tokens_per_s": context / (pms / 1e3),
+                                   "note": "f32 activations, f32-exact product (three tensor-core products per K step)"}
+            except Exception as e:
+                line["prefill"] = {"failed": str(e)}
         model.destroy()
         model = None
         if world == 1 and not args.no_kernels:
